@@ -1,0 +1,199 @@
+/*
+ * C-ABI of the B200 (sm_100a) NVFP4 routed-expert inference kernels.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the
+ * given CUDA stream, allocates nothing, never synchronises, and returns 0 on
+ * success or a non-zero LM_ERR_* code (lm_last_error_string() then describes
+ * the failure for the calling thread).  All checks happen on the host before
+ * any launch.  Buffers are owned by the caller.
+ *
+ * The reference project has no C interface: its device code is generated from
+ * Python (CuTe DSL) and launched through TVM-FFI.  Each entry point below
+ * names the reference host function whose launch it replaces, by file:line in
+ * the reference checkout (package `lightmoe`).
+ *
+ * Data formats
+ *   q      E2M1 codes, two per byte, even contraction index in the low nibble
+ *   sf     E4M3 scale factor per 16 contraction elements, stored in 512-byte
+ *          atoms of 128 rows x 4 factors: byte (row%32)*16 + (row/32%4)*4 + k%4
+ *   varlen scale factors: expert e starts at atom row  m_indptr[e]/128 + e
+ */
+#ifndef LIGHTMOE_B200_H
+#define LIGHTMOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* lm_stream_t; /* cudaStream_t */
+
+enum {
+  LM_OK = 0,
+  LM_ERR_INVALID = 1, /* bad argument (shape, alignment, null pointer) */
+  LM_ERR_CUDA = 2,    /* a CUDA runtime or driver call failed */
+  LM_ERR_LIMIT = 3    /* size beyond a stated maximum */
+};
+
+enum { LM_DTYPE_BF16 = 0, LM_DTYPE_F32 = 1 };
+
+/* scale-factor placement of lm_quantize_rowwise */
+enum {
+  LM_SF_VARLEN = 0,  /* (1, ceil(rows/128)+E, K/64, 32,4,4), expert e at m_indptr[e]/128 + e */
+  LM_SF_BATCHED = 1, /* (E, ceil(rows_per_group/128), K/64, 32,4,4), equal-sized groups   */
+  LM_SF_LINEAR = 2   /* (rows, K/16) row-major bytes                                         */
+};
+
+enum {
+  LM_ACT_NONE = 0,
+  LM_ACT_SWIGLU = 1,
+  LM_ACT_SWIGLU_OAI = 2,
+  LM_ACT_GEGLU = 3,
+  LM_ACT_REGLU = 4,
+  LM_ACT_RELU2 = 5
+};
+
+enum { LM_OUT_BF16 = 0, LM_OUT_F32 = 1, LM_OUT_NVFP4 = 2 };
+
+int lm_version(void);
+const char* lm_last_error_string(void);
+
+/* Number of SMs of the current device (used to size persistent grids). */
+int lm_sm_count(int* out);
+
+/*
+ * Device-side status word of the GEMM kernels.  A kernel whose bounded wait
+ * on a barrier ran out sets a bit here and returns instead of hanging.
+ * Synchronises the stream.  *out == 0 means no kernel has reported a problem
+ * since the last lm_device_status_clear().
+ */
+int lm_device_status(uint32_t* out, lm_stream_t stream);
+int lm_device_status_clear(lm_stream_t stream);
+
+/*
+ * Row-wise NVFP4 quantization, optionally of gathered rows.
+ * Replaces nvfp4_quantize_rowwise (lightmoe/kernels/quantize/runtime.py:107-156,
+ * kernel body lightmoe/kernels/quantize/kernel.py:807-971).
+ *
+ *   x            (src_rows, features) BF16 or FP32, row stride = features
+ *   rows         number of output rows
+ *   m_indptr     (experts+1) int32 prefix of rows per expert; LM_SF_VARLEN only
+ *   rows_per_group  LM_SF_BATCHED only: every group has this many rows
+ *   scale_pair   float[2] = {pts, 1/pts} on the device
+ *   gather_idx   optional (rows) int32: output row r reads x[gather_idx[r]]
+ *   q            (rows, features/2) bytes
+ *   sf           scale factors in the layout named by sf_mode; within an atom
+ *                row that holds valid rows, rows past the group end get 0
+ *   te_math      0: sf = e4m3((amax/6)/pts), q = e2m1(x * ((1/pts)/sf))
+ *                1: sf = e4m3(amax * ((1/pts) * (1/6))), q = e2m1(x * (1/(sf*pts)))
+ * features must be a multiple of 64.
+ */
+int lm_quantize_rowwise(const void* x, int x_dtype, int64_t rows, int features,
+                        const int32_t* m_indptr, int experts, int64_t rows_per_group,
+                        const float* scale_pair, const int32_t* gather_idx, uint8_t* q,
+                        uint8_t* sf, int sf_mode, int te_math, lm_stream_t stream);
+
+/*
+ * Decode quantization: each token row is quantized once (te math) and its
+ * packed row and scale factors are written to every destination slot.
+ * Replaces nvfp4_quantize_decode (lightmoe/kernels/quantize/decode.py:1108-1165).
+ *   slots  (tokens*top_k) int32 destination rows, -1 = dropped
+ *   sf     varlen atoms addressed through m_indptr like LM_SF_VARLEN
+ */
+int lm_quantize_decode(const void* x, int64_t tokens, int features, int top_k,
+                       const int32_t* slots, const int32_t* topk_ids, const int32_t* m_indptr,
+                       int experts, const float* scale_pair, uint8_t* q, uint8_t* sf,
+                       lm_stream_t stream);
+
+/*
+ * Scratch size, in int32 elements, that lm_dispatch needs for `rows`
+ * assignments and `experts` experts.
+ */
+int64_t lm_dispatch_scratch_elems(int64_t rows, int experts);
+
+/*
+ * Stable expert-major permutation of (token, route) pairs.
+ * Replaces moe_dispatch (lightmoe/kernels/routing/dispatch.py:368-397).
+ *
+ *   topk_ids      (tokens, top_k) int32 expert of each pair, values in [0, experts)
+ *   topk_weights  (tokens, top_k) float
+ *   gather        (rows) int32   out: source token of each expert-major row
+ *   m_indptr      (experts+1)    out: prefix of rows per expert
+ *   probs         (rows) float   out: routing weight of each expert-major row
+ *   slots         (rows) int32   out: expert-major row of pair p = token*top_k + route
+ *   padded_offsets (experts)     out: inclusive prefix of ceil(count/plan_tile_rows)*128
+ *   scratch       int32 scratch of lm_dispatch_scratch_elems() elements; when
+ *                 rows <= 1024 it also receives the decode plan:
+ *                 scratch[0] = tile count, scratch[1+i] = expert + tile*experts,
+ *                 scratch[scratch_elems-experts+e] = first atom row of expert e
+ *   plan_tile_rows  rows per plan tile (8,16,32,64 or 128); the multi-block
+ *                 path (rows > 1024) always pads to 128
+ * experts <= 256.  rows = tokens*top_k <= 2^22.
+ */
+int lm_dispatch(const int32_t* topk_ids, const float* topk_weights, int64_t tokens, int top_k,
+                int experts, int32_t* gather, int32_t* m_indptr, float* probs, int32_t* slots,
+                int32_t* padded_offsets, int32_t* scratch, int64_t scratch_elems,
+                int plan_tile_rows, lm_stream_t stream);
+
+/*
+ * Deterministic top-k combine: out[t] = bf16(sum_j f32(rows[slot]) * w[slot]),
+ * j ascending, product rounded before the add, slot -1 skipped.
+ * Replaces moe_finalize (lightmoe/kernels/routing/combine.py:231-281).
+ *   routed_out (rows, hidden) BF16; slots (tokens*top_k); weights (rows) or NULL
+ *   out (tokens, hidden) BF16.  hidden must be a multiple of 8.
+ */
+int lm_finalize(const void* routed_out, const int32_t* slots, const float* weights, void* out,
+                int64_t tokens, int top_k, int hidden, int64_t routed_row_stride,
+                int64_t out_row_stride, lm_stream_t stream);
+
+/*
+ * Grouped / dense block-scaled FP4 GEMM:  out[rows_e, :] = alpha_e * A_e @ B_e^T
+ * with FP32 accumulation, optionally followed by a gated or unary activation
+ * and NVFP4 requantization of the result.
+ * Replaces GroupedNvfp4Gemm.prepare/launch
+ * (lightmoe/kernels/grouped/runtime.py:325-589) and DenseNvfp4Gemm
+ * (lightmoe/kernels/dense/runtime.py:54-143).
+ */
+typedef struct lm_gemm_args {
+  int32_t experts;       /* 1 for a dense GEMM */
+  int32_t n;             /* rows of each B_e (accumulator columns) */
+  int32_t k;             /* contraction length, multiple of 64 */
+  int32_t tile_m;        /* 128 */
+  int32_t tile_n;        /* 64, 128 or 256 (NVFP4 output: 128) */
+  int32_t out_kind;      /* LM_OUT_* */
+  int32_t activation;    /* LM_ACT_*; requires out_kind == LM_OUT_NVFP4 */
+  float clamp_limit;     /* 0 = no clamp */
+  float sigmoid_alpha;
+  float up_bias;
+  int32_t alpha_per_expert; /* 0: alpha[0], 1: alpha[e] */
+  int32_t dense;         /* 1: single group of `rows` rows, m_indptr ignored */
+  int32_t sf_tile_rows;  /* rows per scale-factor atom row group: 128 */
+  int32_t max_ctas;      /* 0 = one CTA per SM */
+  int64_t rows;          /* rows of A and of out */
+  const void* a;         /* (rows, k/2) bytes */
+  const void* b;         /* (experts, n, k/2) bytes */
+  void* out;             /* (rows, n) BF16/F32, or (rows, out_n/2) bytes */
+  const int32_t* m_indptr; /* (experts+1) */
+  const void* sfa;       /* varlen atoms, K/64 atom columns */
+  const void* sfb;       /* (experts, ceil(n/128), k/64, 512) */
+  const float* alpha;    /* (1) or (experts) */
+  void* out_sf;          /* NVFP4 output: varlen atoms with out_n/64 atom columns */
+  const float* out_scale; /* NVFP4 output: {pts, 1/pts} of the result */
+} lm_gemm_args;
+
+/* Caller-provided storage for a prepared GEMM (tensor maps + arguments). */
+typedef struct lm_gemm_plan {
+  uint64_t opaque[128];
+} lm_gemm_plan;
+
+/* Host only: validates `args` and encodes the TMA descriptors into `plan`. */
+int lm_gemm_prepare(const lm_gemm_args* args, lm_gemm_plan* plan);
+/* Launches a prepared GEMM.  Safe inside CUDA Graph capture. */
+int lm_gemm_launch(const lm_gemm_plan* plan, lm_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LIGHTMOE_B200_H */

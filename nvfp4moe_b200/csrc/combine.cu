@@ -1,0 +1,112 @@
+// Deterministic top-k combine (HBM-bound gather-reduce).
+//
+// One thread owns eight BF16 columns (16 bytes) of one token: it walks the
+// token's slots in route order, keeps the FP32 sum in registers and stores the
+// BF16 result once.  The product with the routing weight is rounded before the
+// add (mul.rn then add.rn, never fused), so the result is independent of the
+// launch shape and bit-identical from run to run.
+#include "common.cuh"
+
+namespace lm {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxTopK = 32;
+
+struct CombineParams {
+  const __nv_bfloat16* rows;
+  const int32_t* slots;
+  const float* weights;
+  __nv_bfloat16* out;
+  int64_t tokens;
+  int top_k;
+  int hidden;
+  int64_t row_stride;
+  int64_t out_stride;
+  int vec_per_row;
+};
+
+template <bool kWeighted>
+__global__ void __launch_bounds__(kThreads) combine_kernel(CombineParams p) {
+  const int64_t token = blockIdx.x;
+  const int vec = blockIdx.y * kThreads + threadIdx.x;
+  if (vec >= p.vec_per_row) return;
+  const int col = vec * 8;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+
+  const int32_t* slot_ptr = p.slots + token * p.top_k;
+  // Two gathers in flight: slot j+1 is loaded while slot j is accumulated.
+  int slot = __ldg(slot_ptr);
+  uint4 cur = make_uint4(0, 0, 0, 0);
+  float w = 0.0f;
+  if (slot >= 0) {
+    cur = __ldg(reinterpret_cast<const uint4*>(p.rows + slot * p.row_stride + col));
+    if (kWeighted) w = __ldg(p.weights + slot);
+  }
+  for (int j = 0; j < p.top_k; ++j) {
+    int next_slot = -1;
+    uint4 next = make_uint4(0, 0, 0, 0);
+    float next_w = 0.0f;
+    if (j + 1 < p.top_k) {
+      next_slot = __ldg(slot_ptr + j + 1);
+      if (next_slot >= 0) {
+        next = __ldg(reinterpret_cast<const uint4*>(p.rows + next_slot * p.row_stride + col));
+        if (kWeighted) next_w = __ldg(p.weights + next_slot);
+      }
+    }
+    if (slot >= 0) {
+      uint32_t words[4] = {cur.x, cur.y, cur.z, cur.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float lo = __uint_as_float(words[i] << 16);
+        float hi = __uint_as_float(words[i] & 0xFFFF0000u);
+        if (kWeighted) {
+          lo = __fmul_rn(lo, w);
+          hi = __fmul_rn(hi, w);
+        }
+        acc[2 * i] = __fadd_rn(acc[2 * i], lo);
+        acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], hi);
+      }
+    }
+    slot = next_slot;
+    cur = next;
+    w = next_w;
+  }
+  uint4 packed;
+  uint32_t* pw = reinterpret_cast<uint32_t*>(&packed);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+    pw[i] = *reinterpret_cast<uint32_t*>(&v);
+  }
+  *reinterpret_cast<uint4*>(p.out + token * p.out_stride + col) = packed;
+}
+
+}  // namespace
+}  // namespace lm
+
+extern "C" int lm_finalize(const void* routed_out, const int32_t* slots, const float* weights,
+                           void* out, int64_t tokens, int top_k, int hidden,
+                           int64_t routed_row_stride, int64_t out_row_stride, lm_stream_t stream) {
+  using namespace lm;
+  LM_REQUIRE(routed_out && slots && out, "finalize: null pointer");
+  LM_REQUIRE(hidden > 0 && hidden % 8 == 0, "finalize: hidden must be a multiple of 8");
+  LM_REQUIRE(routed_row_stride % 8 == 0 && out_row_stride % 8 == 0,
+             "finalize: row strides must keep 16-byte alignment");
+  LM_REQUIRE(top_k > 0 && top_k <= kMaxTopK, "finalize: top_k must be in 1..32");
+  LM_REQUIRE(tokens >= 0 && tokens < (1ll << 31), "finalize: bad token count");
+  if (tokens == 0) return LM_OK;
+  CombineParams p{static_cast<const __nv_bfloat16*>(routed_out), slots, weights,
+                  static_cast<__nv_bfloat16*>(out), tokens, top_k, hidden,
+                  routed_row_stride, out_row_stride, hidden / 8};
+  dim3 grid(static_cast<unsigned>(tokens), (p.vec_per_row + kThreads - 1) / kThreads);
+  if (weights != nullptr) {
+    combine_kernel<true><<<grid, kThreads, 0, as_stream(stream)>>>(p);
+  } else {
+    combine_kernel<false><<<grid, kThreads, 0, as_stream(stream)>>>(p);
+  }
+  LM_CUDA(cudaGetLastError());
+  return LM_OK;
+}

@@ -1,0 +1,762 @@
+// Persistent grouped / dense NVFP4 GEMM for sm_100a.
+//
+//   out[rows_e, :] = alpha_e * (A_e . SFA_e) (B_e . SFB_e)^T      FP32 accumulate
+//
+// Warp-specialised CTA of 192 threads, one CTA per SM:
+//   warp 0      TMA producer: A and B tiles (128-byte swizzle) with
+//               cp.async.bulk.tensor, scale-factor atoms with cp.async.bulk
+//   warp 1      allocates TMEM, copies scale factors smem -> TMEM (tcgen05.cp)
+//               and issues tcgen05.mma kind::mxf4nvf4 block-scaled MMAs
+//   warps 2..5  epilogue: tcgen05.ld the accumulator, scale, (activate and
+//               requantize to NVFP4,) store; each warp owns one TMEM lane quarter
+// The accumulator is double-buffered in TMEM so the epilogue of tile i overlaps
+// the main loop of tile i+1.  Tiles are assigned round-robin; every role walks
+// the same tile list, which it derives from m_indptr in shared memory.
+//
+// Rows of expert e are [m_indptr[e], m_indptr[e+1]).  A tile's A rows may run
+// into the next expert (or past the end, where TMA fills zeros); those rows are
+// computed and then not stored.  Every wait on an mbarrier is bounded: when it
+// runs out the CTA raises a bit in a status word and leaves the kernel.
+#include <cuda.h>
+
+#include <cstring>
+
+#include "common.cuh"
+
+namespace lm {
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kStageKBytes = 128;  // 256 FP4 values per row and stage: one swizzle span
+constexpr int kChunksPerStage = 4; // 64-element MMAs (= scale-factor atoms) per stage
+constexpr int kThreads = 192;
+constexpr int kMaxExperts = 256;
+constexpr uint32_t kTmemCols = 512;
+constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s
+
+__device__ uint32_t g_status = 0;
+
+enum : uint32_t {
+  kStatusProducerTimeout = 1u,
+  kStatusMmaTimeout = 2u,
+  kStatusEpilogueTimeout = 4u,
+};
+
+struct GemmParams {
+  int experts;
+  int n;
+  int n_tiles;
+  int k_stages;
+  int atom_cols;      // k / 64
+  int sfb_atom_rows;  // ceil(n / 128)
+  int dense;
+  int alpha_per_expert;
+  int64_t rows;
+  const int32_t* m_indptr;
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  const float* alpha;
+  void* out;
+  uint8_t* out_sf;
+  const float* out_scale;
+  int out_atom_cols;  // NVFP4 output: out_n / 64
+  float clamp_limit;
+  float sigmoid_alpha;
+  float up_bias;
+};
+
+// ------------------------------------------------------------------ PTX glue
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting (this wait ran out, or
+// another role's did); the caller then leaves its loop.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t who) {
+  for (int i = 0; i < 64; ++i)
+    if (mbar_try(bar, parity)) return true;
+  const long long start = clock64();
+  while (true) {
+    if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - start > kWaitLimitCycles) {
+      *abort_flag = 1;
+      atomicOr(&g_status, who);
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+// 32 lanes x 128 bit from shared memory, replicated to the four lane quarters.
+__device__ __forceinline__ void tc_copy_sf(uint32_t tmem_addr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(smem_desc)
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X "
+      "[%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_load32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of
+// 128 bytes, eight-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);  // start address
+  d |= static_cast<uint64_t>(1) << 16;                      // leading byte offset (unused)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;              // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                      // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;                      // SWIZZLE_128B
+  return d;
+}
+
+// Descriptor of one 512-byte scale-factor atom: 32 rows of 16 bytes, no
+// swizzle, eight-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t desc_sf_atom(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+
+// Instruction descriptor: E2M1 x E2M1, UE4M3 scale factors, K-major A and B,
+// M = 128, N = n, K = 64, FP32 accumulate.
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+  return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (0u << 23) |
+         (static_cast<uint32_t>(kTileM >> 4) << 24);
+}
+
+template <int kTileN>
+struct SmemLayout {
+  static constexpr int kABytes = kTileM * kStageKBytes;
+  static constexpr int kBBytes = kTileN * kStageKBytes;
+  static constexpr int kSfaBytes = kChunksPerStage * 512;
+  static constexpr int kSfbAtomRows = (kTileN + 127) / 128;
+  static constexpr int kSfbBytes = kSfbAtomRows * kChunksPerStage * 512;
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kStages = (kTileN <= 128) ? 6 : 4;
+  static constexpr int kAccStages = (kTileN <= 128) ? 2 : 1;
+  static constexpr int kMiscBytes = 4096;
+  static constexpr int kTotal = kStages * kStageBytes + kMiscBytes + 1024;
+  static_assert(kStageBytes % 1024 == 0, "stages must keep 1024-byte alignment");
+};
+
+struct Misc {  // lives after the pipeline stages
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int total_m_tiles;
+  int pad;
+  int cu[kMaxExperts + 1];
+  int prefix[kMaxExperts + 1];
+};
+static_assert(sizeof(Misc) <= 4096, "misc block too large");
+
+struct TileCoord {
+  int expert;
+  int row0;      // first A / out row of the tile
+  int valid;     // rows of the tile that belong to the expert
+  int sf_row;    // scale-factor atom row of the tile
+  int n_tile;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const Misc* m, const GemmParams& p, int tile) {
+  const int mt = tile / p.n_tiles;
+  TileCoord t;
+  t.n_tile = tile - mt * p.n_tiles;
+  int lo = 0, hi = p.experts;
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (m->prefix[mid] <= mt) lo = mid; else hi = mid;
+  }
+  const int local = mt - m->prefix[lo];
+  const int begin = m->cu[lo];
+  const int count = m->cu[lo + 1] - begin;
+  t.expert = lo;
+  t.row0 = begin + local * kTileM;
+  t.valid = min(kTileM, count - local * kTileM);
+  t.sf_row = begin / kTileM + lo + local;
+  return t;
+}
+
+// ------------------------------------------------------------- activations
+template <int kAct>
+__device__ __forceinline__ float gated_value(float g, float u, const GemmParams& p) {
+  if (p.clamp_limit > 0.0f) {
+    g = fminf(g, p.clamp_limit);
+    u = fmaxf(fminf(u, p.clamp_limit), -p.clamp_limit);
+  }
+  if (kAct == LM_ACT_SWIGLU || kAct == LM_ACT_SWIGLU_OAI) {
+    float sig;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(sig) : "f"(1.0f + __expf(-p.sigmoid_alpha * g)));
+    return g * sig * (u + p.up_bias);
+  }
+  if (kAct == LM_ACT_GEGLU) {
+    const float root = 0.7978845608028654f;  // sqrt(2/pi)
+    float arg = root * (g + 0.044715f * g * g * g);
+    float th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(arg));
+    return 0.5f * g * (1.0f + th) * u;
+  }
+  return fmaxf(g, 0.0f) * u;  // reglu
+}
+
+// Requantize 16 post-activation values: returns the E4M3 byte, packs 8 bytes.
+__device__ __forceinline__ uint32_t requant16(const float* h, float inv_pts, uint32_t* packed) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(h[i]));
+  const float scaled = amax * (inv_pts * inv6());
+  const uint32_t sf = f32_to_e4m3(scaled);
+  float rescale;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rescale) : "f"(e4m3_to_f32(sf)));
+  rescale = fminf(rescale * inv_pts, kFltMax);
+  float s[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s[i] = h[i] * rescale;
+  packed[0] = f32x8_to_e2m1(s);
+  packed[1] = f32x8_to_e2m1(s + 8);
+  return sf;
+}
+
+// ------------------------------------------------------------------ kernel
+template <int kTileN, int kOut, int kAct>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const GemmParams p) {
+  using L = SmemLayout<kTileN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  Misc* misc = reinterpret_cast<Misc*>(smem_gen + L::kStages * L::kStageBytes);
+  volatile int* abort_flag = &misc->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- one-time setup
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::kStages; ++s) {
+      mbar_init(smem_u32(&misc->full[s]), 1);
+      mbar_init(smem_u32(&misc->empty[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&misc->acc_full[s]), 1);
+      mbar_init(smem_u32(&misc->acc_empty[s]), 4);
+    }
+    misc->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&misc->tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // expert boundaries -> shared memory
+  if (p.dense) {
+    if (threadIdx.x == 0) {
+      misc->cu[0] = 0;
+      misc->cu[1] = static_cast<int>(p.rows);
+    }
+  } else {
+    for (int e = threadIdx.x; e <= p.experts; e += kThreads) misc->cu[e] = __ldg(p.m_indptr + e);
+  }
+  __syncthreads();
+  if (warp == 2) {
+    // exclusive prefix of row tiles per expert; each lane owns 8 experts
+    int local[8];
+    int sum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      int e = lane * 8 + i;
+      int tiles = 0;
+      if (e < p.experts) tiles = (misc->cu[e + 1] - misc->cu[e] + kTileM - 1) / kTileM;
+      local[i] = sum;
+      sum += tiles;
+    }
+    int incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int t = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+      if (lane >= d) incl += t;
+    }
+    const int base = incl - sum;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      int e = lane * 8 + i;
+      if (e <= p.experts) misc->prefix[e] = base + local[i];
+    }
+    if (lane == 31) misc->total_m_tiles = incl;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  const uint32_t tmem_base = misc->tmem_base;
+  const int total_tiles = misc->total_m_tiles * p.n_tiles;
+  const uint32_t acc_col0 = 0;
+  const uint32_t sfa_col0 = L::kAccStages * kTileN;
+  const uint32_t sfb_col0 = sfa_col0 + kChunksPerStage * 4;
+
+  if (warp == 0) {
+    // ===================================================== TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        const TileCoord t = decode_tile(misc, p, tile);
+        const int b_row = t.expert * p.n + t.n_tile * kTileN;
+        const uint8_t* sfa_src = p.sfa + static_cast<int64_t>(t.sf_row) * p.atom_cols * 512;
+        const int sfb_row0 = t.expert * p.sfb_atom_rows + (t.n_tile * kTileN) / 128;
+        bool ok = true;
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          ok = mbar_wait(smem_u32(&misc->empty[stage]), phase ^ 1u, abort_flag, kStatusProducerTimeout);
+          if (!ok) break;
+          const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
+          const uint32_t sf_bytes = chunks * 512;
+          const uint32_t bar = smem_u32(&misc->full[stage]);
+          const uint32_t st = smem_base + stage * L::kStageBytes;
+          mbar_expect_tx(bar, L::kABytes + L::kBBytes + sf_bytes * (1 + L::kSfbAtomRows));
+          tma_load_2d(st, &tmap_a, ks * kStageKBytes, t.row0, bar);
+          tma_load_2d(st + L::kABytes, &tmap_b, ks * kStageKBytes, b_row, bar);
+          bulk_load(st + L::kABytes + L::kBBytes, sfa_src + static_cast<int64_t>(ks) * kChunksPerStage * 512,
+                    sf_bytes, bar);
+#pragma unroll
+          for (int j = 0; j < L::kSfbAtomRows; ++j) {
+            const uint8_t* src = p.sfb + (static_cast<int64_t>(sfb_row0 + j) * p.atom_cols +
+                                          static_cast<int64_t>(ks) * kChunksPerStage) * 512;
+            bulk_load(st + L::kABytes + L::kBBytes + L::kSfaBytes + j * kChunksPerStage * 512, src,
+                      sf_bytes, bar);
+          }
+          if (++stage == L::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ===================================================== MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(kTileN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        bool ok = mbar_wait(smem_u32(&misc->acc_empty[acc]), acc_phase ^ 1u, abort_flag, kStatusMmaTimeout);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc_col0 + acc * kTileN;
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusMmaTimeout);
+          if (!ok) break;
+          tc_fence_after();
+          const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
+          const uint32_t st = smem_base + stage * L::kStageBytes;
+          const uint32_t sfa_smem = st + L::kABytes + L::kBBytes;
+          const uint32_t sfb_smem = sfa_smem + L::kSfaBytes;
+          const uint64_t a_desc = desc_sw128(st);
+          const uint64_t b_desc = desc_sw128(st + L::kABytes);
+          for (int c = 0; c < chunks; ++c) {
+            const uint32_t sfa_t = tmem_base + sfa_col0 + c * 4;
+            const uint32_t sfb_t = tmem_base + sfb_col0 + c * 4 * L::kSfbAtomRows;
+            tc_copy_sf(sfa_t, desc_sf_atom(sfa_smem + c * 512));
+#pragma unroll
+            for (int j = 0; j < L::kSfbAtomRows; ++j)
+              tc_copy_sf(sfb_t + j * 4, desc_sf_atom(sfb_smem + (j * kChunksPerStage + c) * 512));
+            // 64 FP4 values = 32 bytes along K: +2 in 16-byte descriptor units
+            tc_mma_nvf4(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t, sfb_t,
+                        (ks > 0 || c > 0) ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&misc->empty[stage]));
+          if (++stage == L::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(&misc->acc_full[acc]));
+        if (++acc == L::kAccStages) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ===================================================== epilogue
+    const int quarter = warp & 3;           // TMEM lanes this warp may read
+    const int r = quarter * 32 + lane;      // row of the tile
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    float inv_h = 0.0f;
+    if (kOut == LM_OUT_NVFP4) inv_h = __ldg(p.out_scale + 1);
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const TileCoord t = decode_tile(misc, p, tile);
+      const float alpha = __ldg(p.alpha + (p.alpha_per_expert ? t.expert : 0));
+      if (!mbar_wait(smem_u32(&misc->acc_full[acc]), acc_phase, abort_flag, kStatusEpilogueTimeout)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc_col0 + acc * kTileN;
+      const bool row_ok = r < t.valid;
+      const int64_t out_row = static_cast<int64_t>(t.row0) + r;
+
+      if (kOut == LM_OUT_NVFP4) {
+        constexpr bool kGated = kAct != LM_ACT_RELU2;
+        constexpr int kOutPerChunk = kGated ? 16 : 32;       // outputs per 32 accumulator columns
+        constexpr int kOutPerTile = kOutPerChunk * (kTileN / 32);
+        const int out_n = p.out_atom_cols * 64;
+        uint32_t qwords[kOutPerTile / 8];
+        uint32_t sfbytes[kOutPerTile / 16];
+#pragma unroll
+        for (int c = 0; c < kTileN / 32; ++c) {
+          uint32_t v[32];
+          tc_load32(taddr + c * 32, v);
+          tc_wait_ld();
+          if (kGated) {
+            float h[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              h[i] = gated_value<kAct>(__uint_as_float(v[2 * i]) * alpha,
+                                       __uint_as_float(v[2 * i + 1]) * alpha, p);
+            sfbytes[c] = requant16(h, inv_h, &qwords[2 * c]);
+          } else {
+            float h[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float x = fmaxf(__uint_as_float(v[i]) * alpha, 0.0f);
+              h[i] = x * x;
+            }
+            sfbytes[2 * c] = requant16(h, inv_h, &qwords[4 * c]);
+            sfbytes[2 * c + 1] = requant16(h + 16, inv_h, &qwords[4 * c + 2]);
+          }
+        }
+        if (row_ok) {
+          uint8_t* q = static_cast<uint8_t*>(p.out) + out_row * (out_n >> 1) +
+                       static_cast<int64_t>(t.n_tile) * (kOutPerTile >> 1);
+#pragma unroll
+          for (int i = 0; i < kOutPerTile / 32; ++i)
+            reinterpret_cast<uint4*>(q)[i] =
+                make_uint4(qwords[4 * i], qwords[4 * i + 1], qwords[4 * i + 2], qwords[4 * i + 3]);
+#pragma unroll
+          for (int w = 0; w < kOutPerTile / 64; ++w) {
+            uint32_t word = sfbytes[4 * w] | (sfbytes[4 * w + 1] << 8) | (sfbytes[4 * w + 2] << 16) |
+                            (sfbytes[4 * w + 3] << 24);
+            const int atom_col = t.n_tile * (kOutPerTile / 64) + w;
+            uint8_t* dst = p.out_sf + (static_cast<int64_t>(t.sf_row) * p.out_atom_cols + atom_col) * 512 +
+                           lane * 16 + quarter * 4;
+            *reinterpret_cast<uint32_t*>(dst) = word;
+          }
+        }
+      } else {
+        const int col0 = t.n_tile * kTileN;
+#pragma unroll
+        for (int c = 0; c < kTileN / 32; ++c) {
+          uint32_t v[32];
+          tc_load32(taddr + c * 32, v);
+          tc_wait_ld();
+          const int col = col0 + c * 32;
+          if (row_ok && col < p.n) {
+            if (kOut == LM_OUT_BF16) {
+              __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + out_row * p.n + col;
+              if (col + 32 <= p.n) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  uint32_t w[4];
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]) * alpha,
+                                                             __uint_as_float(v[8 * i + 2 * j + 1]) * alpha);
+                    w[j] = *reinterpret_cast<uint32_t*>(&b);
+                  }
+                  reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+              } else {
+                for (int i = 0; i < 32 && col + i < p.n; ++i)
+                  dst[i] = __float2bfloat16_rn(__uint_as_float(v[i]) * alpha);
+              }
+            } else {
+              float* dst = static_cast<float*>(p.out) + out_row * p.n + col;
+              if (col + 32 <= p.n) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  reinterpret_cast<float4*>(dst)[i] =
+                      make_float4(__uint_as_float(v[4 * i]) * alpha, __uint_as_float(v[4 * i + 1]) * alpha,
+                                  __uint_as_float(v[4 * i + 2]) * alpha, __uint_as_float(v[4 * i + 3]) * alpha);
+              } else {
+                for (int i = 0; i < 32 && col + i < p.n; ++i) dst[i] = __uint_as_float(v[i]) * alpha;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[acc]));
+      if (++acc == L::kAccStages) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---- teardown
+  __syncwarp();
+  if (*abort_flag) {
+    // give copies still in flight time to land before shared memory is released
+    const long long start = clock64();
+    while (clock64() - start < 2000000ll) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+// --------------------------------------------------------------- host side
+struct PlanData {
+  uint32_t magic;
+  int32_t tile_n;
+  int32_t out_kind;
+  int32_t activation;
+  int32_t grid;
+  int32_t smem_bytes;
+  GemmParams params;
+  alignas(64) CUtensorMap map_a;
+  alignas(64) CUtensorMap map_b;
+};
+static_assert(sizeof(PlanData) <= sizeof(lm_gemm_plan), "plan storage too small");
+constexpr uint32_t kPlanMagic = 0x4C4D4750u;
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+        res == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(ptr);
+  }
+  return fn;
+}
+
+int encode_bytes_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows,
+                    uint32_t box_rows) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return set_error(LM_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t dims[2] = {inner_bytes, rows};
+  cuuint64_t strides[1] = {inner_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kStageKBytes), box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(LM_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+  return LM_OK;
+}
+
+template <int kTileN, int kOut, int kAct>
+int launch_variant(const PlanData& pd, cudaStream_t stream) {
+  auto kernel = gemm_kernel<kTileN, kOut, kAct>;
+  static bool configured = false;
+  if (!configured) {
+    LM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 SmemLayout<kTileN>::kTotal));
+    configured = true;
+  }
+  kernel<<<pd.grid, kThreads, SmemLayout<kTileN>::kTotal, stream>>>(pd.map_a, pd.map_b, pd.params);
+  LM_CUDA(cudaGetLastError());
+  return LM_OK;
+}
+
+template <int kTileN>
+int launch_tile(const PlanData& pd, cudaStream_t stream) {
+  if (pd.out_kind == LM_OUT_BF16) return launch_variant<kTileN, LM_OUT_BF16, LM_ACT_NONE>(pd, stream);
+  if (pd.out_kind == LM_OUT_F32) return launch_variant<kTileN, LM_OUT_F32, LM_ACT_NONE>(pd, stream);
+  switch (pd.activation) {
+    case LM_ACT_SWIGLU: return launch_variant<kTileN, LM_OUT_NVFP4, LM_ACT_SWIGLU>(pd, stream);
+    case LM_ACT_SWIGLU_OAI: return launch_variant<kTileN, LM_OUT_NVFP4, LM_ACT_SWIGLU_OAI>(pd, stream);
+    case LM_ACT_GEGLU: return launch_variant<kTileN, LM_OUT_NVFP4, LM_ACT_GEGLU>(pd, stream);
+    case LM_ACT_REGLU: return launch_variant<kTileN, LM_OUT_NVFP4, LM_ACT_REGLU>(pd, stream);
+    case LM_ACT_RELU2: return launch_variant<kTileN, LM_OUT_NVFP4, LM_ACT_RELU2>(pd, stream);
+  }
+  return set_error(LM_ERR_INVALID, "gemm: unknown activation");
+}
+
+}  // namespace
+}  // namespace lm
+
+extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
+  using namespace lm;
+  LM_REQUIRE(a && plan, "gemm: null argument");
+  LM_REQUIRE(a->experts > 0 && a->experts <= kMaxExperts, "gemm: 1..256 experts");
+  LM_REQUIRE(a->n > 0 && a->k > 0 && a->k % 64 == 0, "gemm: K must be a positive multiple of 64");
+  LM_REQUIRE(a->rows > 0 && a->rows < (1ll << 31), "gemm: rows out of range");
+  LM_REQUIRE(a->a && a->b && a->out && a->sfa && a->sfb && a->alpha, "gemm: null operand");
+  LM_REQUIRE(a->dense || a->m_indptr, "gemm: grouped GEMM needs m_indptr");
+  LM_REQUIRE(!a->dense || a->experts == 1, "gemm: dense GEMM has one group");
+  LM_REQUIRE(a->out_kind >= LM_OUT_BF16 && a->out_kind <= LM_OUT_NVFP4, "gemm: unknown output kind");
+  LM_REQUIRE((reinterpret_cast<uintptr_t>(a->a) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->b) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(a->sfa) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->sfb) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(a->out) & 15) == 0,
+             "gemm: operands must be 16-byte aligned");
+  PlanData pd{};
+  pd.magic = kPlanMagic;
+  pd.tile_n = 128;
+  pd.out_kind = a->out_kind;
+  pd.activation = a->activation;
+  GemmParams& p = pd.params;
+  if (a->out_kind == LM_OUT_NVFP4) {
+    LM_REQUIRE(a->activation >= LM_ACT_SWIGLU && a->activation <= LM_ACT_RELU2,
+               "gemm: NVFP4 output requires an activation");
+    LM_REQUIRE(a->n % 128 == 0, "gemm: NVFP4 output requires N aligned to 128");
+    LM_REQUIRE(a->out_sf && a->out_scale, "gemm: NVFP4 output needs out_sf and out_scale");
+    LM_REQUIRE((reinterpret_cast<uintptr_t>(a->out_sf) & 15) == 0, "gemm: out_sf must be 16-byte aligned");
+    const int out_n = a->activation == LM_ACT_RELU2 ? a->n : a->n / 2;
+    LM_REQUIRE(out_n % 64 == 0, "gemm: NVFP4 output width must be a multiple of 64");
+    p.out_atom_cols = out_n / 64;
+  } else {
+    LM_REQUIRE(a->activation == LM_ACT_NONE, "gemm: activations require NVFP4 output");
+    LM_REQUIRE(a->n % 8 == 0, "gemm: N must be a multiple of 8");
+  }
+  p.experts = a->experts;
+  p.n = a->n;
+  p.n_tiles = (a->n + pd.tile_n - 1) / pd.tile_n;
+  p.atom_cols = a->k / 64;
+  p.k_stages = (p.atom_cols + kChunksPerStage - 1) / kChunksPerStage;
+  p.sfb_atom_rows = (a->n + 127) / 128;
+  p.dense = a->dense;
+  p.alpha_per_expert = a->alpha_per_expert;
+  p.rows = a->rows;
+  p.m_indptr = a->m_indptr;
+  p.sfa = static_cast<const uint8_t*>(a->sfa);
+  p.sfb = static_cast<const uint8_t*>(a->sfb);
+  p.alpha = a->alpha;
+  p.out = a->out;
+  p.out_sf = static_cast<uint8_t*>(a->out_sf);
+  p.out_scale = a->out_scale;
+  p.clamp_limit = a->clamp_limit;
+  p.sigmoid_alpha = a->sigmoid_alpha;
+  p.up_bias = a->up_bias;
+  const int sms = sm_count();
+  LM_REQUIRE(sms > 0, "gemm: no CUDA device");
+  pd.grid = a->max_ctas > 0 ? a->max_ctas : sms;
+  // more CTAs than tiles would only idle: rows/128 + experts bounds the row tiles
+  const int64_t max_tiles = ((a->rows + kTileM - 1) / kTileM + a->experts) * p.n_tiles;
+  if (pd.grid > max_tiles) pd.grid = static_cast<int>(max_tiles);
+  int rc = encode_bytes_2d(&pd.map_a, a->a, static_cast<uint64_t>(a->k / 2), static_cast<uint64_t>(a->rows), kTileM);
+  if (rc != LM_OK) return rc;
+  rc = encode_bytes_2d(&pd.map_b, a->b, static_cast<uint64_t>(a->k / 2),
+                       static_cast<uint64_t>(a->experts) * a->n, pd.tile_n);
+  if (rc != LM_OK) return rc;
+  memcpy(plan, &pd, sizeof(pd));
+  return LM_OK;
+}
+
+extern "C" int lm_gemm_launch(const lm_gemm_plan* plan, lm_stream_t stream) {
+  using namespace lm;
+  LM_REQUIRE(plan, "gemm: null plan");
+  PlanData pd;  // the caller's storage need not be 64-byte aligned: work on a copy
+  memcpy(&pd, plan, sizeof(pd));
+  LM_REQUIRE(pd.magic == kPlanMagic, "gemm: plan was not prepared");
+  return launch_tile<128>(pd, as_stream(stream));
+}
+
+extern "C" int lm_device_status(uint32_t* out, lm_stream_t stream) {
+  using namespace lm;
+  LM_REQUIRE(out, "device_status: null pointer");
+  LM_CUDA(cudaStreamSynchronize(as_stream(stream)));
+  LM_CUDA(cudaMemcpyFromSymbol(out, g_status, sizeof(uint32_t)));
+  return LM_OK;
+}
+
+extern "C" int lm_device_status_clear(lm_stream_t stream) {
+  using namespace lm;
+  const uint32_t zero = 0;
+  LM_CUDA(cudaStreamSynchronize(as_stream(stream)));
+  LM_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(uint32_t)));
+  return LM_OK;
+}

@@ -1,0 +1,307 @@
+// Row-wise BF16/FP32 -> NVFP4 quantization (HBM-bound).
+//
+// One CTA covers one 128-row scale-factor atom row and 512 features.  A warp
+// streams one row slice at a time: each lane owns one 16-element group (32 B of
+// BF16), so a warp reads 1 KB contiguous and writes 256 B of packed codes.
+// Scale factors are staged in shared memory in atom order and leave the CTA as
+// 16-byte stores, so every 512-byte atom is written whole.
+#include "common.cuh"
+
+namespace lm {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kTileRows = 128;
+constexpr int kTileCols = 512;  // 32 lanes x 16 elements
+
+struct QuantParams {
+  const void* x;
+  int64_t rows;
+  int features;
+  const int32_t* m_indptr;
+  int experts;
+  int64_t rows_per_group;
+  int tiles_per_group;
+  const float* scale_pair;
+  const int32_t* gather;
+  uint8_t* q;
+  uint8_t* sf;
+  int sf_mode;
+  int te_math;
+};
+
+template <typename In>
+__device__ __forceinline__ void load16(const In* p, float* v);
+
+template <>
+__device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, float* v) {
+  const uint4* src = reinterpret_cast<const uint4*>(p);
+  uint4 a = __ldg(src);
+  uint4 b = __ldg(src + 1);
+  uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+
+template <>
+__device__ __forceinline__ void load16<float>(const float* p, float* v) {
+  const float4* src = reinterpret_cast<const float4*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float4 t = __ldg(src + i);
+    v[4 * i] = t.x;
+    v[4 * i + 1] = t.y;
+    v[4 * i + 2] = t.z;
+    v[4 * i + 3] = t.w;
+  }
+}
+
+// Quantize one 16-element group.  Returns the scale-factor byte; writes the
+// eight packed bytes to `packed`.
+__device__ __forceinline__ uint32_t quantize_group(const float* v, float pts, float inv_pts,
+                                                   bool te_math, uint2* packed) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  float scaled;
+  if (te_math) {
+    scaled = __fmul_rn(amax, __fmul_rn(inv_pts, inv6()));
+  } else {
+    scaled = __fdiv_rn(__fdiv_rn(amax, kF4Max), pts);
+  }
+  scaled = fmaxf(fminf(scaled, kE4M3Max), kE4M3MinSf);
+  uint32_t sf_byte = f32_to_e4m3(scaled);
+  float sf_value = e4m3_to_f32(sf_byte);
+  float factor = te_math ? __fdiv_rn(1.0f, __fmul_rn(sf_value, pts)) : __fdiv_rn(inv_pts, sf_value);
+  float s[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s[i] = __fmul_rn(v[i], factor);
+  packed->x = f32x8_to_e2m1(s);
+  packed->y = f32x8_to_e2m1(s + 8);
+  return sf_byte;
+}
+
+template <typename In>
+__global__ void __launch_bounds__(kThreads) quantize_rowwise_kernel(QuantParams p) {
+  __shared__ __align__(16) uint8_t s_sf[(kTileCols / 64) * 512];
+  __shared__ int s_group[4];  // group, local tile, first row, valid rows
+
+  const int tid = threadIdx.x;
+  const int64_t atom_row = blockIdx.x;
+  const int col0 = blockIdx.y * kTileCols;
+
+  // ---- which rows does this atom row hold?
+  if (tid == 0) s_group[3] = 0;
+  __syncthreads();
+  if (p.sf_mode == LM_SF_VARLEN) {
+    for (int e = tid; e < p.experts; e += kThreads) {
+      int lo = __ldg(p.m_indptr + e);
+      int hi = __ldg(p.m_indptr + e + 1);
+      int64_t first = lo / kTileRows + e;
+      int64_t next = hi / kTileRows + e + 1;
+      if (atom_row >= first && atom_row < next) {
+        int lt = static_cast<int>(atom_row - first);
+        int remaining = (hi - lo) - lt * kTileRows;
+        if (remaining > 0) {
+          s_group[0] = e;
+          s_group[1] = lt;
+          s_group[2] = lo + lt * kTileRows;
+          s_group[3] = remaining < kTileRows ? remaining : kTileRows;
+        }
+      }
+    }
+  } else if (tid == 0) {
+    int64_t group = p.sf_mode == LM_SF_BATCHED ? atom_row / p.tiles_per_group : 0;
+    int lt = p.sf_mode == LM_SF_BATCHED ? static_cast<int>(atom_row % p.tiles_per_group)
+                                        : static_cast<int>(atom_row);
+    int64_t group_rows = p.sf_mode == LM_SF_BATCHED ? p.rows_per_group : p.rows;
+    int64_t remaining = group_rows - static_cast<int64_t>(lt) * kTileRows;
+    s_group[0] = static_cast<int>(group);
+    s_group[1] = lt;
+    s_group[2] = 0;
+    s_group[3] = remaining <= 0 ? 0 : (remaining < kTileRows ? static_cast<int>(remaining) : kTileRows);
+  }
+  __syncthreads();
+  const int valid = s_group[3];
+  if (valid == 0) return;
+  int64_t row0;
+  if (p.sf_mode == LM_SF_VARLEN) {
+    row0 = s_group[2];
+  } else {
+    row0 = static_cast<int64_t>(s_group[0]) * (p.sf_mode == LM_SF_BATCHED ? p.rows_per_group : 0) +
+           static_cast<int64_t>(s_group[1]) * kTileRows;
+  }
+
+  const bool blocked = p.sf_mode != LM_SF_LINEAR;
+  if (blocked && valid < kTileRows) {
+    uint4* z = reinterpret_cast<uint4*>(s_sf);
+    for (int i = tid; i < static_cast<int>(sizeof(s_sf) / 16); i += kThreads) z[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+  }
+
+  const float pts = __ldg(p.scale_pair);
+  const float inv_pts = __ldg(p.scale_pair + 1);
+  const bool te = p.te_math != 0;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int col = col0 + lane * 16;
+  const bool col_ok = col < p.features;
+  const In* x = static_cast<const In*>(p.x);
+  const int groups_per_row = p.features >> 4;
+
+  constexpr int kUnroll = 4;
+  for (int base = warp; base < valid; base += kWarps * kUnroll) {
+    float v[kUnroll][16];
+    bool ok[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      int r = base + u * kWarps;
+      ok[u] = col_ok && r < valid;
+      if (ok[u]) {
+        int64_t src = row0 + r;
+        if (p.gather != nullptr) src = __ldg(p.gather + src);
+        load16<In>(x + src * p.features + col, v[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (!ok[u]) continue;
+      int r = base + u * kWarps;
+      uint2 packed;
+      uint32_t sf_byte = quantize_group(v[u], pts, inv_pts, te, &packed);
+      int64_t out_row = row0 + r;
+      *reinterpret_cast<uint2*>(p.q + out_row * (p.features >> 1) + (col >> 1)) = packed;
+      if (blocked) {
+        s_sf[(lane >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (lane & 3)] =
+            static_cast<uint8_t>(sf_byte);
+      } else {
+        p.sf[out_row * groups_per_row + (col >> 4)] = static_cast<uint8_t>(sf_byte);
+      }
+    }
+  }
+  if (!blocked) return;
+  __syncthreads();
+
+  // ---- atoms leave as 16-byte stores: thread i -> atom i / 32, piece i % 32
+  const int atom_cols = p.features >> 6;
+  const int atom = tid >> 5;
+  const int atom_col = (col0 >> 6) + atom;
+  if (atom_col < atom_cols) {
+    uint4 piece = reinterpret_cast<const uint4*>(s_sf)[tid];
+    uint8_t* dst = p.sf + (atom_row * atom_cols + atom_col) * 512 + (tid & 31) * 16;
+    *reinterpret_cast<uint4*>(dst) = piece;
+  }
+}
+
+// ---------------------------------------------------------------- decode path
+// One warp per (token, 512-feature slice): quantize once, store to each slot.
+struct DecodeQuantParams {
+  const __nv_bfloat16* x;
+  int64_t tokens;
+  int features;
+  int top_k;
+  const int32_t* slots;
+  const int32_t* topk_ids;
+  const int32_t* m_indptr;
+  const float* scale_pair;
+  uint8_t* q;
+  uint8_t* sf;
+};
+
+__global__ void __launch_bounds__(kThreads) quantize_decode_kernel(DecodeQuantParams p) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int64_t token = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  if (token >= p.tokens) return;
+  const int col = blockIdx.y * kTileCols + lane * 16;
+  if (col >= p.features) return;
+  const float pts = __ldg(p.scale_pair);
+  const float inv_pts = __ldg(p.scale_pair + 1);
+  float v[16];
+  load16<__nv_bfloat16>(p.x + token * p.features + col, v);
+  uint2 packed;
+  uint32_t sf_byte = quantize_group(v, pts, inv_pts, true, &packed);
+  const int atom_cols = p.features >> 6;
+  for (int j = 0; j < p.top_k; ++j) {
+    int slot = __ldg(p.slots + token * p.top_k + j);
+    if (slot < 0) continue;
+    int e = __ldg(p.topk_ids + token * p.top_k + j);
+    int lo = __ldg(p.m_indptr + e);
+    int local = slot - lo;
+    *reinterpret_cast<uint2*>(p.q + static_cast<int64_t>(slot) * (p.features >> 1) + (col >> 1)) = packed;
+    int64_t atom_row = lo / kTileRows + e + local / kTileRows;
+    p.sf[sf_offset(atom_row, atom_cols, local % kTileRows, col >> 4)] = static_cast<uint8_t>(sf_byte);
+  }
+}
+
+}  // namespace
+}  // namespace lm
+
+extern "C" int lm_quantize_rowwise(const void* x, int x_dtype, int64_t rows, int features,
+                                   const int32_t* m_indptr, int experts, int64_t rows_per_group,
+                                   const float* scale_pair, const int32_t* gather_idx, uint8_t* q,
+                                   uint8_t* sf, int sf_mode, int te_math, lm_stream_t stream) {
+  using namespace lm;
+  LM_REQUIRE(x && scale_pair && q && sf, "quantize: null pointer");
+  LM_REQUIRE(x_dtype == LM_DTYPE_BF16 || x_dtype == LM_DTYPE_F32, "quantize: x must be BF16 or FP32");
+  LM_REQUIRE(features > 0 && features % 64 == 0, "quantize: features must be a multiple of 64");
+  LM_REQUIRE(rows >= 0, "quantize: negative row count");
+  LM_REQUIRE(sf_mode >= LM_SF_VARLEN && sf_mode <= LM_SF_LINEAR, "quantize: unknown sf_mode");
+  if (rows == 0) return LM_OK;
+  QuantParams p{};
+  p.x = x;
+  p.rows = rows;
+  p.features = features;
+  p.m_indptr = m_indptr;
+  p.experts = experts;
+  p.rows_per_group = rows_per_group;
+  p.scale_pair = scale_pair;
+  p.gather = gather_idx;
+  p.q = q;
+  p.sf = sf;
+  p.sf_mode = sf_mode;
+  p.te_math = te_math;
+  int64_t atom_rows;
+  if (sf_mode == LM_SF_VARLEN) {
+    LM_REQUIRE(m_indptr != nullptr && experts > 0, "quantize: varlen layout needs m_indptr");
+    atom_rows = (rows + 127) / 128 + experts;
+  } else if (sf_mode == LM_SF_BATCHED) {
+    LM_REQUIRE(rows_per_group > 0 && rows % rows_per_group == 0,
+               "quantize: rows must be a multiple of rows_per_group");
+    p.tiles_per_group = static_cast<int>((rows_per_group + 127) / 128);
+    atom_rows = (rows / rows_per_group) * p.tiles_per_group;
+  } else {
+    atom_rows = (rows + 127) / 128;
+  }
+  LM_REQUIRE(atom_rows < (1ll << 31), "quantize: too many rows");
+  dim3 grid(static_cast<unsigned>(atom_rows), (features + kTileCols - 1) / kTileCols);
+  if (x_dtype == LM_DTYPE_BF16) {
+    quantize_rowwise_kernel<__nv_bfloat16><<<grid, kThreads, 0, as_stream(stream)>>>(p);
+  } else {
+    quantize_rowwise_kernel<float><<<grid, kThreads, 0, as_stream(stream)>>>(p);
+  }
+  LM_CUDA(cudaGetLastError());
+  return LM_OK;
+}
+
+extern "C" int lm_quantize_decode(const void* x, int64_t tokens, int features, int top_k,
+                                  const int32_t* slots, const int32_t* topk_ids,
+                                  const int32_t* m_indptr, int experts, const float* scale_pair,
+                                  uint8_t* q, uint8_t* sf, lm_stream_t stream) {
+  using namespace lm;
+  (void)experts;
+  LM_REQUIRE(x && slots && topk_ids && m_indptr && scale_pair && q && sf, "quantize_decode: null pointer");
+  LM_REQUIRE(features > 0 && features % 64 == 0, "quantize_decode: features must be a multiple of 64");
+  LM_REQUIRE(top_k > 0 && tokens >= 0, "quantize_decode: bad sizes");
+  if (tokens == 0) return LM_OK;
+  DecodeQuantParams p{static_cast<const __nv_bfloat16*>(x), tokens, features, top_k, slots,
+                      topk_ids, m_indptr, scale_pair, q, sf};
+  dim3 grid(static_cast<unsigned>((tokens + kWarps - 1) / kWarps), (features + kTileCols - 1) / kTileCols);
+  quantize_decode_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(p);
+  LM_CUDA(cudaGetLastError());
+  return LM_OK;
+}

@@ -1,0 +1,282 @@
+"""Host runtime of the grouped NVFP4 GEMM.
+
+Mirrors ``GroupedNvfp4Gemm`` of the reference
+(``lightmoe/kernels/grouped/runtime.py:178-624``): same constructor and
+``prepare`` / ``launch`` / ``run`` signatures, same validation rules and
+messages.  ``prepare`` encodes the TMA descriptors once through
+``lm_gemm_prepare``; ``launch`` is a single ``lm_gemm_launch`` call on the
+current stream and is safe inside CUDA Graph capture.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ... import _lib
+from ..gated import GatedBackwardEpilogue, GatedEpilogue, resolve_gemm_epilogue
+from ..unary import UnaryBackwardEpilogue, UnaryEpilogue
+
+DECODE_GRID_PERSISTENT = 0
+DECODE_GRID_DOUBLE = 1
+
+
+def _resolve_dynamic_schedule(use_dynamic_sched: bool | None, k: int) -> bool:
+    """Scheduling policy flag of the reference (``runtime.py:22-25``).
+
+    This kernel's static round-robin tile walk gives every CTA the same number
+    of equally sized tiles, so the flag selects nothing here; it is kept
+    because callers read it back.
+    """
+    if use_dynamic_sched is None:
+        return k > 2048
+    return bool(use_dynamic_sched)
+
+
+def _decode_grid_mode(gather_b: bool, k: int, n: int, rows: int, experts: int) -> int:
+    """Grid policy table of the reference (``runtime.py:28-35``)."""
+    if not gather_b or rows <= 1:
+        return DECODE_GRID_PERSISTENT
+    if k >= 4096 and n >= 4096 and rows <= (64 if experts >= 48 else 16):
+        return DECODE_GRID_DOUBLE
+    if k >= 3072 and n == 3072 and rows <= 32:
+        return DECODE_GRID_DOUBLE
+    return DECODE_GRID_PERSISTENT
+
+
+def _out_kind(dtype: torch.dtype) -> int:
+    if dtype == torch.bfloat16:
+        return _lib.OUT_BF16
+    if dtype == torch.float32:
+        return _lib.OUT_F32
+    return _lib.OUT_NVFP4
+
+
+class GroupedNvfp4Gemm:
+    """Grouped NVFP4 GEMM for contiguous expert-major assignments."""
+
+    def __init__(
+        self,
+        experts: int,
+        n: int,
+        k: int,
+        tile_m: int,
+        tile_n: int,
+        output_dtype: torch.dtype = torch.bfloat16,
+        activation: str | None = None,
+        dactivation: str | None = None,
+        epilogue=None,
+        use_dynamic_sched: bool | None = None,
+        use_pdl: bool = False,
+        swap_ab: bool = False,
+        fast_decode_sched: bool = False,
+        direct_routes: int = 0,
+        broadcast_a: bool = False,
+        gather_b: bool = False,
+    ):
+        activation, dactivation = resolve_gemm_epilogue(epilogue, activation, dactivation)
+        save_preact = isinstance(epilogue, (GatedEpilogue, UnaryEpilogue)) and epilogue.save_preact
+        gated_policy = isinstance(epilogue, (GatedEpilogue, GatedBackwardEpilogue))
+        self.gated_clamp_limit = (
+            float(epilogue.clamp_limit) if gated_policy and epilogue.clamp_limit is not None else 0.0
+        )
+        self.activation_sigmoid_alpha = epilogue.sigmoid_alpha if gated_policy else 1.0
+        self.activation_up_bias = epilogue.up_bias if gated_policy else 0.0
+        if epilogue is None and activation is not None:
+            epilogue = UnaryEpilogue(activation) if activation == "relu2" else GatedEpilogue(activation)
+            if isinstance(epilogue, GatedEpilogue):
+                self.gated_clamp_limit = float(epilogue.clamp_limit or 0.0)
+                self.activation_sigmoid_alpha = epilogue.sigmoid_alpha
+                self.activation_up_bias = epilogue.up_bias
+        if experts <= 0 or n <= 0 or k <= 0:
+            raise ValueError("experts, N, and K must be positive")
+        if experts > 256:
+            raise ValueError("grouped GEMM supports at most 256 local experts")
+        if k % 64:
+            raise ValueError("grouped GEMM requires K aligned to 64")
+        if tile_m not in (128, 256) or tile_n < 8 or tile_n > 256 or tile_n % 8:
+            raise ValueError("grouped GEMM supports M=128/256 and N=8..256 aligned to 8")
+        if output_dtype not in (torch.bfloat16, torch.float32, torch.int32, torch.float4_e2m1fn_x2):
+            raise ValueError("grouped GEMM output must be BF16, FP32, Int32, or NVFP4")
+        activations = (None, "swiglu", "swiglu_oai", "geglu", "reglu", "relu2")
+        if activation not in activations:
+            raise ValueError("unsupported grouped GEMM activation")
+        if dactivation not in activations:
+            raise ValueError("unsupported grouped GEMM derivative")
+        if activation is not None and dactivation is not None:
+            raise ValueError("activation and dactivation are mutually exclusive")
+        if dactivation is not None or save_preact or output_dtype == torch.int32:
+            raise NotImplementedError("backward epilogues belong to the training path")
+        if output_dtype == torch.float4_e2m1fn_x2 and activation is None:
+            raise ValueError("NVFP4 output requires an activation epilogue")
+        if output_dtype == torch.float4_e2m1fn_x2 and n % 128:
+            raise ValueError("gated NVFP4 output requires N aligned to 128")
+        if activation is not None and output_dtype != torch.float4_e2m1fn_x2:
+            raise NotImplementedError("activation epilogues write NVFP4 in the inference path")
+        gated = activation is not None and activation != "relu2"
+        gated_tile = tile_m if swap_ab else tile_n
+        if gated and (n % 2 or gated_tile % 128):
+            axis = "tile_M" if swap_ab else "tile_N"
+            raise ValueError(f"gated GEMM requires even N and {axis} aligned to 128")
+        if swap_ab and activation is not None and tile_n > 64:
+            raise ValueError("operand-swapped activation GEMM requires tile_N at most 64")
+        self.experts = experts
+        self.n = n
+        self.k = k
+        self.tile_m = tile_m
+        self.tile_n = tile_n
+        self.output_dtype = output_dtype
+        self.activation = activation
+        self.dactivation = dactivation
+        self.save_preact = save_preact
+        self.epilogue = epilogue
+        self.use_dynamic_sched = _resolve_dynamic_schedule(use_dynamic_sched, k)
+        self.use_pdl = bool(use_pdl)
+        self.swap_ab = bool(swap_ab)
+        self.fast_decode_sched = bool(fast_decode_sched)
+        self.direct_routes = int(direct_routes)
+        self.broadcast_a = bool(broadcast_a)
+        self.gather_b = bool(gather_b)
+        self._direct_c_store = False
+        if self.fast_decode_sched and self.use_dynamic_sched:
+            raise ValueError("fast decode scheduling requires a static GEMM")
+        if self.direct_routes < 0 or self.direct_routes > 32:
+            raise ValueError("direct route count must be between 0 and 32")
+        if self.direct_routes:
+            raise NotImplementedError("direct routing is not part of the inference plan")
+        if self.broadcast_a:
+            raise ValueError("broadcast A requires direct routing")
+        if self.gather_b and not (self.swap_ab and self.fast_decode_sched):
+            raise ValueError("gather B requires swapped fast decode")
+        if self.gather_b:
+            raise NotImplementedError("token-major gather is not part of this build's decode path")
+        self.output_n = n
+        if gated:
+            self.output_n = n // 2
+        self.device = torch.cuda.current_device()
+        self.stages = 6
+        self._plan = None
+
+    def prepare(
+        self,
+        a,
+        b,
+        out,
+        cu,
+        sfa,
+        sfb,
+        alpha,
+        output_sf=None,
+        output_scale=None,
+        preact=None,
+        aux=None,
+        decode_plan=None,
+        gather_idx=None,
+    ):
+        tensors = {"A": a, "B": b, "output": out, "cu": cu, "SFA": sfa, "SFB": sfb, "alpha": alpha}
+        for name, tensor in tensors.items():
+            if not tensor.is_cuda or tensor.device.index != self.device:
+                raise ValueError(f"{name} must be on CUDA device {self.device}")
+            if not tensor.is_contiguous():
+                raise ValueError(f"{name} must be contiguous")
+        if a.dtype != torch.float4_e2m1fn_x2 or a.ndim != 2 or a.shape[1] * 2 != self.k:
+            raise ValueError(f"A must have packed shape (M, {self.k // 2})")
+        if b.dtype != torch.float4_e2m1fn_x2 or tuple(b.shape) != (self.experts, self.n, self.k // 2):
+            raise ValueError("B does not match the compiled expert geometry")
+        rows = a.shape[0]
+        nvfp4_out = self.output_dtype == torch.float4_e2m1fn_x2
+        output_cols = self.output_n // 2 if nvfp4_out else self.output_n
+        if tuple(out.shape) != (rows, output_cols) or out.dtype != self.output_dtype:
+            raise ValueError(
+                f"output must use {self.output_dtype} with shape ({rows}, {output_cols})"
+            )
+        if cu.dtype != torch.int32 or tuple(cu.shape) != (self.experts + 1,):
+            raise ValueError(
+                f"routing metadata must be contiguous int32 with shape {(self.experts + 1,)}"
+            )
+        expected_sfa = (1, -(-rows // 128) + self.experts, self.k // 64, 32, 4, 4)
+        expected_sfb = (self.experts, -(-self.n // 128), self.k // 64, 32, 4, 4)
+        if sfa.dtype != torch.float8_e4m3fn or tuple(sfa.shape) != expected_sfa:
+            raise ValueError(f"SFA must have shape {expected_sfa}")
+        if sfb.dtype != torch.float8_e4m3fn or tuple(sfb.shape) != expected_sfb:
+            raise ValueError(f"SFB must have shape {expected_sfb}")
+        if alpha.dtype != torch.float32 or tuple(alpha.shape) not in ((1,), (self.experts,)):
+            raise ValueError(
+                f"alpha must be contiguous float32 with shape (1,) or ({self.experts},)"
+            )
+        if nvfp4_out:
+            expected_output_sf = (1, -(-rows // 128) + self.experts, self.output_n // 64, 32, 4, 4)
+            if (
+                output_sf is None
+                or not output_sf.is_cuda
+                or output_sf.dtype != torch.float8_e4m3fn
+                or tuple(output_sf.shape) != expected_output_sf
+                or not output_sf.is_contiguous()
+                or output_sf.device.index != self.device
+            ):
+                raise ValueError(f"output_sf must have shape {expected_output_sf}")
+            if (
+                output_scale is None
+                or not output_scale.is_cuda
+                or output_scale.dtype != torch.float32
+                or tuple(output_scale.shape) != (2,)
+                or not output_scale.is_contiguous()
+                or output_scale.device.index != self.device
+            ):
+                raise ValueError("output_scale must be contiguous float32 [pts, inv_pts]")
+        args = _lib.GemmArgs()
+        args.experts = self.experts
+        args.n = self.n
+        args.k = self.k
+        args.tile_m = self.tile_m
+        args.tile_n = self.tile_n
+        args.out_kind = _out_kind(self.output_dtype)
+        args.activation = _lib.ACTIVATIONS[self.activation]
+        args.clamp_limit = self.gated_clamp_limit
+        args.sigmoid_alpha = self.activation_sigmoid_alpha
+        args.up_bias = self.activation_up_bias
+        args.alpha_per_expert = int(alpha.shape[0] == self.experts and self.experts > 1)
+        args.dense = 0
+        args.sf_tile_rows = 128
+        args.max_ctas = 0
+        args.rows = rows
+        args.a = a.data_ptr()
+        args.b = b.data_ptr()
+        args.out = out.data_ptr()
+        args.m_indptr = cu.data_ptr()
+        args.sfa = sfa.data_ptr()
+        args.sfb = sfb.data_ptr()
+        args.alpha = alpha.data_ptr()
+        args.out_sf = output_sf.data_ptr() if nvfp4_out else None
+        args.out_scale = output_scale.data_ptr() if nvfp4_out else None
+        plan = _lib.GemmPlan()
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().lm_gemm_prepare(ctypes.byref(args), ctypes.byref(plan)))
+        self._plan = plan
+        # keep operands alive for as long as the plan may launch
+        self._keepalive = (a, b, out, cu, sfa, sfb, alpha, output_sf, output_scale)
+
+    def launch(self):
+        if self._plan is None:
+            raise RuntimeError("prepare must run before launch")
+        _lib.check(_lib.lib().lm_gemm_launch(ctypes.byref(self._plan), _lib.stream_handle()))
+
+    def __call__(self, a, b, out, cu, sfa, sfb, alpha, output_sf=None, output_scale=None,
+                 preact=None, aux=None, decode_plan=None, gather_idx=None):
+        self.prepare(a, b, out, cu, sfa, sfb, alpha, output_sf, output_scale, preact, aux,
+                     decode_plan, gather_idx)
+        self.launch()
+
+    run = __call__
+
+
+def grouped_nvfp4_gemm(experts, n, k, tile_m, tile_n, output_dtype=torch.bfloat16, activation=None,
+                       dactivation=None, epilogue=None, use_dynamic_sched=None, use_pdl=False,
+                       swap_ab=False, fast_decode_sched=False, direct_routes=0, broadcast_a=False):
+    return GroupedNvfp4Gemm(experts, n, k, tile_m, tile_n, output_dtype, activation, dactivation,
+                            epilogue, use_dynamic_sched, use_pdl, swap_ab, fast_decode_sched,
+                            direct_routes, broadcast_a)
+
+
+__all__ = ["GroupedNvfp4Gemm", "grouped_nvfp4_gemm"]
