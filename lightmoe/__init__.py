@@ -13,6 +13,8 @@ import sys
 import nvfp4moe_b200 as _impl
 
 for _info in pkgutil.walk_packages(_impl.__path__, _impl.__name__ + "."):
+    if _info.name.rsplit(".", 1)[-1].startswith("lib"):
+        continue  # the CUDA shared library sits in the package folder; it is not a Python module
     _module = importlib.import_module(_info.name)
     sys.modules[__name__ + _info.name[len(_impl.__name__):]] = _module
 
