@@ -1,0 +1,359 @@
+"""Benchmark of the complete NVFP4 MoE layer (prefill) on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Workload (``config.workload`` = "c2_moe_layer_prefill"): hidden 2048,
+intermediate 512, 256 experts, top-8, SwiGLU, 8192 tokens per GPU with BF16
+activations drawn N(0,1), router logits drawn N(0,1) -> softmax -> top-k ->
+renormalise, NVFP4 weights drawn N(0,0.02).  One step = dispatch, quantize,
+fc1 (+activation +requantization), fc2, weighted combine of one batch.  With
+N > 1 the 256 experts are sharded expert-parallel and every GPU brings its own
+8192 tokens (weak scaling), with NCCL all-to-all dispatch and combine.
+
+Prints one JSON line: tokens/s over all GPUs (``value``: inputs resident in
+HBM; ``e2e``: host buffers, copies timed), the roofline of the dominant kernel
+and a CPU baseline (the CPU oracle on a bounded sample).  ``--impl reference``
+times that CPU oracle alone.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HIDDEN, INTER, EXPERTS, TOPK, TOKENS = 2048, 512, 256, 8, 8192
+WORKLOAD = "c2_moe_layer_prefill"
+
+
+def _peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return float(data["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def _routing(tokens, experts, k, seed, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(tokens, experts, generator=g)
+    topv, topi = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+    topv = (topv / topv.sum(-1, keepdim=True)).float().contiguous()
+    return topi.to(torch.int32).contiguous().to(device), topv.to(device)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                     "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+                if out.returncode == 0 and out.stdout.strip():
+                    self.samples.append([f.strip() for f in out.stdout.strip().split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=10)
+
+    def summary(self):
+        clocks = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        maxes = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = sorted({n for s in self.samples for n, v in zip(names, s[2:6]) if v == "Active"})
+        return {"sm_mhz": statistics.median(clocks) if clocks else None,
+                "sm_max_mhz": max(maxes) if maxes else None, "reasons": reasons,
+                "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------ CPU arm
+def _cpu_sample(threads: int):
+    """The CPU oracle on 1/16 of the experts with all their rows (same per-expert shape)."""
+    from oracle import nvfp4_oracle as O
+
+    torch.set_num_threads(threads)
+    experts, tokens = EXPERTS // 16, TOKENS // 16
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(tokens, HIDDEN, generator=g).to(torch.bfloat16)
+    ids, w = _routing(tokens, experts, TOPK, 0)
+    gate_up = (torch.randn(experts, 2 * INTER, HIDDEN, generator=g) * 0.02).to(torch.bfloat16)
+    down = (torch.randn(experts, HIDDEN, INTER, generator=g) * 0.02).to(torch.bfloat16)
+    w1 = O.pack_weights(gate_up)
+    w2 = O.pack_weights(down)
+    xs, hs = O.calibrate(x, ids, w, *w1)
+
+    def step():
+        return O.moe_layer(x, ids, w, *w1, *w2, xs, hs)
+
+    sample = (f"{tokens} tokens over {experts} of {EXPERTS} experts (top-{TOPK}, "
+              f"{tokens * TOPK // experts} rows per expert as in the full workload)")
+    return step, tokens, sample
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    step, tokens, sample = _cpu_sample(threads)
+    for _ in range(max(args.warmup, 1)):
+        step()
+    times = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    total = sum(times)
+    value = tokens * args.steps / total
+    line = {
+        "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e4m3) with f32 accumulate", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "hidden": HIDDEN, "intermediate": INTER, "experts": EXPERTS,
+                   "top_k": TOPK, "tokens_per_gpu": TOKENS, "activation": "swiglu"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ GPU arm
+def _event_ms(fn, iters, stream=None):
+    start = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    stop = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    for i in range(iters):
+        start[i].record()
+        fn()
+        stop[i].record()
+    torch.cuda.synchronize()
+    return [s.elapsed_time(e) for s, e in zip(start, stop)]
+
+
+def _stage_times(plan, x, ids, w, iters=20):
+    """Average device time of each kernel of one step (outside the timed region)."""
+    from nvfp4moe_b200.kernels.quantize.runtime import nvfp4_quantize_rowwise
+    from nvfp4moe_b200.kernels.routing.combine import moe_finalize
+
+    tokens = x.shape[0]
+    rows = tokens * plan.topk
+    ex = plan._full_execution(tokens, decode=False)
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=x.device)
+    stages = {
+        "dispatch": lambda: plan._dispatch(ids, w, rows),
+        "quantize": lambda: nvfp4_quantize_rowwise(x, plan._m_indptr, plan._x_scale, ex.qx, ex.sfx,
+                                                   gather_idx=plan._gather[:rows], te_math=True),
+        "fc1": ex.fc1.launch,
+        "fc2": ex.fc2.launch,
+        "combine": lambda: moe_finalize(ex.routed_out, plan._slots[:rows], plan._out[:tokens],
+                                        plan.topk, weights=plan._probs[:rows]),
+    }
+    out = {}
+    for name, fn in stages.items():
+        samples = []
+        for _ in range(iters):
+            flush.zero_()  # evict L2 between samples
+            samples += _event_ms(fn, 1)
+        out[name] = statistics.median(samples)
+    plan.run_prefill(x, ids, w)  # leave the workspace consistent
+    return out
+
+
+def _algorithmic_bytes(rows, tokens, e_local):
+    q = 0.5625  # packed FP4 + one scale byte per 16 values
+    return {
+        "dispatch": rows * 8 + rows * 12 + (2 * e_local + 1) * 4,
+        "quantize": tokens * HIDDEN * 2 + rows * HIDDEN * q,
+        "fc1": rows * HIDDEN * q + e_local * 2 * INTER * HIDDEN * q + rows * INTER * q,
+        "fc2": rows * INTER * q + e_local * HIDDEN * INTER * q + rows * HIDDEN * 2,
+        "combine": rows * HIDDEN * 2 + rows * 8 + tokens * HIDDEN * 2,
+    }
+
+
+def run_ours(args):
+    import torch.distributed as dist
+
+    from nvfp4moe_b200 import InferenceMoE, _lib
+    from nvfp4moe_b200.expert_parallel import ExpertParallelMoE
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    e_local = EXPERTS // world
+
+    g = torch.Generator(device=device).manual_seed(1234 + rank)
+    gate = (torch.randn(e_local, INTER, HIDDEN, generator=g, device=device) * 0.02).to(torch.bfloat16)
+    up = (torch.randn(e_local, INTER, HIDDEN, generator=g, device=device) * 0.02).to(torch.bfloat16)
+    down = (torch.randn(e_local, HIDDEN, INTER, generator=g, device=device) * 0.02).to(torch.bfloat16)
+    x_host = torch.randn(TOKENS, HIDDEN, generator=torch.Generator().manual_seed(rank)).to(torch.bfloat16).pin_memory()
+    ids_host, w_host = _routing(TOKENS, EXPERTS, TOPK, rank)
+    ids_host, w_host = ids_host.pin_memory(), w_host.pin_memory()
+    x, ids, w = x_host.to(device), ids_host.to(device), w_host.to(device)
+
+    if world == 1:
+        layer = InferenceMoE(HIDDEN, INTER, EXPERTS, TOPK, TOKENS, device=device)
+        layer.load_weights(gate, up, down)
+        layer.calibrate(x, ids, w)
+        step = lambda: layer.run_prefill(x, ids, w)
+        launches_per_step = 6  # dispatch count + scatter, quantize, fc1, fc2, combine
+    else:
+        layer = ExpertParallelMoE(HIDDEN, INTER, EXPERTS, TOPK, TOKENS, group=None, device=device,
+                                  max_recv_rows=4 * TOKENS * TOPK)
+        layer.load_weights(gate, up, down)
+        # activations are N(0,1) and weights N(0,0.02) on every rank: fixed scales from rank-local data
+        probe = InferenceMoE(HIDDEN, INTER, e_local, TOPK, 1024, device=device)
+        probe.load_weights(gate, up, down)
+        pid, pw = _routing(1024, e_local, TOPK, 7, device)
+        probe.calibrate(x[:1024], pid, pw)
+        scales = torch.stack((probe._x_scale[0], probe._h_scale[0]))
+        dist.all_reduce(scales, op=dist.ReduceOp.MAX)
+        layer.set_activation_scales(scales[0:1], scales[1:2])
+        del probe
+        step = lambda: layer.run(x, ids, w)
+        launches_per_step = 8  # 2x2 dispatch kernels, quantize, fc1, fc2, combine
+    del gate, up, down
+    torch.cuda.empty_cache()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    # ---- timed region: device-resident inputs; the working set (weights + workspace,
+    # > 700 MB per step) is far larger than the 126 MB L2, so no explicit flush is needed
+    with ClockSampler(local_rank) as sampler:
+        barrier()
+        times = _event_ms(step, args.steps)
+        barrier()
+    total_ms = torch.tensor([sum(times)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    total_ms = float(total_ms)
+    value = TOKENS * world * args.steps / (total_ms / 1e3)
+
+    # ---- end to end through the public call with host buffers
+    out_host = torch.empty(TOKENS, HIDDEN, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        ids.copy_(ids_host, non_blocking=True)
+        w.copy_(w_host, non_blocking=True)
+        out_host.copy_(step(), non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e2e_ms = torch.tensor([sum(_event_ms(e2e_step, args.steps))], dtype=torch.float64, device=device)
+    barrier()
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_value = TOKENS * world * args.steps / (float(e2e_ms) / 1e3)
+    h2d = x_host.numel() * 2 + ids_host.numel() * 4 + w_host.numel() * 4
+    d2h = out_host.numel() * 2
+
+    status = _lib.device_status()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    line = {
+        "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "nvfp4 (e2m1 x e4m3) with f32 accumulate", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "hidden": HIDDEN, "intermediate": INTER, "experts": EXPERTS,
+                   "top_k": TOPK, "tokens_per_gpu": TOKENS, "activation": "swiglu",
+                   "parallelism": f"ep{world}", "l2": "working set per step exceeds L2; no flush"},
+        "clocks": sampler.summary(),
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches_per_step * args.steps,
+        "device_status": status,
+    }
+    if world == 1:
+        stage_ms = _stage_times(layer, x, ids, w)
+        algo = _algorithmic_bytes(TOKENS * TOPK, TOKENS, EXPERTS)
+        top = max(stage_ms, key=stage_ms.get)
+        peak, kind = _peaks()
+        achieved = algo[top] / (stage_ms[top] * 1e-3) / 1e9
+        line["roofline"] = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peak,
+                            "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                            "peak_source": kind}
+        line["stages_ms"] = stage_ms
+        line["stages_gbs"] = {k: algo[k] / (v * 1e-3) / 1e9 for k, v in stage_ms.items()}
+        flops = 2.0 * TOKENS * TOPK * HIDDEN * INTER * 3
+        line["gemm_tflops"] = {"fc1": 2.0 * TOKENS * TOPK * 2 * INTER * HIDDEN / (stage_ms["fc1"] * 1e-3) / 1e12,
+                               "fc2": 2.0 * TOKENS * TOPK * HIDDEN * INTER / (stage_ms["fc2"] * 1e-3) / 1e12,
+                               "layer_flop": flops}
+        if not args.no_cpu:
+            threads = os.cpu_count() or 1
+            cpu_step, cpu_tokens, sample = _cpu_sample(threads)
+            cpu_step()
+            t0 = time.perf_counter()
+            reps = 2
+            for _ in range(reps):
+                cpu_step()
+            cpu_s = (time.perf_counter() - t0) / reps
+            line["cpu_baseline"] = {"value": cpu_tokens / cpu_s, "unit": "tokens/s", "cores": threads,
+                                    "kind": "port", "sample": sample}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

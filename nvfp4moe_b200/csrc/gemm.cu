@@ -32,7 +32,7 @@ constexpr int kChunksPerStage = 4; // 64-element MMAs (= scale-factor atoms) per
 constexpr int kThreads = 192;
 constexpr int kMaxExperts = 256;
 constexpr uint32_t kTmemCols = 512;
-constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s
+constexpr long long kWaitLimitCycles = 2000000000ll;  // about one second
 
 __device__ uint32_t g_status = 0;
 

@@ -1,0 +1,97 @@
+"""Host-side logic of the expert-parallel exchange on two gloo ranks (CPU)."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from nvfp4moe_b200.expert_parallel import (ExpertParallelExchange, owner_splits,
+                                           received_expert_ids, reference_step)
+
+EXPERTS, TOPK, HIDDEN, TOKENS = 8, 2, 16, 24
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _inputs(rank: int):
+    g = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(TOKENS, HIDDEN, generator=g).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(EXPERTS, generator=g)[:TOPK] for _ in range(TOKENS)]).int()
+    if rank == 1:
+        ids[ids == 6] = 7  # expert 6 gets nothing from rank 1
+    w = torch.rand(TOKENS, TOPK, generator=g)
+    return x, ids, w
+
+
+def _expert_fn(rows: torch.Tensor, global_expert: torch.Tensor) -> torch.Tensor:
+    """Stand-in for the expert GEMMs: depends on the row and on which expert ran it."""
+    return (rows.float() * (global_expert.float().unsqueeze(1) + 1.0)).to(torch.bfloat16)
+
+
+def _expected(x, ids, w):
+    out = torch.zeros(TOKENS, HIDDEN)
+    for t in range(TOKENS):
+        for j in range(TOPK):
+            e = ids[t, j].reshape(1)
+            out[t] += _expert_fn(x[t : t + 1], e)[0].float() * w[t, j]
+    return out
+
+
+def _worker(rank: int, world: int, port: int, fail_rank: int, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        exchange = ExpertParallelExchange(EXPERTS)
+        assert exchange.local_experts == EXPERTS // world
+        x, ids, w = _inputs(rank)
+        first_local = rank * exchange.local_experts
+
+        def compute(rows, local_ids):
+            return _expert_fn(rows, local_ids + first_local)
+
+        out = reference_step(x, ids, w, compute, exchange)
+        expected = _expected(x, ids, w)
+        results[rank] = bool(torch.allclose(out, expected, rtol=1e-5, atol=1e-5))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_exchange_matches_single_process():
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker, args=(world, _free_port(), -1, results), nprocs=world, join=True)
+    assert dict(results) == {0: True, 1: True}
+
+
+def test_split_helpers():
+    m_indptr = torch.tensor([0, 3, 3, 7, 8, 8, 10, 15, 16], dtype=torch.int32)
+    assert owner_splits(m_indptr, 2).tolist() == [8, 8]
+    assert owner_splits(m_indptr, 4).tolist() == [3, 5, 2, 6]
+    assert owner_splits(m_indptr, 1).tolist() == [16]
+    counts = torch.tensor([[2, 0, 1], [0, 3, 0]], dtype=torch.int32)
+    assert received_expert_ids(counts).tolist() == [0, 0, 2, 1, 1, 1]
+
+
+def test_single_rank_exchange_is_the_identity():
+    exchange = ExpertParallelExchange(EXPERTS)
+    assert exchange.world == 1
+    x, ids, w = _inputs(0)
+    out = reference_step(x, ids, w, lambda rows, e: _expert_fn(rows, e), exchange)
+    assert torch.allclose(out, _expected(x, ids, w), rtol=1e-5, atol=1e-5)
+
+
+def test_expert_count_must_divide_over_ranks(monkeypatch):
+    monkeypatch.setattr(dist, "is_initialized", lambda: True)
+    monkeypatch.setattr(dist, "get_world_size", lambda group=None: 3)
+    monkeypatch.setattr(dist, "get_rank", lambda group=None: 0)
+    with pytest.raises(ValueError, match="divisible"):
+        ExpertParallelExchange(EXPERTS)

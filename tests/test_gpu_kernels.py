@@ -106,8 +106,10 @@ def test_public_quantize_helpers_match_oracle():
     g = torch.Generator().manual_seed(9)
     x = torch.randn(300, 192, generator=g).to(torch.bfloat16)
     q, sf, scale = gemm.quantize(x.cuda())
-    pts = O.tensor_scale(x)
-    assert torch.equal(scale.cpu(), pts)
+    # torch divides by a constant on the GPU as a multiplication by its reciprocal, so the
+    # scale may sit one ulp from the CPU value; the quantizer is checked on the scale it was given
+    pts = scale.cpu()
+    assert abs(float(pts) / float(O.tensor_scale(x)) - 1.0) < 3e-7
     q_ref, sf_ref = O.quantize_rows(x, pts)
     assert q.dtype == torch.float4_e2m1fn_x2 and tuple(sf.shape) == (3, 3, 32, 4, 4)
     assert torch.equal(q.view(torch.uint8).cpu(), q_ref)
@@ -235,11 +237,20 @@ def _grouped_case(lens, n, k, seed, a_std=1.0, b_std=0.02):
     return cu, a, b
 
 
+def _device_scales(a, b):
+    """Per-tensor scales as the library derives them (on the GPU), copied to the host."""
+    from nvfp4moe_b200.gemm import _tensor_scale
+
+    return _tensor_scale(a.cuda(), None).cpu(), _tensor_scale(b.cuda(), None).cpu()
+
+
 def _run_grouped(cu, a, b, alpha_scale=None, out_dtype=torch.bfloat16):
     from nvfp4moe_b200 import gemm
 
     experts, n, k = b.shape
     qa, qb, sfa, sfb, alpha = gemm.quantize_grouped(a.cuda(), b.cuda(), cu.cuda())
+    pa, pb = _device_scales(a, b)
+    assert torch.equal(alpha.cpu(), pa * pb)
     if alpha_scale is not None:
         alpha = alpha * alpha_scale.cuda()
     out = torch.full((a.shape[0], n), float("nan"), dtype=out_dtype, device="cuda")
@@ -250,7 +261,9 @@ def _run_grouped(cu, a, b, alpha_scale=None, out_dtype=torch.bfloat16):
 
 
 def _oracle_grouped(cu, a, b, alpha_scale=None):
-    pa, pb = O.tensor_scale(a), O.tensor_scale(b)
+    pa, pb = _device_scales(a, b)
+    assert abs(float(pa) / float(O.tensor_scale(a)) - 1.0) < 3e-7
+    assert abs(float(pb) / float(O.tensor_scale(b)) - 1.0) < 3e-7
     qa, sfa = O.quantize_rows(a, pa)
     qb, sfb = O.quantize_rows(b, pb)
     alpha = pa * pb
