@@ -138,6 +138,35 @@ int lm_dispatch(const int32_t* topk_ids, const float* topk_weights, int64_t toke
                 int plan_tile_rows, lm_stream_t stream);
 
 /*
+ * lm_dispatch for callers that have no device memory to give as scratch and
+ * may not obtain any: a plugin inside a serving process whose memory pool
+ * already owns the whole GPU, or a host runtime that forbids its extensions to
+ * call the CUDA allocator.  This entry point has no counterpart in the
+ * reference.  It computes exactly what lm_dispatch computes, but keeps the
+ * per-chunk counts in a fixed array inside the library (128 KB of device
+ * memory per GPU, held until the process exits) and calls no allocating
+ * routine.
+ *
+ *   Limit: tokens * top_k <= lm_dispatch_static_max_rows() (131072) and
+ *   experts <= 256; larger inputs return LM_ERR_LIMIT and launch nothing.
+ *   plan_out / plan_elems: optional buffer for the decode plan that the
+ *   single-block path (rows <= 1024) writes, laid out as lm_dispatch lays it
+ *   out in its scratch; NULL to drop the plan.
+ *
+ * The first call on each device looks up the array's device address (with
+ * that device current); make that first call before any stream capture
+ * begins.  All calls on a device share the one array and nothing in it needs
+ * to start at zero -- each call overwrites every entry it later reads -- but
+ * two calls that overlap on the GPU (different streams) race on it: keep calls
+ * on one device in stream order.
+ */
+int64_t lm_dispatch_static_max_rows(void);
+int lm_dispatch_static(const int32_t* topk_ids, const float* topk_weights, int64_t tokens,
+                       int top_k, int experts, int32_t* gather, int32_t* m_indptr, float* probs,
+                       int32_t* slots, int32_t* padded_offsets, int32_t* plan_out,
+                       int64_t plan_elems, int plan_tile_rows, lm_stream_t stream);
+
+/*
  * Deterministic top-k combine: out[t] = bf16(sum_j f32(rows[slot]) * w[slot]),
  * j ascending, product rounded before the add, slot -1 skipped.
  * Replaces moe_finalize (lightmoe/kernels/routing/combine.py:231-281).

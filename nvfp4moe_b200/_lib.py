@@ -76,6 +76,11 @@ _SIGNATURES = {
         c_i32,
         [c_ptr, c_ptr, c_i64, c_i32, c_i32, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i32, c_ptr],
     ),
+    "lm_dispatch_static_max_rows": (c_i64, []),
+    "lm_dispatch_static": (
+        c_i32,
+        [c_ptr, c_ptr, c_i64, c_i32, c_i32, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i32, c_ptr],
+    ),
     "lm_finalize": (c_i32, [c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i32, c_i32, c_i64, c_i64, c_ptr]),
     "lm_gemm_prepare": (c_i32, [ctypes.POINTER(GemmArgs), ctypes.POINTER(GemmPlan)]),
     "lm_gemm_launch": (c_i32, [ctypes.POINTER(GemmPlan), c_ptr]),

@@ -163,6 +163,29 @@ __global__ void __launch_bounds__(kThreads) dispatch_scatter_kernel(DispatchPara
   }
 }
 
+// Scratch of the entry point that allocates nothing: room for the per-chunk
+// counts of 128 chunks x 256 experts (131072 assignments).  Every GPU that loads
+// the library holds these 128 KB until the process exits.
+constexpr int kStaticChunks = 128;
+constexpr int64_t kStaticElems = static_cast<int64_t>(kStaticChunks) * kMaxExperts;
+static __device__ __align__(256) int32_t g_static_scratch[kStaticElems];
+
+// In host code the array's name is only a handle; the device address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+int static_scratch_ptr(int32_t** out) {
+  static int32_t* cached[64] = {nullptr};
+  int device = 0;
+  LM_CUDA(cudaGetDevice(&device));
+  if (device < 0 || device >= 64) return set_error(LM_ERR_LIMIT, "dispatch_static: device index out of range");
+  if (cached[device] == nullptr) {
+    int32_t* ptr = nullptr;
+    LM_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch));
+    cached[device] = ptr;
+  }
+  *out = cached[device];
+  return LM_OK;
+}
+
 }  // namespace
 }  // namespace lm
 
@@ -195,6 +218,52 @@ extern "C" int lm_dispatch(const int32_t* topk_ids, const float* topk_weights, i
     dispatch_scatter_kernel<true><<<1, kThreads, smem, s>>>(p);
   } else {
     LM_REQUIRE(scratch_elems >= static_cast<int64_t>(chunks) * experts, "dispatch: scratch too small");
+    dispatch_count_kernel<<<chunks, kThreads, 0, s>>>(p);
+    LM_CUDA(cudaGetLastError());
+    dispatch_scatter_kernel<false><<<chunks, kThreads, smem, s>>>(p);
+  }
+  LM_CUDA(cudaGetLastError());
+  return LM_OK;
+}
+
+extern "C" int64_t lm_dispatch_static_max_rows(void) {
+  return static_cast<int64_t>(lm::kStaticChunks) * lm::kChunk;
+}
+
+extern "C" int lm_dispatch_static(const int32_t* topk_ids, const float* topk_weights, int64_t tokens,
+                                  int top_k, int experts, int32_t* gather, int32_t* m_indptr,
+                                  float* probs, int32_t* slots, int32_t* padded_offsets,
+                                  int32_t* plan_out, int64_t plan_elems, int plan_tile_rows,
+                                  lm_stream_t stream) {
+  using namespace lm;
+  LM_REQUIRE(topk_ids && topk_weights && gather && m_indptr && probs && slots && padded_offsets,
+             "dispatch_static: null pointer");
+  LM_REQUIRE(experts > 0 && experts <= kMaxExperts, "dispatch_static: at most 256 experts");
+  LM_REQUIRE(top_k > 0 && tokens > 0, "dispatch_static: empty routing");
+  LM_REQUIRE(plan_tile_rows > 0 && 128 % plan_tile_rows == 0,
+             "dispatch_static: plan_tile_rows must divide 128");
+  const int64_t rows = tokens * top_k;
+  if (rows > lm_dispatch_static_max_rows())
+    return set_error(LM_ERR_LIMIT, "dispatch_static: %lld assignments exceed the built-in scratch (%lld)",
+                     static_cast<long long>(rows), static_cast<long long>(lm_dispatch_static_max_rows()));
+  int32_t* scratch = nullptr;
+  int rc = static_scratch_ptr(&scratch);
+  if (rc != LM_OK) return rc;
+  const int chunks = static_cast<int>((rows + kChunk - 1) / kChunk);
+  DispatchParams p{topk_ids, topk_weights, rows,    top_k,         experts,      gather, m_indptr,
+                   probs,    slots,        padded_offsets, scratch, kStaticElems, plan_tile_rows, chunks};
+  const size_t smem = sizeof(int) * (static_cast<size_t>(kSegments) * experts + kChunk);
+  cudaStream_t s = as_stream(stream);
+  if (chunks == 1) {
+    // the single-block path writes the decode plan where the scratch pointer says
+    if (plan_out != nullptr) {
+      int64_t plan_need = 1 + (rows + plan_tile_rows - 1) / plan_tile_rows + experts + experts;
+      LM_REQUIRE(plan_elems >= plan_need, "dispatch_static: plan_out too small for the decode plan");
+      p.scratch = plan_out;
+      p.scratch_elems = plan_elems;
+    }
+    dispatch_scatter_kernel<true><<<1, kThreads, smem, s>>>(p);
+  } else {
     dispatch_count_kernel<<<chunks, kThreads, 0, s>>>(p);
     LM_CUDA(cudaGetLastError());
     dispatch_scatter_kernel<false><<<chunks, kThreads, smem, s>>>(p);
