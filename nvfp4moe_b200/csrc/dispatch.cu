@@ -119,6 +119,7 @@ __global__ void __launch_bounds__(kThreads) dispatch_scatter_kernel(DispatchPara
     if (kSingle) {
       total = in_chunk;
     } else {
+#pragma unroll 8
       for (int b = 0; b < p.chunks; ++b) {
         int c = __ldg(p.scratch + static_cast<int64_t>(b) * E + tid);
         total += c;

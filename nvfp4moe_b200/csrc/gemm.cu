@@ -2,15 +2,19 @@
 //
 //   out[rows_e, :] = alpha_e * (A_e . SFA_e) (B_e . SFB_e)^T      FP32 accumulate
 //
-// Warp-specialised CTA of 192 threads, one CTA per SM:
-//   warp 0      TMA producer: A and B tiles (128-byte swizzle) with
-//               cp.async.bulk.tensor, scale-factor atoms with cp.async.bulk
-//   warp 1      allocates TMEM, copies scale factors smem -> TMEM (tcgen05.cp)
-//               and issues tcgen05.mma kind::mxf4nvf4 block-scaled MMAs
-//   warps 2..5  epilogue: tcgen05.ld the accumulator, scale, (activate and
-//               requantize to NVFP4,) store; each warp owns one TMEM lane quarter
-// The accumulator is double-buffered in TMEM so the epilogue of tile i overlaps
-// the main loop of tile i+1.  Tiles are assigned round-robin; every role walks
+// Warp-specialised CTA of 512 threads, one CTA per SM:
+//   warp 0       TMA producer: A and B tiles (128-byte swizzle) with
+//                cp.async.bulk.tensor, scale-factor atoms with cp.async.bulk
+//   warp 1       allocates TMEM and issues tcgen05.mma kind::mxf4nvf4 block-scaled MMAs
+//   warps 4..7   move the scale factors of each stage from shared memory to TMEM with
+//                ld.shared + tcgen05.st (one warp per TMEM lane quarter).  tcgen05.cp
+//                would do the same from the MMA thread, but measured here it holds the
+//                tensor pipe for ~90 cycles per 512-byte atom, serialised with the MMAs
+//   warps 8..15  epilogue in two groups of four: tcgen05.ld the accumulator, scale,
+//                (activate and requantize to NVFP4,) store; each warp owns one TMEM
+//                lane quarter; group g drains accumulator stage g
+// The accumulator is double-buffered in TMEM, so the epilogues of tiles i and i+1
+// overlap each other and the main loop of tile i+2.  Tiles are assigned round-robin; every role walks
 // the same tile list, which it derives from m_indptr in shared memory.
 //
 // Rows of expert e are [m_indptr[e], m_indptr[e+1]).  A tile's A rows may run
@@ -19,6 +23,7 @@
 // runs out the CTA raises a bit in a status word and leaves the kernel.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -29,17 +34,38 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kStageKBytes = 128;  // 256 FP4 values per row and stage: one swizzle span
 constexpr int kChunksPerStage = 4; // 64-element MMAs (= scale-factor atoms) per stage
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;
+constexpr int kFirstSfWarp = 4;        // warps 4..7 write scale factors into TMEM
+constexpr int kFirstEpilogueWarp = 8;  // warps 8..15: two epilogue groups of four
+constexpr int kThreads = 32 * (kFirstEpilogueWarp + kEpilogueWarps);
 constexpr int kMaxExperts = 256;
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitLimitCycles = 2000000000ll;  // about one second
 
 __device__ uint32_t g_status = 0;
 
+#ifdef LM_GEMM_PROFILE
+// Cycle counters of CTA 0, written when the library is built with -DLM_GEMM_PROFILE:
+// [0] producer waits on empty, [1] MMA waits on full, [2] MMA waits on acc_empty,
+// [3] epilogue (warp 2) waits on acc_full, [4] epilogue (warp 2) busy, [5] kernel cycles,
+// [6] tiles of CTA 0, [7] MMA issue cycles
+__device__ unsigned long long g_prof[8];
+#define LM_PROF_DECL long long prof_t0 = clock64(), prof_acc0 = 0, prof_acc1 = 0, prof_acc2 = 0; (void)prof_t0; (void)prof_acc0; (void)prof_acc1; (void)prof_acc2
+#define LM_PROF_BEGIN() prof_t0 = clock64()
+#define LM_PROF_END(acc) acc += clock64() - prof_t0
+#define LM_PROF_STORE(idx, acc) if (blockIdx.x == 0) g_prof[idx] = static_cast<unsigned long long>(acc)
+#else
+#define LM_PROF_DECL
+#define LM_PROF_BEGIN()
+#define LM_PROF_END(acc)
+#define LM_PROF_STORE(idx, acc)
+#endif
+
 enum : uint32_t {
   kStatusProducerTimeout = 1u,
   kStatusMmaTimeout = 2u,
   kStatusEpilogueTimeout = 4u,
+  kStatusSfTimeout = 8u,
 };
 
 struct GemmParams {
@@ -63,6 +89,7 @@ struct GemmParams {
   float clamp_limit;
   float sigmoid_alpha;
   float up_bias;
+  int debug_flags;  // profiling builds only: 1 = skip scale-factor copies, 2 = skip MMAs
 };
 
 // ------------------------------------------------------------------ PTX glue
@@ -111,6 +138,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       return false;
     }
   }
+}
+
+// True in exactly one lane of a converged warp.  Issuing TMA and tcgen05 instructions under
+// this predicate (instead of `lane == 0`) lets the compiler keep their operands in uniform
+// registers: the surrounding control flow stays warp-uniform.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xFFFFFFFF;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
@@ -173,6 +213,18 @@ __device__ __forceinline__ void tc_load32(uint32_t taddr, uint32_t* r) {
       : "memory");
 }
 
+__device__ __forceinline__ void tc_store32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+      "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+      "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -214,24 +266,37 @@ struct SmemLayout {
   static constexpr int kSfbAtomRows = (kTileN + 127) / 128;
   static constexpr int kSfbBytes = kSfbAtomRows * kChunksPerStage * 512;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kStages = (kTileN <= 128) ? 6 : 4;
-  static constexpr int kAccStages = (kTileN <= 128) ? 2 : 1;
+  static constexpr int kStages = 5;
+  static constexpr int kAccStages = 2;
+  // BF16 output staging: every epilogue warp owns 32 rows of 64 columns (+16 B pad per row)
+  static constexpr int kStoreRowPitch = 64 * 2 + 16;
+  static constexpr int kStoreBytesPerWarp = 32 * kStoreRowPitch;
+  static constexpr int kStoreBytes = kEpilogueWarps * kStoreBytesPerWarp;
   static constexpr int kMiscBytes = 4096;
-  static constexpr int kTotal = kStages * kStageBytes + kMiscBytes + 1024;
+  static constexpr int kTotal = kStages * kStageBytes + kStoreBytes + kMiscBytes + 1024;
+  // TMEM columns: accumulators, then one scale-factor slot per shared-memory stage
+  // (A factors in the first 16 columns of a slot, B factors after them)
+  static constexpr uint32_t kSfCol = kAccStages * kTileN;
+  static constexpr uint32_t kSfaCols = kChunksPerStage * 4;
+  static constexpr uint32_t kSfSlotCols = kSfaCols * (1 + kSfbAtomRows);
+  static_assert(kSfSlotCols == 32, "the scale-factor writer stores 32 columns per stage");
+  static_assert(kSfCol + kStages * kSfSlotCols <= kTmemCols, "TMEM budget");
   static_assert(kStageBytes % 1024 == 0, "stages must keep 1024-byte alignment");
+  static_assert(kTotal <= 232448, "shared memory budget");
 };
 
-struct Misc {  // lives after the pipeline stages
+struct Misc {  // lives after the pipeline stages and the store staging
   uint64_t full[8];
   uint64_t empty[8];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t sf_full[8];
   uint32_t tmem_base;
   int abort_flag;
   int total_m_tiles;
   int pad;
   int cu[kMaxExperts + 1];
-  int prefix[kMaxExperts + 1];
+  int prefix[kMaxExperts + 2];
 };
 static_assert(sizeof(Misc) <= 4096, "misc block too large");
 
@@ -243,24 +308,25 @@ struct TileCoord {
   int n_tile;
 };
 
-__device__ __forceinline__ TileCoord decode_tile(const Misc* m, const GemmParams& p, int tile) {
-  const int mt = tile / p.n_tiles;
-  TileCoord t;
-  t.n_tile = tile - mt * p.n_tiles;
-  int lo = 0, hi = p.experts;
-  while (hi - lo > 1) {
-    int mid = (lo + hi) >> 1;
-    if (m->prefix[mid] <= mt) lo = mid; else hi = mid;
+// Maps the linear tile index (row tile major, column tile minor) to its expert.
+// A role visits tiles in increasing order, so the expert cursor only moves forward.
+struct TileWalker {
+  int expert = 0;
+  __device__ __forceinline__ TileCoord at(const Misc* m, const GemmParams& p, int tile) {
+    const int mt = tile / p.n_tiles;
+    while (expert + 1 < p.experts && m->prefix[expert + 1] <= mt) ++expert;
+    const int local = mt - m->prefix[expert];
+    const int begin = m->cu[expert];
+    const int count = m->cu[expert + 1] - begin;
+    TileCoord t;
+    t.n_tile = tile - mt * p.n_tiles;
+    t.expert = expert;
+    t.row0 = begin + local * kTileM;
+    t.valid = min(kTileM, count - local * kTileM);
+    t.sf_row = begin / kTileM + expert + local;
+    return t;
   }
-  const int local = mt - m->prefix[lo];
-  const int begin = m->cu[lo];
-  const int count = m->cu[lo + 1] - begin;
-  t.expert = lo;
-  t.row0 = begin + local * kTileM;
-  t.valid = min(kTileM, count - local * kTileM);
-  t.sf_row = begin / kTileM + lo + local;
-  return t;
-}
+};
 
 // ------------------------------------------------------------- activations
 template <int kAct>
@@ -302,6 +368,11 @@ __device__ __forceinline__ uint32_t requant16(const float* h, float inv_pts, uin
   return sf;
 }
 
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&b);
+}
+
 // ------------------------------------------------------------------ kernel
 template <int kTileN, int kOut, int kAct>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -311,7 +382,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  Misc* misc = reinterpret_cast<Misc*>(smem_gen + L::kStages * L::kStageBytes);
+  const uint32_t store_base = smem_base + L::kStages * L::kStageBytes;
+  Misc* misc = reinterpret_cast<Misc*>(smem_gen + L::kStages * L::kStageBytes + L::kStoreBytes);
   volatile int* abort_flag = &misc->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -322,6 +394,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     for (int s = 0; s < L::kStages; ++s) {
       mbar_init(smem_u32(&misc->full[s]), 1);
       mbar_init(smem_u32(&misc->empty[s]), 1);
+      mbar_init(smem_u32(&misc->sf_full[s]), 4);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&misc->acc_full[s]), 1);
@@ -370,9 +443,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       int e = lane * 8 + i;
-      if (e <= p.experts) misc->prefix[e] = base + local[i];
+      if (e < p.experts) misc->prefix[e] = base + local[i];
     }
-    if (lane == 31) misc->total_m_tiles = incl;
+    if (lane == 31) {
+      misc->total_m_tiles = incl;
+      misc->prefix[p.experts] = incl;
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -380,101 +456,177 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   const uint32_t tmem_base = misc->tmem_base;
   const int total_tiles = misc->total_m_tiles * p.n_tiles;
-  const uint32_t acc_col0 = 0;
-  const uint32_t sfa_col0 = L::kAccStages * kTileN;
-  const uint32_t sfb_col0 = sfa_col0 + kChunksPerStage * 4;
 
   if (warp == 0) {
     // ===================================================== TMA producer
-    if (lane == 0) {
+    {
+      TileWalker walker;
       int stage = 0;
       uint32_t phase = 0;
+      LM_PROF_DECL;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-        const TileCoord t = decode_tile(misc, p, tile);
+        const TileCoord t = walker.at(misc, p, tile);
         const int b_row = t.expert * p.n + t.n_tile * kTileN;
         const uint8_t* sfa_src = p.sfa + static_cast<int64_t>(t.sf_row) * p.atom_cols * 512;
         const int sfb_row0 = t.expert * p.sfb_atom_rows + (t.n_tile * kTileN) / 128;
         bool ok = true;
         for (int ks = 0; ks < p.k_stages; ++ks) {
+          LM_PROF_BEGIN();
           ok = mbar_wait(smem_u32(&misc->empty[stage]), phase ^ 1u, abort_flag, kStatusProducerTimeout);
+          LM_PROF_END(prof_acc0);
           if (!ok) break;
           const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
           const uint32_t sf_bytes = chunks * 512;
           const uint32_t bar = smem_u32(&misc->full[stage]);
           const uint32_t st = smem_base + stage * L::kStageBytes;
-          mbar_expect_tx(bar, L::kABytes + L::kBBytes + sf_bytes * (1 + L::kSfbAtomRows));
-          tma_load_2d(st, &tmap_a, ks * kStageKBytes, t.row0, bar);
-          tma_load_2d(st + L::kABytes, &tmap_b, ks * kStageKBytes, b_row, bar);
-          bulk_load(st + L::kABytes + L::kBBytes, sfa_src + static_cast<int64_t>(ks) * kChunksPerStage * 512,
-                    sf_bytes, bar);
+          if (elect_one()) {
+            mbar_expect_tx(bar, L::kABytes + L::kBBytes + sf_bytes * (1 + L::kSfbAtomRows));
+            tma_load_2d(st, &tmap_a, ks * kStageKBytes, t.row0, bar);
+            tma_load_2d(st + L::kABytes, &tmap_b, ks * kStageKBytes, b_row, bar);
+            bulk_load(st + L::kABytes + L::kBBytes,
+                      sfa_src + static_cast<int64_t>(ks) * kChunksPerStage * 512, sf_bytes, bar);
 #pragma unroll
-          for (int j = 0; j < L::kSfbAtomRows; ++j) {
-            const uint8_t* src = p.sfb + (static_cast<int64_t>(sfb_row0 + j) * p.atom_cols +
-                                          static_cast<int64_t>(ks) * kChunksPerStage) * 512;
-            bulk_load(st + L::kABytes + L::kBBytes + L::kSfaBytes + j * kChunksPerStage * 512, src,
-                      sf_bytes, bar);
+            for (int j = 0; j < L::kSfbAtomRows; ++j) {
+              const uint8_t* src = p.sfb + (static_cast<int64_t>(sfb_row0 + j) * p.atom_cols +
+                                            static_cast<int64_t>(ks) * kChunksPerStage) * 512;
+              bulk_load(st + L::kABytes + L::kBBytes + L::kSfaBytes + j * kChunksPerStage * 512, src,
+                        sf_bytes, bar);
+            }
           }
+          __syncwarp();
           if (++stage == L::kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
       }
+      if (lane == 0) { LM_PROF_STORE(0, prof_acc0); }
     }
   } else if (warp == 1) {
     // ===================================================== MMA issuer
-    if (lane == 0) {
+    {
+#ifdef LM_GEMM_PROFILE
+      // timing experiments only: bits 8.. of debug_flags override the instruction's N
+      const uint32_t idesc = (p.debug_flags >> 8) ? make_idesc(p.debug_flags >> 8) : make_idesc(kTileN);
+#else
       constexpr uint32_t idesc = make_idesc(kTileN);
+#endif
       int stage = 0;
       uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-        bool ok = mbar_wait(smem_u32(&misc->acc_empty[acc]), acc_phase ^ 1u, abort_flag, kStatusMmaTimeout);
+      int it = 0;
+      LM_PROF_DECL;
+      const long long prof_start = clock64();
+      (void)prof_start;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        LM_PROF_BEGIN();
+        bool ok = mbar_wait(smem_u32(&misc->acc_empty[acc]), ((it >> 1) & 1u) ^ 1u, abort_flag,
+                            kStatusMmaTimeout);
+        LM_PROF_END(prof_acc1);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc_col0 + acc * kTileN;
+        const uint32_t d_tmem = tmem_base + acc * kTileN;
         for (int ks = 0; ks < p.k_stages; ++ks) {
+          LM_PROF_BEGIN();
           ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusMmaTimeout);
+          LM_PROF_END(prof_acc0);
           if (!ok) break;
           tc_fence_after();
+          LM_PROF_BEGIN();
           const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
           const uint32_t st = smem_base + stage * L::kStageBytes;
-          const uint32_t sfa_smem = st + L::kABytes + L::kBBytes;
-          const uint32_t sfb_smem = sfa_smem + L::kSfaBytes;
+          // the scale factors of this stage sit in the TMEM slot of the same index
+          LM_PROF_END(prof_acc2);
+          LM_PROF_BEGIN();
+          ok = mbar_wait(smem_u32(&misc->sf_full[stage]), phase, abort_flag, kStatusMmaTimeout);
+          LM_PROF_END(prof_acc0);
+          if (!ok) break;
+          tc_fence_after();
+          LM_PROF_BEGIN();
+          const uint32_t sfa_t = tmem_base + L::kSfCol + stage * L::kSfSlotCols;
+          const uint32_t sfb_t = sfa_t + L::kSfaCols;
           const uint64_t a_desc = desc_sw128(st);
           const uint64_t b_desc = desc_sw128(st + L::kABytes);
-          for (int c = 0; c < chunks; ++c) {
-            const uint32_t sfa_t = tmem_base + sfa_col0 + c * 4;
-            const uint32_t sfb_t = tmem_base + sfb_col0 + c * 4 * L::kSfbAtomRows;
-            tc_copy_sf(sfa_t, desc_sf_atom(sfa_smem + c * 512));
-#pragma unroll
-            for (int j = 0; j < L::kSfbAtomRows; ++j)
-              tc_copy_sf(sfb_t + j * 4, desc_sf_atom(sfb_smem + (j * kChunksPerStage + c) * 512));
-            // 64 FP4 values = 32 bytes along K: +2 in 16-byte descriptor units
-            tc_mma_nvf4(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t, sfb_t,
-                        (ks > 0 || c > 0) ? 1u : 0u);
+          if (elect_one()) {
+#ifdef LM_GEMM_PROFILE
+            if (!(p.debug_flags & 2))
+#endif
+            for (int c = 0; c < chunks; ++c) {
+              // 64 FP4 values = 32 bytes along K: +2 in 16-byte descriptor units
+              tc_mma_nvf4(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4,
+                          sfb_t + c * 4 * L::kSfbAtomRows, (ks > 0 || c > 0) ? 1u : 0u);
+            }
+            tc_commit(smem_u32(&misc->empty[stage]));
           }
-          tc_commit(smem_u32(&misc->empty[stage]));
+          __syncwarp();
+          LM_PROF_END(prof_acc2);
           if (++stage == L::kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        tc_commit(smem_u32(&misc->acc_full[acc]));
-        if (++acc == L::kAccStages) { acc = 0; acc_phase ^= 1u; }
+        if (elect_one()) tc_commit(smem_u32(&misc->acc_full[acc]));
+        __syncwarp();
+      }
+      if (lane == 0) {
+        LM_PROF_STORE(1, prof_acc0);
+        LM_PROF_STORE(2, prof_acc1);
+        LM_PROF_STORE(7, prof_acc2);
+        LM_PROF_STORE(5, clock64() - prof_start);
+        LM_PROF_STORE(6, it);
       }
     }
-  } else {
+  } else if (warp >= kFirstSfWarp && warp < kFirstSfWarp + 4) {
+    // ===================================================== scale factors -> TMEM
+    // Lane l of every quarter needs the same 32 words per stage: for each of the four
+    // 64-element chunks, the 16 bytes at (chunk * 512 + l * 16) of the A atoms (factors of
+    // rows l, l+32, l+64, l+96) and the same for the B atoms.
+    const int quarter = warp & 3;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int ks = 0; ks < p.k_stages; ++ks) {
+        ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusSfTimeout);
+        if (!ok) break;
+        const uint32_t src = smem_base + stage * L::kStageBytes + L::kABytes + L::kBBytes + lane * 16;
+        uint32_t w[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(w[4 * c]), "=r"(w[4 * c + 1]), "=r"(w[4 * c + 2]), "=r"(w[4 * c + 3])
+                       : "r"(src + c * 512));
+        const uint32_t dst = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + L::kSfCol +
+                             stage * L::kSfSlotCols;
+        tc_store32(dst, w);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&misc->sf_full[stage]));
+        if (++stage == L::kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp >= kFirstEpilogueWarp) {
     // ===================================================== epilogue
+    // Two groups of four warps; group g drains accumulator stage g, i.e. every other tile.
+    const int group = (warp - kFirstEpilogueWarp) >> 2;
     const int quarter = warp & 3;           // TMEM lanes this warp may read
     const int r = quarter * 32 + lane;      // row of the tile
-    int acc = 0;
+    const uint32_t my_store = store_base + (warp - kFirstEpilogueWarp) * L::kStoreBytesPerWarp +
+                              lane * L::kStoreRowPitch;
+    TileWalker walker;
     uint32_t acc_phase = 0;
+    LM_PROF_DECL;
     float inv_h = 0.0f;
     if (kOut == LM_OUT_NVFP4) inv_h = __ldg(p.out_scale + 1);
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-      const TileCoord t = decode_tile(misc, p, tile);
+    for (int tile = blockIdx.x + group * gridDim.x; tile < total_tiles; tile += 2 * gridDim.x) {
+      const TileCoord t = walker.at(misc, p, tile);
       const float alpha = __ldg(p.alpha + (p.alpha_per_expert ? t.expert : 0));
-      if (!mbar_wait(smem_u32(&misc->acc_full[acc]), acc_phase, abort_flag, kStatusEpilogueTimeout)) break;
+      LM_PROF_END(prof_acc1);  // busy since the previous wait ended
+      LM_PROF_BEGIN();
+      const bool got = mbar_wait(smem_u32(&misc->acc_full[group]), acc_phase, abort_flag, kStatusEpilogueTimeout);
+      LM_PROF_END(prof_acc0);
+      LM_PROF_BEGIN();
+      if (!got) break;
+      acc_phase ^= 1u;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc_col0 + acc * kTileN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + group * kTileN;
       const bool row_ok = r < t.valid;
       const int64_t out_row = static_cast<int64_t>(t.row0) + r;
 
@@ -508,6 +660,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             sfbytes[2 * c + 1] = requant16(h + 16, inv_h, &qwords[4 * c + 2]);
           }
         }
+        // the accumulator is in registers: hand the TMEM stage back before storing
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[group]));
         if (row_ok) {
           uint8_t* q = static_cast<uint8_t*>(p.out) + out_row * (out_n >> 1) +
                        static_cast<int64_t>(t.n_tile) * (kOutPerTile >> 1);
@@ -525,52 +681,74 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             *reinterpret_cast<uint32_t*>(dst) = word;
           }
         }
+      } else if (kOut == LM_OUT_BF16) {
+        // Each lane converts its row, parks 64 columns (128 B) in its own shared-memory
+        // row and sends them to HBM with one bulk copy: row stores leave as whole lines.
+        const int col0 = t.n_tile * kTileN;
+        __nv_bfloat16* out_base = static_cast<__nv_bfloat16*>(p.out) + out_row * p.n;
+#pragma unroll
+        for (int half = 0; half < kTileN / 64; ++half) {
+          uint32_t packed[32];
+#pragma unroll
+          for (int part = 0; part < 2; ++part) {
+            uint32_t v[32];
+            tc_load32(taddr + half * 64 + part * 32, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              packed[part * 16 + i] =
+                  pack_bf16x2(__uint_as_float(v[2 * i]) * alpha, __uint_as_float(v[2 * i + 1]) * alpha);
+          }
+          if (half == kTileN / 64 - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[group]));
+          }
+          // my previous bulk store must have finished reading my staging row
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_store + i * 16),
+                         "r"(packed[4 * i]), "r"(packed[4 * i + 1]), "r"(packed[4 * i + 2]),
+                         "r"(packed[4 * i + 3])
+                         : "memory");
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          const int col = col0 + half * 64;
+          if (row_ok && col < p.n) {
+            const uint32_t bytes = static_cast<uint32_t>(min(64, p.n - col)) * 2u;
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(out_base + col),
+                         "r"(my_store), "r"(bytes)
+                         : "memory");
+          }
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
       } else {
         const int col0 = t.n_tile * kTileN;
+        float* out_base = static_cast<float*>(p.out) + out_row * p.n;
 #pragma unroll
         for (int c = 0; c < kTileN / 32; ++c) {
           uint32_t v[32];
           tc_load32(taddr + c * 32, v);
           tc_wait_ld();
           const int col = col0 + c * 32;
-          if (row_ok && col < p.n) {
-            if (kOut == LM_OUT_BF16) {
-              __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + out_row * p.n + col;
-              if (col + 32 <= p.n) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  uint32_t w[4];
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]) * alpha,
-                                                             __uint_as_float(v[8 * i + 2 * j + 1]) * alpha);
-                    w[j] = *reinterpret_cast<uint32_t*>(&b);
-                  }
-                  reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
-                }
-              } else {
-                for (int i = 0; i < 32 && col + i < p.n; ++i)
-                  dst[i] = __float2bfloat16_rn(__uint_as_float(v[i]) * alpha);
-              }
-            } else {
-              float* dst = static_cast<float*>(p.out) + out_row * p.n + col;
-              if (col + 32 <= p.n) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  reinterpret_cast<float4*>(dst)[i] =
-                      make_float4(__uint_as_float(v[4 * i]) * alpha, __uint_as_float(v[4 * i + 1]) * alpha,
-                                  __uint_as_float(v[4 * i + 2]) * alpha, __uint_as_float(v[4 * i + 3]) * alpha);
-              } else {
-                for (int i = 0; i < 32 && col + i < p.n; ++i) dst[i] = __uint_as_float(v[i]) * alpha;
-              }
-            }
+          for (int i = 0; i < 8; ++i) {
+            if (row_ok && col + 4 * i < p.n)  // N is a multiple of 8: groups of four never straddle the edge
+              reinterpret_cast<float4*>(out_base + col)[i] =
+                  make_float4(__uint_as_float(v[4 * i]) * alpha, __uint_as_float(v[4 * i + 1]) * alpha,
+                              __uint_as_float(v[4 * i + 2]) * alpha, __uint_as_float(v[4 * i + 3]) * alpha);
           }
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[group]));
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[acc]));
-      if (++acc == L::kAccStages) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (kOut == LM_OUT_BF16) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    LM_PROF_END(prof_acc1);
+    if (warp == kFirstEpilogueWarp && lane == 0) {
+      LM_PROF_STORE(3, prof_acc0);
+      LM_PROF_STORE(4, prof_acc1);
     }
   }
 
@@ -721,6 +899,9 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   p.clamp_limit = a->clamp_limit;
   p.sigmoid_alpha = a->sigmoid_alpha;
   p.up_bias = a->up_bias;
+#ifdef LM_GEMM_PROFILE
+  if (const char* flags = getenv("LM_GEMM_DEBUG")) p.debug_flags = atoi(flags);
+#endif
   const int sms = sm_count();
   LM_REQUIRE(sms > 0, "gemm: no CUDA device");
   pd.grid = a->max_ctas > 0 ? a->max_ctas : sms;
@@ -760,3 +941,12 @@ extern "C" int lm_device_status_clear(lm_stream_t stream) {
   LM_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(uint32_t)));
   return LM_OK;
 }
+
+#ifdef LM_GEMM_PROFILE
+extern "C" int lm_gemm_profile_read(unsigned long long* out, lm_stream_t stream) {
+  using namespace lm;
+  LM_CUDA(cudaStreamSynchronize(as_stream(stream)));
+  LM_CUDA(cudaMemcpyFromSymbol(out, g_prof, sizeof(g_prof)));
+  return LM_OK;
+}
+#endif

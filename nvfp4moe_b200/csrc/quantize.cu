@@ -31,42 +31,65 @@ struct QuantParams {
   int te_math;
 };
 
+// Sixteen consecutive inputs of one row, kept as loaded (8 registers for BF16).
 template <typename In>
-__device__ __forceinline__ void load16(const In* p, float* v);
+struct Slice;
 
 template <>
-__device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, float* v) {
-  const uint4* src = reinterpret_cast<const uint4*>(p);
-  uint4 a = __ldg(src);
-  uint4 b = __ldg(src + 1);
-  uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    v[2 * i] = __uint_as_float(w[i] << 16);
-    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+struct Slice<__nv_bfloat16> {
+  static constexpr int kUnroll = 4;
+  uint32_t w[8];
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+    const uint4* src = reinterpret_cast<const uint4*>(p);
+    uint4 a = __ldg(src);
+    uint4 b = __ldg(src + 1);
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+    w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
   }
-}
+  // max |x|: comparisons in BF16 pick one of the inputs unchanged, so the result is exact
+  __device__ __forceinline__ float amax() const {
+    uint32_t m[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m[i] = w[i] & 0x7FFF7FFFu;
+#pragma unroll
+    for (int d = 4; d >= 1; d >>= 1)
+#pragma unroll
+      for (int i = 0; i < d; ++i)
+        asm("max.bf16x2 %0, %1, %2;" : "=r"(m[i]) : "r"(m[i]), "r"(m[i + d]));
+    return fmaxf(__uint_as_float(m[0] << 16), __uint_as_float(m[0] & 0xFFFF0000u));
+  }
+  __device__ __forceinline__ float lo(int pair) const { return __uint_as_float(w[pair] << 16); }
+  __device__ __forceinline__ float hi(int pair) const { return __uint_as_float(w[pair] & 0xFFFF0000u); }
+};
 
 template <>
-__device__ __forceinline__ void load16<float>(const float* p, float* v) {
-  const float4* src = reinterpret_cast<const float4*>(p);
+struct Slice<float> {
+  static constexpr int kUnroll = 2;
+  float v[16];
+  __device__ __forceinline__ void load(const float* p) {
+    const float4* src = reinterpret_cast<const float4*>(p);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float4 t = __ldg(src + i);
-    v[4 * i] = t.x;
-    v[4 * i + 1] = t.y;
-    v[4 * i + 2] = t.z;
-    v[4 * i + 3] = t.w;
+    for (int i = 0; i < 4; ++i) {
+      float4 t = __ldg(src + i);
+      v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+    }
   }
-}
+  __device__ __forceinline__ float amax() const {
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+    return m;
+  }
+  __device__ __forceinline__ float lo(int pair) const { return v[2 * pair]; }
+  __device__ __forceinline__ float hi(int pair) const { return v[2 * pair + 1]; }
+};
 
 // Quantize one 16-element group.  Returns the scale-factor byte; writes the
 // eight packed bytes to `packed`.
-__device__ __forceinline__ uint32_t quantize_group(const float* v, float pts, float inv_pts,
+template <typename In>
+__device__ __forceinline__ uint32_t quantize_group(const Slice<In>& x, float pts, float inv_pts,
                                                    bool te_math, uint2* packed) {
-  float amax = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  const float amax = x.amax();
   float scaled;
   if (te_math) {
     scaled = __fmul_rn(amax, __fmul_rn(inv_pts, inv6()));
@@ -77,16 +100,17 @@ __device__ __forceinline__ uint32_t quantize_group(const float* v, float pts, fl
   uint32_t sf_byte = f32_to_e4m3(scaled);
   float sf_value = e4m3_to_f32(sf_byte);
   float factor = te_math ? __fdiv_rn(1.0f, __fmul_rn(sf_value, pts)) : __fdiv_rn(inv_pts, sf_value);
-  float s[16];
+  uint32_t out[2] = {0u, 0u};
 #pragma unroll
-  for (int i = 0; i < 16; ++i) s[i] = __fmul_rn(v[i], factor);
-  packed->x = f32x8_to_e2m1(s);
-  packed->y = f32x8_to_e2m1(s + 8);
+  for (int i = 0; i < 8; ++i)
+    out[i >> 2] |= f32x2_to_e2m1(__fmul_rn(x.lo(i), factor), __fmul_rn(x.hi(i), factor)) << (8 * (i & 3));
+  packed->x = out[0];
+  packed->y = out[1];
   return sf_byte;
 }
 
 template <typename In>
-__global__ void __launch_bounds__(kThreads) quantize_rowwise_kernel(QuantParams p) {
+__global__ void __launch_bounds__(kThreads, 4) quantize_rowwise_kernel(QuantParams p) {
   __shared__ __align__(16) uint8_t s_sf[(kTileCols / 64) * 512];
   __shared__ int s_group[4];  // group, local tile, first row, valid rows
 
@@ -153,24 +177,33 @@ __global__ void __launch_bounds__(kThreads) quantize_rowwise_kernel(QuantParams 
   const In* x = static_cast<const In*>(p.x);
   const int groups_per_row = p.features >> 4;
 
-  constexpr int kUnroll = 4;
-  for (int base = warp; base < valid; base += kWarps * kUnroll) {
-    float v[kUnroll][16];
+  // The warp owns rows warp, warp + 8, ...: lane i fetches the source row of the i-th of
+  // them up front, so no row load waits on an index load.
+  int64_t my_src = 0;
+  {
+    const int r = warp + lane * kWarps;
+    if (lane < kTileRows / kWarps && r < valid) {
+      my_src = row0 + r;
+      if (p.gather != nullptr) my_src = __ldg(p.gather + my_src);
+    }
+  }
+
+  constexpr int kUnroll = Slice<In>::kUnroll;
+  for (int base = 0; base < kTileRows / kWarps; base += kUnroll) {
+    if (warp + base * kWarps >= valid) break;
+    Slice<In> v[kUnroll];
     bool ok[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      int r = base + u * kWarps;
+      const int r = warp + (base + u) * kWarps;
+      const int64_t src = __shfl_sync(0xFFFFFFFFu, my_src, base + u);
       ok[u] = col_ok && r < valid;
-      if (ok[u]) {
-        int64_t src = row0 + r;
-        if (p.gather != nullptr) src = __ldg(p.gather + src);
-        load16<In>(x + src * p.features + col, v[u]);
-      }
+      if (ok[u]) v[u].load(x + src * p.features + col);
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       if (!ok[u]) continue;
-      int r = base + u * kWarps;
+      const int r = warp + (base + u) * kWarps;
       uint2 packed;
       uint32_t sf_byte = quantize_group(v[u], pts, inv_pts, te, &packed);
       int64_t out_row = row0 + r;
@@ -221,8 +254,8 @@ __global__ void __launch_bounds__(kThreads) quantize_decode_kernel(DecodeQuantPa
   if (col >= p.features) return;
   const float pts = __ldg(p.scale_pair);
   const float inv_pts = __ldg(p.scale_pair + 1);
-  float v[16];
-  load16<__nv_bfloat16>(p.x + token * p.features + col, v);
+  Slice<__nv_bfloat16> v;
+  v.load(p.x + token * p.features + col);
   uint2 packed;
   uint32_t sf_byte = quantize_group(v, pts, inv_pts, true, &packed);
   const int atom_cols = p.features >> 6;
