@@ -14,8 +14,14 @@
 //                (activate and requantize to NVFP4,) store; each warp owns one TMEM
 //                lane quarter; group g drains accumulator stage g
 // The accumulator is double-buffered in TMEM, so the epilogues of tiles i and i+1
-// overlap each other and the main loop of tile i+2.  Tiles are assigned round-robin; every role walks
-// the same tile list, which it derives from m_indptr in shared memory.
+// overlap each other and the main loop of tile i+2.
+//
+// Work is cut into units of one 128-row tile times a run of 128-column tiles and dealt
+// round-robin to the CTAs.  When the contraction is short enough (K <= 2048) the A tile
+// and its scale factors stay resident in shared memory for the whole unit and only B
+// streams through the ring, which halves the L2 -> SM traffic; otherwise A and B stream
+// together and a unit is a single tile.  Every role derives the same unit list from
+// m_indptr in shared memory.
 //
 // Rows of expert e are [m_indptr[e], m_indptr[e+1]).  A tile's A rows may run
 // into the next expert (or past the end, where TMA fills zeros); those rows are
@@ -32,6 +38,7 @@ namespace lm {
 namespace {
 
 constexpr int kTileM = 128;
+constexpr int kTileN = 128;
 constexpr int kStageKBytes = 128;  // 256 FP4 values per row and stage: one swizzle span
 constexpr int kChunksPerStage = 4; // 64-element MMAs (= scale-factor atoms) per stage
 constexpr int kEpilogueWarps = 8;
@@ -41,6 +48,28 @@ constexpr int kThreads = 32 * (kFirstEpilogueWarp + kEpilogueWarps);
 constexpr int kMaxExperts = 256;
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitLimitCycles = 2000000000ll;  // about one second
+
+// shared memory: operand slots of 18 KB (a 128 x 128 B tile + its 2 KB of scale factors)
+constexpr int kTileBytes = kTileM * kStageKBytes;        // 16384
+constexpr int kSfBytes = kChunksPerStage * 512;          // 2048
+constexpr int kSlotBytes = kTileBytes + kSfBytes;        // 18432
+constexpr int kMaxRing = 8;      // ring stages (also TMEM scale-factor slots)
+constexpr int kMaxResident = 8;  // resident A stages: K <= 2048
+constexpr int kStoreRowPitch = 64 * 2 + 16;              // BF16 staging row: 64 columns + pad
+constexpr int kStoreBytesPerWarp = 32 * kStoreRowPitch;
+constexpr int kStoreBytes = kEpilogueWarps * kStoreBytesPerWarp;
+constexpr int kMiscBytes = 4096;
+constexpr int kSmemLimit = 232448;
+constexpr uint32_t kSfCol = 2 * kTileN;  // TMEM: two accumulators, then 32 columns per ring stage
+static_assert(kSlotBytes % 1024 == 0, "operand slots must keep 1024-byte alignment");
+static_assert(kSfCol + kMaxRing * 32 <= kTmemCols, "TMEM budget");
+
+__host__ __device__ constexpr int data_slots(int out_kind) {
+  return (kSmemLimit - 1024 - kMiscBytes - (out_kind == LM_OUT_BF16 ? kStoreBytes : 0)) / kSlotBytes;
+}
+__host__ __device__ constexpr int smem_bytes(int out_kind) {
+  return 1024 + kMiscBytes + (out_kind == LM_OUT_BF16 ? kStoreBytes : 0) + data_slots(out_kind) * kSlotBytes;
+}
 
 __device__ uint32_t g_status = 0;
 
@@ -77,6 +106,10 @@ struct GemmParams {
   int sfb_atom_rows;  // ceil(n / 128)
   int dense;
   int alpha_per_expert;
+  int a_resident;     // 1: A stays in shared memory for a whole unit
+  int ring_stages;    // stages of the streaming ring
+  int n_per_unit;     // column tiles per unit
+  int units_per_mtile;
   int64_t rows;
   const int32_t* m_indptr;
   const uint8_t* sfa;
@@ -181,12 +214,6 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
                : "memory");
 }
 
-// 32 lanes x 128 bit from shared memory, replicated to the four lane quarters.
-__device__ __forceinline__ void tc_copy_sf(uint32_t tmem_addr, uint64_t smem_desc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(smem_desc)
-               : "memory");
-}
-
 __device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                             uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
                                             uint32_t accumulate) {
@@ -241,16 +268,6 @@ __device__ __forceinline__ uint64_t desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
-// Descriptor of one 512-byte scale-factor atom: 32 rows of 16 bytes, no
-// swizzle, eight-row groups 128 bytes apart.
-__device__ __forceinline__ uint64_t desc_sf_atom(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>(128 >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  return d;
-}
-
 // Instruction descriptor: E2M1 x E2M1, UE4M3 scale factors, K-major A and B,
 // M = 128, N = n, K = 64, FP32 accumulate.
 __host__ __device__ constexpr uint32_t make_idesc(int n) {
@@ -258,39 +275,14 @@ __host__ __device__ constexpr uint32_t make_idesc(int n) {
          (static_cast<uint32_t>(kTileM >> 4) << 24);
 }
 
-template <int kTileN>
-struct SmemLayout {
-  static constexpr int kABytes = kTileM * kStageKBytes;
-  static constexpr int kBBytes = kTileN * kStageKBytes;
-  static constexpr int kSfaBytes = kChunksPerStage * 512;
-  static constexpr int kSfbAtomRows = (kTileN + 127) / 128;
-  static constexpr int kSfbBytes = kSfbAtomRows * kChunksPerStage * 512;
-  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kStages = 5;
-  static constexpr int kAccStages = 2;
-  // BF16 output staging: every epilogue warp owns 32 rows of 64 columns (+16 B pad per row)
-  static constexpr int kStoreRowPitch = 64 * 2 + 16;
-  static constexpr int kStoreBytesPerWarp = 32 * kStoreRowPitch;
-  static constexpr int kStoreBytes = kEpilogueWarps * kStoreBytesPerWarp;
-  static constexpr int kMiscBytes = 4096;
-  static constexpr int kTotal = kStages * kStageBytes + kStoreBytes + kMiscBytes + 1024;
-  // TMEM columns: accumulators, then one scale-factor slot per shared-memory stage
-  // (A factors in the first 16 columns of a slot, B factors after them)
-  static constexpr uint32_t kSfCol = kAccStages * kTileN;
-  static constexpr uint32_t kSfaCols = kChunksPerStage * 4;
-  static constexpr uint32_t kSfSlotCols = kSfaCols * (1 + kSfbAtomRows);
-  static_assert(kSfSlotCols == 32, "the scale-factor writer stores 32 columns per stage");
-  static_assert(kSfCol + kStages * kSfSlotCols <= kTmemCols, "TMEM budget");
-  static_assert(kStageBytes % 1024 == 0, "stages must keep 1024-byte alignment");
-  static_assert(kTotal <= 232448, "shared memory budget");
-};
-
-struct Misc {  // lives after the pipeline stages and the store staging
-  uint64_t full[8];
-  uint64_t empty[8];
+struct Misc {  // lives after the operand slots and the store staging
+  uint64_t full[kMaxRing];         // ring stage filled by TMA
+  uint64_t empty[kMaxRing];        // ring stage drained by the MMAs
+  uint64_t sf_full[kMaxRing];      // scale factors of the ring stage are in TMEM
+  uint64_t a_full[kMaxResident];   // resident A stage filled
+  uint64_t a_empty[kMaxResident];  // resident A stage no longer read
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
-  uint64_t sf_full[8];
   uint32_t tmem_base;
   int abort_flag;
   int total_m_tiles;
@@ -298,28 +290,25 @@ struct Misc {  // lives after the pipeline stages and the store staging
   int cu[kMaxExperts + 1];
   int prefix[kMaxExperts + 2];
 };
-static_assert(sizeof(Misc) <= 4096, "misc block too large");
+static_assert(sizeof(Misc) <= kMiscBytes, "misc block too large");
 
-struct TileCoord {
+struct RowTile {
   int expert;
-  int row0;      // first A / out row of the tile
-  int valid;     // rows of the tile that belong to the expert
-  int sf_row;    // scale-factor atom row of the tile
-  int n_tile;
+  int row0;    // first A / out row of the tile
+  int valid;   // rows of the tile that belong to the expert
+  int sf_row;  // scale-factor atom row of the tile
 };
 
-// Maps the linear tile index (row tile major, column tile minor) to its expert.
-// A role visits tiles in increasing order, so the expert cursor only moves forward.
+// Maps a row-tile index to its expert.  A role visits row tiles in increasing order, so
+// the expert cursor only moves forward.
 struct TileWalker {
   int expert = 0;
-  __device__ __forceinline__ TileCoord at(const Misc* m, const GemmParams& p, int tile) {
-    const int mt = tile / p.n_tiles;
+  __device__ __forceinline__ RowTile at(const Misc* m, const GemmParams& p, int mt) {
     while (expert + 1 < p.experts && m->prefix[expert + 1] <= mt) ++expert;
     const int local = mt - m->prefix[expert];
     const int begin = m->cu[expert];
     const int count = m->cu[expert + 1] - begin;
-    TileCoord t;
-    t.n_tile = tile - mt * p.n_tiles;
+    RowTile t;
     t.expert = expert;
     t.row0 = begin + local * kTileM;
     t.valid = min(kTileM, count - local * kTileM);
@@ -327,6 +316,20 @@ struct TileWalker {
     return t;
   }
 };
+
+// The column-tile run [n_begin, n_end) of row tile mt that makes up one unit.
+struct Unit {
+  int mt;
+  int n_begin;
+  int n_end;
+};
+__device__ __forceinline__ Unit decode_unit(const GemmParams& p, int unit) {
+  Unit u;
+  u.mt = unit / p.units_per_mtile;
+  u.n_begin = (unit - u.mt * p.units_per_mtile) * p.n_per_unit;
+  u.n_end = min(u.n_begin + p.n_per_unit, p.n_tiles);
+  return u;
+}
 
 // ------------------------------------------------------------- activations
 template <int kAct>
@@ -374,27 +377,37 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 // ------------------------------------------------------------------ kernel
-template <int kTileN, int kOut, int kAct>
+template <int kOut, int kAct>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const GemmParams p) {
-  using L = SmemLayout<kTileN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t store_base = smem_base + L::kStages * L::kStageBytes;
-  Misc* misc = reinterpret_cast<Misc*>(smem_gen + L::kStages * L::kStageBytes + L::kStoreBytes);
+  constexpr int kSlots = data_slots(kOut);
+  const uint32_t store_base = smem_base + kSlots * kSlotBytes;
+  Misc* misc = reinterpret_cast<Misc*>(smem_gen + kSlots * kSlotBytes +
+                                       (kOut == LM_OUT_BF16 ? kStoreBytes : 0));
   volatile int* abort_flag = &misc->abort_flag;
+
+  // operand slots: [resident A stages][ring stages]; a ring stage is B (+ A when streaming)
+  const bool resident = p.a_resident != 0;
+  const uint32_t ring_base = smem_base + (resident ? p.k_stages * kSlotBytes : 0);
+  const uint32_t ring_stride = resident ? kSlotBytes : 2 * kSlotBytes;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   // ---- one-time setup
   if (threadIdx.x == 0) {
-    for (int s = 0; s < L::kStages; ++s) {
+    for (int s = 0; s < kMaxRing; ++s) {
       mbar_init(smem_u32(&misc->full[s]), 1);
       mbar_init(smem_u32(&misc->empty[s]), 1);
       mbar_init(smem_u32(&misc->sf_full[s]), 4);
+    }
+    for (int s = 0; s < kMaxResident; ++s) {
+      mbar_init(smem_u32(&misc->a_full[s]), 1);
+      mbar_init(smem_u32(&misc->a_empty[s]), 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&misc->acc_full[s]), 1);
@@ -455,71 +468,86 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   tc_fence_after();
 
   const uint32_t tmem_base = misc->tmem_base;
-  const int total_tiles = misc->total_m_tiles * p.n_tiles;
+  const int total_units = misc->total_m_tiles * p.units_per_mtile;
 
   if (warp == 0) {
     // ===================================================== TMA producer
-    {
-      TileWalker walker;
-      int stage = 0;
-      uint32_t phase = 0;
-      LM_PROF_DECL;
-      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-        const TileCoord t = walker.at(misc, p, tile);
-        const int b_row = t.expert * p.n + t.n_tile * kTileN;
-        const uint8_t* sfa_src = p.sfa + static_cast<int64_t>(t.sf_row) * p.atom_cols * 512;
-        const int sfb_row0 = t.expert * p.sfb_atom_rows + (t.n_tile * kTileN) / 128;
-        bool ok = true;
+    TileWalker walker;
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t a_phase = 0;
+    bool ok = true;
+    LM_PROF_DECL;
+    for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+      const Unit u = decode_unit(p, unit);
+      const RowTile t = walker.at(misc, p, u.mt);
+      const uint8_t* sfa_src = p.sfa + static_cast<int64_t>(t.sf_row) * p.atom_cols * 512;
+      for (int nt = u.n_begin; nt < u.n_end && ok; ++nt) {
+        const int b_row = t.expert * p.n + nt * kTileN;
+        const uint8_t* sfb_src =
+            p.sfb + static_cast<int64_t>(t.expert * p.sfb_atom_rows + nt) * p.atom_cols * 512;
         for (int ks = 0; ks < p.k_stages; ++ks) {
+          const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
+          const uint32_t sf_bytes = chunks * 512;
+          if (resident && nt == u.n_begin) {
+            // the unit's A tile, stage by stage, as soon as the previous unit has let go of it
+            LM_PROF_BEGIN();
+            ok = mbar_wait(smem_u32(&misc->a_empty[ks]), a_phase ^ 1u, abort_flag, kStatusProducerTimeout);
+            LM_PROF_END(prof_acc0);
+            if (!ok) break;
+            if (elect_one()) {
+              const uint32_t bar = smem_u32(&misc->a_full[ks]);
+              const uint32_t dst = smem_base + ks * kSlotBytes;
+              mbar_expect_tx(bar, kTileBytes + sf_bytes);
+              tma_load_2d(dst, &tmap_a, ks * kStageKBytes, t.row0, bar);
+              bulk_load(dst + kTileBytes, sfa_src + static_cast<int64_t>(ks) * kSfBytes, sf_bytes, bar);
+            }
+            __syncwarp();
+          }
           LM_PROF_BEGIN();
           ok = mbar_wait(smem_u32(&misc->empty[stage]), phase ^ 1u, abort_flag, kStatusProducerTimeout);
           LM_PROF_END(prof_acc0);
           if (!ok) break;
-          const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
-          const uint32_t sf_bytes = chunks * 512;
-          const uint32_t bar = smem_u32(&misc->full[stage]);
-          const uint32_t st = smem_base + stage * L::kStageBytes;
           if (elect_one()) {
-            mbar_expect_tx(bar, L::kABytes + L::kBBytes + sf_bytes * (1 + L::kSfbAtomRows));
-            tma_load_2d(st, &tmap_a, ks * kStageKBytes, t.row0, bar);
-            tma_load_2d(st + L::kABytes, &tmap_b, ks * kStageKBytes, b_row, bar);
-            bulk_load(st + L::kABytes + L::kBBytes,
-                      sfa_src + static_cast<int64_t>(ks) * kChunksPerStage * 512, sf_bytes, bar);
-#pragma unroll
-            for (int j = 0; j < L::kSfbAtomRows; ++j) {
-              const uint8_t* src = p.sfb + (static_cast<int64_t>(sfb_row0 + j) * p.atom_cols +
-                                            static_cast<int64_t>(ks) * kChunksPerStage) * 512;
-              bulk_load(st + L::kABytes + L::kBBytes + L::kSfaBytes + j * kChunksPerStage * 512, src,
+            const uint32_t bar = smem_u32(&misc->full[stage]);
+            const uint32_t dst = ring_base + stage * ring_stride;
+            mbar_expect_tx(bar, (kTileBytes + sf_bytes) * (resident ? 1 : 2));
+            tma_load_2d(dst, &tmap_b, ks * kStageKBytes, b_row, bar);
+            bulk_load(dst + kTileBytes, sfb_src + static_cast<int64_t>(ks) * kSfBytes, sf_bytes, bar);
+            if (!resident) {
+              tma_load_2d(dst + kSlotBytes, &tmap_a, ks * kStageKBytes, t.row0, bar);
+              bulk_load(dst + kSlotBytes + kTileBytes, sfa_src + static_cast<int64_t>(ks) * kSfBytes,
                         sf_bytes, bar);
             }
           }
           __syncwarp();
-          if (++stage == L::kStages) { stage = 0; phase ^= 1u; }
+          if (++stage == p.ring_stages) { stage = 0; phase ^= 1u; }
         }
-        if (!ok) break;
       }
-      if (lane == 0) { LM_PROF_STORE(0, prof_acc0); }
+      a_phase ^= 1u;
     }
+    if (lane == 0) { LM_PROF_STORE(0, prof_acc0); }
   } else if (warp == 1) {
     // ===================================================== MMA issuer
-    {
 #ifdef LM_GEMM_PROFILE
-      // timing experiments only: bits 8.. of debug_flags override the instruction's N
-      const uint32_t idesc = (p.debug_flags >> 8) ? make_idesc(p.debug_flags >> 8) : make_idesc(kTileN);
+    const uint32_t idesc = (p.debug_flags >> 8) ? make_idesc(p.debug_flags >> 8) : make_idesc(kTileN);
 #else
-      constexpr uint32_t idesc = make_idesc(kTileN);
+    constexpr uint32_t idesc = make_idesc(kTileN);
 #endif
-      int stage = 0;
-      uint32_t phase = 0;
-      int it = 0;
-      LM_PROF_DECL;
-      const long long prof_start = clock64();
-      (void)prof_start;
-      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t a_phase = 0;
+    int it = 0;
+    bool ok = true;
+    LM_PROF_DECL;
+    const long long prof_start = clock64();
+    (void)prof_start;
+    for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+      const Unit u = decode_unit(p, unit);
+      for (int nt = u.n_begin; nt < u.n_end && ok; ++nt, ++it) {
         const int acc = it & 1;
         LM_PROF_BEGIN();
-        bool ok = mbar_wait(smem_u32(&misc->acc_empty[acc]), ((it >> 1) & 1u) ^ 1u, abort_flag,
-                            kStatusMmaTimeout);
+        ok = mbar_wait(smem_u32(&misc->acc_empty[acc]), ((it >> 1) & 1u) ^ 1u, abort_flag, kStatusMmaTimeout);
         LM_PROF_END(prof_acc1);
         if (!ok) break;
         tc_fence_after();
@@ -527,50 +555,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         for (int ks = 0; ks < p.k_stages; ++ks) {
           LM_PROF_BEGIN();
           ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusMmaTimeout);
+          if (ok && resident && nt == u.n_begin)
+            ok = mbar_wait(smem_u32(&misc->a_full[ks]), a_phase, abort_flag, kStatusMmaTimeout);
+          // the scale factors of this stage sit in the TMEM slot of the same index
+          if (ok) ok = mbar_wait(smem_u32(&misc->sf_full[stage]), phase, abort_flag, kStatusMmaTimeout);
           LM_PROF_END(prof_acc0);
           if (!ok) break;
           tc_fence_after();
           LM_PROF_BEGIN();
           const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
-          const uint32_t st = smem_base + stage * L::kStageBytes;
-          // the scale factors of this stage sit in the TMEM slot of the same index
-          LM_PROF_END(prof_acc2);
-          LM_PROF_BEGIN();
-          ok = mbar_wait(smem_u32(&misc->sf_full[stage]), phase, abort_flag, kStatusMmaTimeout);
-          LM_PROF_END(prof_acc0);
-          if (!ok) break;
-          tc_fence_after();
-          LM_PROF_BEGIN();
-          const uint32_t sfa_t = tmem_base + L::kSfCol + stage * L::kSfSlotCols;
-          const uint32_t sfb_t = sfa_t + L::kSfaCols;
-          const uint64_t a_desc = desc_sw128(st);
-          const uint64_t b_desc = desc_sw128(st + L::kABytes);
+          const uint32_t b_smem = ring_base + stage * ring_stride;
+          const uint32_t a_smem = resident ? smem_base + ks * kSlotBytes : b_smem + kSlotBytes;
+          const uint32_t sfa_t = tmem_base + kSfCol + stage * 32;
+          const uint32_t sfb_t = sfa_t + 16;
+          const uint64_t a_desc = desc_sw128(a_smem);
+          const uint64_t b_desc = desc_sw128(b_smem);
           if (elect_one()) {
 #ifdef LM_GEMM_PROFILE
             if (!(p.debug_flags & 2))
 #endif
             for (int c = 0; c < chunks; ++c) {
               // 64 FP4 values = 32 bytes along K: +2 in 16-byte descriptor units
-              tc_mma_nvf4(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4,
-                          sfb_t + c * 4 * L::kSfbAtomRows, (ks > 0 || c > 0) ? 1u : 0u);
+              tc_mma_nvf4(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 4,
+                          (ks > 0 || c > 0) ? 1u : 0u);
             }
             tc_commit(smem_u32(&misc->empty[stage]));
+            if (resident && nt == u.n_end - 1) tc_commit(smem_u32(&misc->a_empty[ks]));
           }
           __syncwarp();
           LM_PROF_END(prof_acc2);
-          if (++stage == L::kStages) { stage = 0; phase ^= 1u; }
+          if (++stage == p.ring_stages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         if (elect_one()) tc_commit(smem_u32(&misc->acc_full[acc]));
         __syncwarp();
       }
-      if (lane == 0) {
-        LM_PROF_STORE(1, prof_acc0);
-        LM_PROF_STORE(2, prof_acc1);
-        LM_PROF_STORE(7, prof_acc2);
-        LM_PROF_STORE(5, clock64() - prof_start);
-        LM_PROF_STORE(6, it);
-      }
+      a_phase ^= 1u;
+    }
+    if (lane == 0) {
+      LM_PROF_STORE(1, prof_acc0);
+      LM_PROF_STORE(2, prof_acc1);
+      LM_PROF_STORE(7, prof_acc2);
+      LM_PROF_STORE(5, clock64() - prof_start);
+      LM_PROF_STORE(6, it);
     }
   } else if (warp >= kFirstSfWarp && warp < kFirstSfWarp + 4) {
     // ===================================================== scale factors -> TMEM
@@ -580,27 +607,40 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int quarter = warp & 3;
     int stage = 0;
     uint32_t phase = 0;
+    uint32_t a_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      for (int ks = 0; ks < p.k_stages; ++ks) {
-        ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusSfTimeout);
-        if (!ok) break;
-        const uint32_t src = smem_base + stage * L::kStageBytes + L::kABytes + L::kBBytes + lane * 16;
-        uint32_t w[32];
+    for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+      const Unit u = decode_unit(p, unit);
+      for (int nt = u.n_begin; nt < u.n_end && ok; ++nt) {
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusSfTimeout);
+          if (ok && resident && nt == u.n_begin)
+            ok = mbar_wait(smem_u32(&misc->a_full[ks]), a_phase, abort_flag, kStatusSfTimeout);
+          if (!ok) break;
+          const uint32_t b_smem = ring_base + stage * ring_stride;
+          const uint32_t a_smem = resident ? smem_base + ks * kSlotBytes : b_smem + kSlotBytes;
+          const uint32_t sfa_src = a_smem + kTileBytes + lane * 16;
+          const uint32_t sfb_src = b_smem + kTileBytes + lane * 16;
+          uint32_t w[32];
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(w[4 * c]), "=r"(w[4 * c + 1]), "=r"(w[4 * c + 2]), "=r"(w[4 * c + 3])
-                       : "r"(src + c * 512));
-        const uint32_t dst = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + L::kSfCol +
-                             stage * L::kSfSlotCols;
-        tc_store32(dst, w);
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&misc->sf_full[stage]));
-        if (++stage == L::kStages) { stage = 0; phase ^= 1u; }
+          for (int c = 0; c < 4; ++c) {
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(w[4 * c]), "=r"(w[4 * c + 1]), "=r"(w[4 * c + 2]), "=r"(w[4 * c + 3])
+                         : "r"(sfa_src + c * 512));
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(w[16 + 4 * c]), "=r"(w[17 + 4 * c]), "=r"(w[18 + 4 * c]), "=r"(w[19 + 4 * c])
+                         : "r"(sfb_src + c * 512));
+          }
+          const uint32_t dst = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kSfCol + stage * 32;
+          tc_store32(dst, w);
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&misc->sf_full[stage]));
+          if (++stage == p.ring_stages) { stage = 0; phase ^= 1u; }
+        }
       }
+      a_phase ^= 1u;
     }
   } else if (warp >= kFirstEpilogueWarp) {
     // ===================================================== epilogue
@@ -608,143 +648,154 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int group = (warp - kFirstEpilogueWarp) >> 2;
     const int quarter = warp & 3;           // TMEM lanes this warp may read
     const int r = quarter * 32 + lane;      // row of the tile
-    const uint32_t my_store = store_base + (warp - kFirstEpilogueWarp) * L::kStoreBytesPerWarp +
-                              lane * L::kStoreRowPitch;
+    const uint32_t warp_store = store_base + (warp - kFirstEpilogueWarp) * kStoreBytesPerWarp;
+    (void)warp_store;
     TileWalker walker;
     uint32_t acc_phase = 0;
+    int it = 0;
+    bool ok = true;
     LM_PROF_DECL;
     float inv_h = 0.0f;
     if (kOut == LM_OUT_NVFP4) inv_h = __ldg(p.out_scale + 1);
-    for (int tile = blockIdx.x + group * gridDim.x; tile < total_tiles; tile += 2 * gridDim.x) {
-      const TileCoord t = walker.at(misc, p, tile);
+    for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+      const Unit u = decode_unit(p, unit);
+      const RowTile t = walker.at(misc, p, u.mt);
       const float alpha = __ldg(p.alpha + (p.alpha_per_expert ? t.expert : 0));
-      LM_PROF_END(prof_acc1);  // busy since the previous wait ended
-      LM_PROF_BEGIN();
-      const bool got = mbar_wait(smem_u32(&misc->acc_full[group]), acc_phase, abort_flag, kStatusEpilogueTimeout);
-      LM_PROF_END(prof_acc0);
-      LM_PROF_BEGIN();
-      if (!got) break;
-      acc_phase ^= 1u;
-      tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + group * kTileN;
       const bool row_ok = r < t.valid;
       const int64_t out_row = static_cast<int64_t>(t.row0) + r;
+      for (int nt = u.n_begin; nt < u.n_end; ++nt, ++it) {
+        if ((it & 1) != group) continue;
+        LM_PROF_END(prof_acc1);  // busy since the previous wait ended
+        LM_PROF_BEGIN();
+        ok = mbar_wait(smem_u32(&misc->acc_full[group]), acc_phase, abort_flag, kStatusEpilogueTimeout);
+        LM_PROF_END(prof_acc0);
+        LM_PROF_BEGIN();
+        if (!ok) break;
+        acc_phase ^= 1u;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + group * kTileN;
 
-      if (kOut == LM_OUT_NVFP4) {
-        constexpr bool kGated = kAct != LM_ACT_RELU2;
-        constexpr int kOutPerChunk = kGated ? 16 : 32;       // outputs per 32 accumulator columns
-        constexpr int kOutPerTile = kOutPerChunk * (kTileN / 32);
-        const int out_n = p.out_atom_cols * 64;
-        uint32_t qwords[kOutPerTile / 8];
-        uint32_t sfbytes[kOutPerTile / 16];
+        if (kOut == LM_OUT_NVFP4) {
+          constexpr bool kGated = kAct != LM_ACT_RELU2;
+          constexpr int kOutPerChunk = kGated ? 16 : 32;       // outputs per 32 accumulator columns
+          constexpr int kOutPerTile = kOutPerChunk * (kTileN / 32);
+          const int out_n = p.out_atom_cols * 64;
+          uint32_t qwords[kOutPerTile / 8];
+          uint32_t sfbytes[kOutPerTile / 16];
 #pragma unroll
-        for (int c = 0; c < kTileN / 32; ++c) {
-          uint32_t v[32];
-          tc_load32(taddr + c * 32, v);
-          tc_wait_ld();
-          if (kGated) {
-            float h[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              h[i] = gated_value<kAct>(__uint_as_float(v[2 * i]) * alpha,
-                                       __uint_as_float(v[2 * i + 1]) * alpha, p);
-            sfbytes[c] = requant16(h, inv_h, &qwords[2 * c]);
-          } else {
-            float h[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              float x = fmaxf(__uint_as_float(v[i]) * alpha, 0.0f);
-              h[i] = x * x;
-            }
-            sfbytes[2 * c] = requant16(h, inv_h, &qwords[4 * c]);
-            sfbytes[2 * c + 1] = requant16(h + 16, inv_h, &qwords[4 * c + 2]);
-          }
-        }
-        // the accumulator is in registers: hand the TMEM stage back before storing
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[group]));
-        if (row_ok) {
-          uint8_t* q = static_cast<uint8_t*>(p.out) + out_row * (out_n >> 1) +
-                       static_cast<int64_t>(t.n_tile) * (kOutPerTile >> 1);
-#pragma unroll
-          for (int i = 0; i < kOutPerTile / 32; ++i)
-            reinterpret_cast<uint4*>(q)[i] =
-                make_uint4(qwords[4 * i], qwords[4 * i + 1], qwords[4 * i + 2], qwords[4 * i + 3]);
-#pragma unroll
-          for (int w = 0; w < kOutPerTile / 64; ++w) {
-            uint32_t word = sfbytes[4 * w] | (sfbytes[4 * w + 1] << 8) | (sfbytes[4 * w + 2] << 16) |
-                            (sfbytes[4 * w + 3] << 24);
-            const int atom_col = t.n_tile * (kOutPerTile / 64) + w;
-            uint8_t* dst = p.out_sf + (static_cast<int64_t>(t.sf_row) * p.out_atom_cols + atom_col) * 512 +
-                           lane * 16 + quarter * 4;
-            *reinterpret_cast<uint32_t*>(dst) = word;
-          }
-        }
-      } else if (kOut == LM_OUT_BF16) {
-        // Each lane converts its row, parks 64 columns (128 B) in its own shared-memory
-        // row and sends them to HBM with one bulk copy: row stores leave as whole lines.
-        const int col0 = t.n_tile * kTileN;
-        __nv_bfloat16* out_base = static_cast<__nv_bfloat16*>(p.out) + out_row * p.n;
-#pragma unroll
-        for (int half = 0; half < kTileN / 64; ++half) {
-          uint32_t packed[32];
-#pragma unroll
-          for (int part = 0; part < 2; ++part) {
+          for (int c = 0; c < kTileN / 32; ++c) {
             uint32_t v[32];
-            tc_load32(taddr + half * 64 + part * 32, v);
+            tc_load32(taddr + c * 32, v);
             tc_wait_ld();
+            if (kGated) {
+              float h[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-              packed[part * 16 + i] =
-                  pack_bf16x2(__uint_as_float(v[2 * i]) * alpha, __uint_as_float(v[2 * i + 1]) * alpha);
+              for (int i = 0; i < 16; ++i)
+                h[i] = gated_value<kAct>(__uint_as_float(v[2 * i]) * alpha,
+                                         __uint_as_float(v[2 * i + 1]) * alpha, p);
+              sfbytes[c] = requant16(h, inv_h, &qwords[2 * c]);
+            } else {
+              float h[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                float x = fmaxf(__uint_as_float(v[i]) * alpha, 0.0f);
+                h[i] = x * x;
+              }
+              sfbytes[2 * c] = requant16(h, inv_h, &qwords[4 * c]);
+              sfbytes[2 * c + 1] = requant16(h + 16, inv_h, &qwords[4 * c + 2]);
+            }
           }
-          if (half == kTileN / 64 - 1) {
-            tc_fence_before();
+          // the accumulator is in registers: hand the TMEM stage back before storing
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[group]));
+          if (row_ok) {
+            uint8_t* q = static_cast<uint8_t*>(p.out) + out_row * (out_n >> 1) +
+                         static_cast<int64_t>(nt) * (kOutPerTile >> 1);
+#pragma unroll
+            for (int i = 0; i < kOutPerTile / 32; ++i)
+              reinterpret_cast<uint4*>(q)[i] =
+                  make_uint4(qwords[4 * i], qwords[4 * i + 1], qwords[4 * i + 2], qwords[4 * i + 3]);
+#pragma unroll
+            for (int w = 0; w < kOutPerTile / 64; ++w) {
+              uint32_t word = sfbytes[4 * w] | (sfbytes[4 * w + 1] << 8) | (sfbytes[4 * w + 2] << 16) |
+                              (sfbytes[4 * w + 3] << 24);
+              const int atom_col = nt * (kOutPerTile / 64) + w;
+              uint8_t* dst = p.out_sf + (static_cast<int64_t>(t.sf_row) * p.out_atom_cols + atom_col) * 512 +
+                             lane * 16 + quarter * 4;
+              *reinterpret_cast<uint32_t*>(dst) = word;
+            }
+          }
+        } else if (kOut == LM_OUT_BF16) {
+          // Lane = row while converting; the warp's 32 x 64 block is transposed through its
+          // shared-memory staging so that a global store covers four whole 128-byte row pieces.
+          const int col0 = nt * kTileN;
+          const int rows_here = t.valid - quarter * 32;  // valid rows among this warp's 32
+          __nv_bfloat16* warp_out =
+              static_cast<__nv_bfloat16*>(p.out) + (static_cast<int64_t>(t.row0) + quarter * 32) * p.n;
+#pragma unroll
+          for (int half = 0; half < kTileN / 64; ++half) {
+            uint32_t packed[32];
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+              uint32_t v[32];
+              tc_load32(taddr + half * 64 + part * 32, v);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                packed[part * 16 + i] =
+                    pack_bf16x2(__uint_as_float(v[2 * i]) * alpha, __uint_as_float(v[2 * i + 1]) * alpha);
+            }
+            if (half == kTileN / 64 - 1) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[group]));
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(warp_store + lane * kStoreRowPitch +
+                                                                             i * 16),
+                           "r"(packed[4 * i]), "r"(packed[4 * i + 1]), "r"(packed[4 * i + 2]),
+                           "r"(packed[4 * i + 3])
+                           : "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[group]));
-          }
-          // my previous bulk store must have finished reading my staging row
-          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            const int piece = lane & 7;
+            const int col = col0 + half * 64 + piece * 8;
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_store + i * 16),
-                         "r"(packed[4 * i]), "r"(packed[4 * i + 1]), "r"(packed[4 * i + 2]),
-                         "r"(packed[4 * i + 3])
-                         : "memory");
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          const int col = col0 + half * 64;
-          if (row_ok && col < p.n) {
-            const uint32_t bytes = static_cast<uint32_t>(min(64, p.n - col)) * 2u;
-            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(out_base + col),
-                         "r"(my_store), "r"(bytes)
-                         : "memory");
+            for (int i = 0; i < 8; ++i) {
+              const int row = 4 * i + (lane >> 3);
+              uint4 d;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(d.x), "=r"(d.y), "=r"(d.z), "=r"(d.w)
+                           : "r"(warp_store + row * kStoreRowPitch + piece * 16));
+              if (row < rows_here && col < p.n)
+                *reinterpret_cast<uint4*>(warp_out + static_cast<int64_t>(row) * p.n + col) = d;
+            }
+            __syncwarp();
           }
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        } else {
+          const int col0 = nt * kTileN;
+          float* out_base = static_cast<float*>(p.out) + out_row * p.n;
+#pragma unroll
+          for (int c = 0; c < kTileN / 32; ++c) {
+            uint32_t v[32];
+            tc_load32(taddr + c * 32, v);
+            tc_wait_ld();
+            const int col = col0 + c * 32;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              if (row_ok && col + 4 * i < p.n)  // N is a multiple of 8: groups of four never straddle the edge
+                reinterpret_cast<float4*>(out_base + col)[i] =
+                    make_float4(__uint_as_float(v[4 * i]) * alpha, __uint_as_float(v[4 * i + 1]) * alpha,
+                                __uint_as_float(v[4 * i + 2]) * alpha, __uint_as_float(v[4 * i + 3]) * alpha);
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[group]));
         }
-      } else {
-        const int col0 = t.n_tile * kTileN;
-        float* out_base = static_cast<float*>(p.out) + out_row * p.n;
-#pragma unroll
-        for (int c = 0; c < kTileN / 32; ++c) {
-          uint32_t v[32];
-          tc_load32(taddr + c * 32, v);
-          tc_wait_ld();
-          const int col = col0 + c * 32;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            if (row_ok && col + 4 * i < p.n)  // N is a multiple of 8: groups of four never straddle the edge
-              reinterpret_cast<float4*>(out_base + col)[i] =
-                  make_float4(__uint_as_float(v[4 * i]) * alpha, __uint_as_float(v[4 * i + 1]) * alpha,
-                              __uint_as_float(v[4 * i + 2]) * alpha, __uint_as_float(v[4 * i + 3]) * alpha);
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[group]));
       }
     }
-    if (kOut == LM_OUT_BF16) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     LM_PROF_END(prof_acc1);
     if (warp == kFirstEpilogueWarp && lane == 0) {
       LM_PROF_STORE(3, prof_acc0);
@@ -772,11 +823,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 // --------------------------------------------------------------- host side
 struct PlanData {
   uint32_t magic;
-  int32_t tile_n;
   int32_t out_kind;
   int32_t activation;
   int32_t grid;
-  int32_t smem_bytes;
   GemmParams params;
   alignas(64) CUtensorMap map_a;
   alignas(64) CUtensorMap map_b;
@@ -816,30 +865,28 @@ int encode_bytes_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, ui
   return LM_OK;
 }
 
-template <int kTileN, int kOut, int kAct>
+template <int kOut, int kAct>
 int launch_variant(const PlanData& pd, cudaStream_t stream) {
-  auto kernel = gemm_kernel<kTileN, kOut, kAct>;
+  auto kernel = gemm_kernel<kOut, kAct>;
   static bool configured = false;
   if (!configured) {
-    LM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 SmemLayout<kTileN>::kTotal));
+    LM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(kOut)));
     configured = true;
   }
-  kernel<<<pd.grid, kThreads, SmemLayout<kTileN>::kTotal, stream>>>(pd.map_a, pd.map_b, pd.params);
+  kernel<<<pd.grid, kThreads, smem_bytes(kOut), stream>>>(pd.map_a, pd.map_b, pd.params);
   LM_CUDA(cudaGetLastError());
   return LM_OK;
 }
 
-template <int kTileN>
-int launch_tile(const PlanData& pd, cudaStream_t stream) {
-  if (pd.out_kind == LM_OUT_BF16) return launch_variant<kTileN, LM_OUT_BF16, LM_ACT_NONE>(pd, stream);
-  if (pd.out_kind == LM_OUT_F32) return launch_variant<kTileN, LM_OUT_F32, LM_ACT_NONE>(pd, stream);
+int launch_plan(const PlanData& pd, cudaStream_t stream) {
+  if (pd.out_kind == LM_OUT_BF16) return launch_variant<LM_OUT_BF16, LM_ACT_NONE>(pd, stream);
+  if (pd.out_kind == LM_OUT_F32) return launch_variant<LM_OUT_F32, LM_ACT_NONE>(pd, stream);
   switch (pd.activation) {
-    case LM_ACT_SWIGLU: return launch_variant<kTileN, LM_OUT_NVFP4, LM_ACT_SWIGLU>(pd, stream);
-    case LM_ACT_SWIGLU_OAI: return launch_variant<kTileN, LM_OUT_NVFP4, LM_ACT_SWIGLU_OAI>(pd, stream);
-    case LM_ACT_GEGLU: return launch_variant<kTileN, LM_OUT_NVFP4, LM_ACT_GEGLU>(pd, stream);
-    case LM_ACT_REGLU: return launch_variant<kTileN, LM_OUT_NVFP4, LM_ACT_REGLU>(pd, stream);
-    case LM_ACT_RELU2: return launch_variant<kTileN, LM_OUT_NVFP4, LM_ACT_RELU2>(pd, stream);
+    case LM_ACT_SWIGLU: return launch_variant<LM_OUT_NVFP4, LM_ACT_SWIGLU>(pd, stream);
+    case LM_ACT_SWIGLU_OAI: return launch_variant<LM_OUT_NVFP4, LM_ACT_SWIGLU_OAI>(pd, stream);
+    case LM_ACT_GEGLU: return launch_variant<LM_OUT_NVFP4, LM_ACT_GEGLU>(pd, stream);
+    case LM_ACT_REGLU: return launch_variant<LM_OUT_NVFP4, LM_ACT_REGLU>(pd, stream);
+    case LM_ACT_RELU2: return launch_variant<LM_OUT_NVFP4, LM_ACT_RELU2>(pd, stream);
   }
   return set_error(LM_ERR_INVALID, "gemm: unknown activation");
 }
@@ -863,7 +910,6 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
              "gemm: operands must be 16-byte aligned");
   PlanData pd{};
   pd.magic = kPlanMagic;
-  pd.tile_n = 128;
   pd.out_kind = a->out_kind;
   pd.activation = a->activation;
   GemmParams& p = pd.params;
@@ -882,7 +928,7 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   }
   p.experts = a->experts;
   p.n = a->n;
-  p.n_tiles = (a->n + pd.tile_n - 1) / pd.tile_n;
+  p.n_tiles = (a->n + kTileN - 1) / kTileN;
   p.atom_cols = a->k / 64;
   p.k_stages = (p.atom_cols + kChunksPerStage - 1) / kChunksPerStage;
   p.sfb_atom_rows = (a->n + 127) / 128;
@@ -905,13 +951,35 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   const int sms = sm_count();
   LM_REQUIRE(sms > 0, "gemm: no CUDA device");
   pd.grid = a->max_ctas > 0 ? a->max_ctas : sms;
-  // more CTAs than tiles would only idle: rows/128 + experts bounds the row tiles
-  const int64_t max_tiles = ((a->rows + kTileM - 1) / kTileM + a->experts) * p.n_tiles;
-  if (pd.grid > max_tiles) pd.grid = static_cast<int>(max_tiles);
+
+  // ---- shared-memory plan: keep A resident when the contraction is short enough
+  const int slots = data_slots(a->out_kind);
+  const int64_t m_tiles_est = (a->rows + kTileM - 1) / kTileM + (a->dense ? 0 : a->experts / 2);
+  // Resident A halves the bytes an SM has to pull in per tile, but the ring that is left must
+  // still hold enough bytes in flight to cover the load latency (measured: a 4-stage ring of B
+  // tiles loses more than the halved traffic wins), so it needs at least six ring stages.
+  p.a_resident = (p.k_stages <= kMaxResident && slots - p.k_stages >= 6 && p.n_tiles >= 2) ? 1 : 0;
+#ifdef LM_GEMM_PROFILE
+  if (p.debug_flags & 4) p.a_resident = 0;
+#endif
+  if (p.a_resident) {
+    p.ring_stages = slots - p.k_stages < kMaxRing ? slots - p.k_stages : kMaxRing;
+    // the longest run of column tiles that still leaves about eight units per CTA
+    int run = p.n_tiles;
+    while (run > 1 && m_tiles_est * ((p.n_tiles + run - 1) / run) < 8ll * pd.grid) run = (run + 1) / 2;
+    p.n_per_unit = run;
+  } else {
+    p.ring_stages = slots / 2 < kMaxRing ? slots / 2 : kMaxRing;
+    p.n_per_unit = 1;
+  }
+  p.units_per_mtile = (p.n_tiles + p.n_per_unit - 1) / p.n_per_unit;
+  // more CTAs than units would only idle: rows/128 + experts bounds the row tiles
+  const int64_t max_units = ((a->rows + kTileM - 1) / kTileM + a->experts) * p.units_per_mtile;
+  if (pd.grid > max_units) pd.grid = static_cast<int>(max_units);
   int rc = encode_bytes_2d(&pd.map_a, a->a, static_cast<uint64_t>(a->k / 2), static_cast<uint64_t>(a->rows), kTileM);
   if (rc != LM_OK) return rc;
   rc = encode_bytes_2d(&pd.map_b, a->b, static_cast<uint64_t>(a->k / 2),
-                       static_cast<uint64_t>(a->experts) * a->n, pd.tile_n);
+                       static_cast<uint64_t>(a->experts) * a->n, kTileN);
   if (rc != LM_OK) return rc;
   memcpy(plan, &pd, sizeof(pd));
   return LM_OK;
@@ -923,7 +991,7 @@ extern "C" int lm_gemm_launch(const lm_gemm_plan* plan, lm_stream_t stream) {
   PlanData pd;  // the caller's storage need not be 64-byte aligned: work on a copy
   memcpy(&pd, plan, sizeof(pd));
   LM_REQUIRE(pd.magic == kPlanMagic, "gemm: plan was not prepared");
-  return launch_tile<128>(pd, as_stream(stream));
+  return launch_plan(pd, as_stream(stream));
 }
 
 extern "C" int lm_device_status(uint32_t* out, lm_stream_t stream) {
