@@ -100,12 +100,14 @@ __device__ __forceinline__ uint32_t quantize_group(const Slice<In>& x, float pts
   uint32_t sf_byte = f32_to_e4m3(scaled);
   float sf_value = e4m3_to_f32(sf_byte);
   float factor = te_math ? __fdiv_rn(1.0f, __fmul_rn(sf_value, pts)) : __fdiv_rn(inv_pts, sf_value);
-  uint32_t out[2] = {0u, 0u};
+  float s[16];
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
-    out[i >> 2] |= f32x2_to_e2m1(__fmul_rn(x.lo(i), factor), __fmul_rn(x.hi(i), factor)) << (8 * (i & 3));
-  packed->x = out[0];
-  packed->y = out[1];
+  for (int i = 0; i < 8; ++i) {
+    s[2 * i] = __fmul_rn(x.lo(i), factor);
+    s[2 * i + 1] = __fmul_rn(x.hi(i), factor);
+  }
+  packed->x = f32x8_to_e2m1(s);
+  packed->y = f32x8_to_e2m1(s + 8);
   return sf_byte;
 }
 
@@ -230,9 +232,11 @@ __global__ void __launch_bounds__(kThreads, 4) quantize_rowwise_kernel(QuantPara
   }
 }
 
-// ---------------------------------------------------------------- decode path
-// One warp per (token, 512-feature slice): quantize once, store to each slot.
-struct DecodeQuantParams {
+// ------------------------------------------------- quantize once, scatter to slots
+// One warp per (token, 512-feature slice): the slice is quantized once and its packed codes
+// (256 B, one coalesced store) and scale factors (eight 4-byte words, one per 64-feature atom)
+// are written to every expert-major row the token was routed to.
+struct ScatterQuantParams {
   const __nv_bfloat16* x;
   int64_t tokens;
   int features;
@@ -245,29 +249,51 @@ struct DecodeQuantParams {
   uint8_t* sf;
 };
 
-__global__ void __launch_bounds__(kThreads) quantize_decode_kernel(DecodeQuantParams p) {
+__global__ void __launch_bounds__(kThreads) quantize_scatter_kernel(ScatterQuantParams p) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int64_t token = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
   if (token >= p.tokens) return;
   const int col = blockIdx.y * kTileCols + lane * 16;
-  if (col >= p.features) return;
+  const bool col_ok = col < p.features;
+  // destination of route `lane` (lanes beyond top_k idle): row, then its scale-factor atom row
+  int my_slot = -1, my_atom_row = 0, my_r = 0;
+  if (lane < p.top_k) {
+    my_slot = __ldg(p.slots + token * p.top_k + lane);
+    if (my_slot >= 0) {
+      const int e = __ldg(p.topk_ids + token * p.top_k + lane);
+      const int lo = __ldg(p.m_indptr + e);
+      const int local = my_slot - lo;
+      my_atom_row = lo / kTileRows + e + local / kTileRows;
+      my_r = local % kTileRows;
+    }
+  }
   const float pts = __ldg(p.scale_pair);
   const float inv_pts = __ldg(p.scale_pair + 1);
   Slice<__nv_bfloat16> v;
-  v.load(p.x + token * p.features + col);
-  uint2 packed;
-  uint32_t sf_byte = quantize_group(v, pts, inv_pts, true, &packed);
+  uint2 packed = make_uint2(0, 0);
+  uint32_t sf_byte = 0;
+  if (col_ok) {
+    v.load(p.x + token * p.features + col);
+    sf_byte = quantize_group(v, pts, inv_pts, true, &packed);
+  }
+  // four neighbouring lanes hold the four factors of one atom word
+  uint32_t word = sf_byte;
+  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 1) << 8;
+  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 2) << 16;
+  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 3) << 24;
   const int atom_cols = p.features >> 6;
   for (int j = 0; j < p.top_k; ++j) {
-    int slot = __ldg(p.slots + token * p.top_k + j);
-    if (slot < 0) continue;
-    int e = __ldg(p.topk_ids + token * p.top_k + j);
-    int lo = __ldg(p.m_indptr + e);
-    int local = slot - lo;
+    const int slot = __shfl_sync(0xFFFFFFFFu, my_slot, j);
+    const int atom_row = __shfl_sync(0xFFFFFFFFu, my_atom_row, j);
+    const int r = __shfl_sync(0xFFFFFFFFu, my_r, j);
+    if (slot < 0 || !col_ok) continue;
     *reinterpret_cast<uint2*>(p.q + static_cast<int64_t>(slot) * (p.features >> 1) + (col >> 1)) = packed;
-    int64_t atom_row = lo / kTileRows + e + local / kTileRows;
-    p.sf[sf_offset(atom_row, atom_cols, local % kTileRows, col >> 4)] = static_cast<uint8_t>(sf_byte);
+    if ((lane & 3) == 0) {
+      uint8_t* dst = p.sf + (static_cast<int64_t>(atom_row) * atom_cols + (col >> 6)) * 512 +
+                     (r & 31) * 16 + (r >> 5) * 4;
+      *reinterpret_cast<uint32_t*>(dst) = word;
+    }
   }
 }
 
@@ -331,10 +357,11 @@ extern "C" int lm_quantize_decode(const void* x, int64_t tokens, int features, i
   LM_REQUIRE(features > 0 && features % 64 == 0, "quantize_decode: features must be a multiple of 64");
   LM_REQUIRE(top_k > 0 && tokens >= 0, "quantize_decode: bad sizes");
   if (tokens == 0) return LM_OK;
-  DecodeQuantParams p{static_cast<const __nv_bfloat16*>(x), tokens, features, top_k, slots,
-                      topk_ids, m_indptr, scale_pair, q, sf};
+  LM_REQUIRE(top_k <= 32, "quantize_decode: top_k must be at most 32");
+  ScatterQuantParams p{static_cast<const __nv_bfloat16*>(x), tokens, features, top_k, slots,
+                       topk_ids, m_indptr, scale_pair, q, sf};
   dim3 grid(static_cast<unsigned>((tokens + kWarps - 1) / kWarps), (features + kTileCols - 1) / kTileCols);
-  quantize_decode_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(p);
+  quantize_scatter_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(p);
   LM_CUDA(cudaGetLastError());
   return LM_OK;
 }

@@ -565,9 +565,10 @@ class InferenceMoE:
         output = self._output_view(out, tokens, "out")
         execution = self._full_execution(tokens, decode=False)
         self._dispatch(topk_ids, topk_weights, rows)
-        nvfp4_quantize_rowwise(x, self._m_indptr, self._x_scale, execution.qx, execution.sfx,
-                               gather_idx=self._gather[:rows],
-                               padded_offsets=self._padded_offsets, te_math=True)
+        # each token is quantized once and its codes and scale factors are written to all of
+        # its expert-major rows: same bits as quantizing the gathered rows, 1/top_k of the math
+        nvfp4_quantize_decode(x, topk_ids, self._slots[:rows], self._m_indptr,
+                              self._padded_offsets, self._x_scale, execution.qx, execution.sfx)
         execution.fc1.launch()
         execution.fc2.launch()
         moe_finalize(execution.routed_out, self._slots[:rows], output, self.topk, tile_t=1,
