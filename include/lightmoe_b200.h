@@ -138,6 +138,20 @@ int lm_dispatch(const int32_t* topk_ids, const float* topk_weights, int64_t toke
                 int plan_tile_rows, lm_stream_t stream);
 
 /*
+ * Decode step preparation in one launch: lm_dispatch followed by lm_quantize_decode for at
+ * most 1024 assignments.  Every CTA repeats the single-block dispatch in shared memory, so
+ * the launch has no inter-CTA dependency.
+ * Replaces nvfp4_dispatch_quantize_decode (lightmoe/kernels/quantize/decode.py:1168-1257).
+ * Arguments as in lm_dispatch and lm_quantize_decode; x is (tokens, features) BF16.
+ */
+int lm_dispatch_quantize_decode(const void* x, const int32_t* topk_ids, const float* topk_weights,
+                                int64_t tokens, int top_k, int experts, int features,
+                                int32_t* gather, int32_t* m_indptr, float* probs, int32_t* slots,
+                                int32_t* padded_offsets, int32_t* scratch, int64_t scratch_elems,
+                                int plan_tile_rows, const float* scale_pair, uint8_t* q, uint8_t* sf,
+                                lm_stream_t stream);
+
+/*
  * lm_dispatch for callers that have no device memory to give as scratch and
  * may not obtain any: a plugin inside a serving process whose memory pool
  * already owns the whole GPU, or a host runtime that forbids its extensions to
@@ -214,7 +228,7 @@ typedef struct lm_gemm_args {
 
 /* Caller-provided storage for a prepared GEMM (tensor maps + arguments). */
 typedef struct lm_gemm_plan {
-  uint64_t opaque[128];
+  uint64_t opaque[160];
 } lm_gemm_plan;
 
 /* Host only: validates `args` and encodes the TMA descriptors into `plan`. */

@@ -54,7 +54,7 @@ class GemmArgs(ctypes.Structure):
 
 
 class GemmPlan(ctypes.Structure):
-    _fields_ = [("opaque", ctypes.c_uint64 * 128)]
+    _fields_ = [("opaque", ctypes.c_uint64 * 160)]
 
 
 _SIGNATURES = {
@@ -75,6 +75,11 @@ _SIGNATURES = {
     "lm_dispatch": (
         c_i32,
         [c_ptr, c_ptr, c_i64, c_i32, c_i32, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i32, c_ptr],
+    ),
+    "lm_dispatch_quantize_decode": (
+        c_i32,
+        [c_ptr, c_ptr, c_ptr, c_i64, c_i32, c_i32, c_i32, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
+         c_i64, c_i32, c_ptr, c_ptr, c_ptr, c_ptr],
     ),
     "lm_dispatch_static_max_rows": (c_i64, []),
     "lm_dispatch_static": (

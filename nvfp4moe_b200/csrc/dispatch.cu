@@ -7,6 +7,7 @@
 //               gives each chunk its stable base (prefix over experts, then over
 //               earlier chunks) and scatters.
 #include "common.cuh"
+#include "quantize_math.cuh"
 
 namespace lm {
 namespace {
@@ -70,18 +71,18 @@ __device__ __forceinline__ int block_inclusive_scan(int v, int* s_warp) {
   return v + add;
 }
 
+// Places the pairs of one 1024-pair chunk.  s_seg [kSegments][experts], s_chunk [kChunk],
+// s_base [kMaxExperts] and s_warp [3][8] are shared-memory work areas; on return s_chunk
+// holds each pair's expert (-1 = dropped), s_base each expert's first row for this chunk
+// and, when s_slot is given, s_slot each pair's destination row (-1 = dropped).  Global
+// outputs are written only when write_global is set.
 template <bool kSingle>
-__global__ void __launch_bounds__(kThreads) dispatch_scatter_kernel(DispatchParams p) {
-  extern __shared__ int s_dyn[];
-  int* s_seg = s_dyn;                        // [kSegments][experts]
-  int* s_chunk = s_seg + kSegments * p.experts;  // [kChunk]
-  __shared__ int s_base[kMaxExperts];
-  __shared__ int s_warp[3][kThreads / 32];
-
+__device__ __forceinline__ void dispatch_chunk(const DispatchParams& p, int chunk, bool write_global,
+                                               int* s_seg, int* s_chunk, int* s_base,
+                                               int (*s_warp)[kThreads / 32], int* s_slot) {
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const int chunk = blockIdx.x;
   const int64_t chunk_base = static_cast<int64_t>(chunk) * kChunk;
   const int E = p.experts;
 
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(kThreads) dispatch_scatter_kernel(DispatchPara
   const int incl_tiles = block_inclusive_scan(tiles, s_warp[2]);
   if (tid < E) {
     s_base[tid] = incl_rows - total + before;
-    if (chunk == 0) {
+    if (chunk == 0 && write_global) {
       p.m_indptr[tid + 1] = incl_rows;
       p.padded[tid] = incl_pad;
       if (tid == 0) p.m_indptr[0] = 0;
@@ -154,12 +155,97 @@ __global__ void __launch_bounds__(kThreads) dispatch_scatter_kernel(DispatchPara
     int j = tid + i * kThreads;
     int64_t pos = chunk_base + j;
     int e = s_chunk[j];
-    if (pos < p.rows && e < 0) p.slots[pos] = -1;  // dropped pair: the combine skips it
-    if (pos < p.rows && e >= 0) {
-      int dst = s_base[e] + s_seg[(i * (kThreads / 32) + warp) * E + e] + rank[i];
+    int dst = -1;
+    if (pos < p.rows && e >= 0) dst = s_base[e] + s_seg[(i * (kThreads / 32) + warp) * E + e] + rank[i];
+    if (s_slot != nullptr) s_slot[j] = dst;
+    if (!write_global || pos >= p.rows) continue;
+    p.slots[pos] = dst;  // -1 for a dropped pair: the combine skips it
+    if (dst >= 0) {
       p.gather[dst] = static_cast<int32_t>(pos / p.top_k);
       p.probs[dst] = __ldg(p.weights + pos);
-      p.slots[pos] = dst;
+    }
+  }
+}
+
+template <bool kSingle>
+__global__ void __launch_bounds__(kThreads) dispatch_scatter_kernel(DispatchParams p) {
+  extern __shared__ int s_dyn[];
+  int* s_seg = s_dyn;                            // [kSegments][experts]
+  int* s_chunk = s_seg + kSegments * p.experts;  // [kChunk]
+  __shared__ int s_base[kMaxExperts];
+  __shared__ int s_warp[3][kThreads / 32];
+  dispatch_chunk<kSingle>(p, blockIdx.x, true, s_seg, s_chunk, s_base, s_warp, nullptr);
+}
+
+// ------------------------------------------------ decode: dispatch + quantize, one launch
+// For at most 1024 pairs.  Every CTA repeats the (tiny) single-chunk dispatch in its own
+// shared memory, so no CTA waits for another; CTA (0,0) alone writes the routing outputs.
+// Then each warp quantizes one (token, 512-feature slice) once and writes codes and scale
+// factors to all of the token's rows, as the stand-alone quantize-scatter kernel does.
+struct DecodePrepareParams {
+  DispatchParams d;
+  const __nv_bfloat16* x;
+  int features;
+  const float* scale_pair;
+  uint8_t* q;
+  uint8_t* sf;
+};
+
+__global__ void __launch_bounds__(kThreads) dispatch_quantize_decode_kernel(DecodePrepareParams p) {
+  extern __shared__ int s_dyn[];
+  const int E = p.d.experts;
+  int* s_seg = s_dyn;
+  int* s_chunk = s_seg + kSegments * E;
+  int* s_slot = s_chunk + kChunk;
+  __shared__ int s_base[kMaxExperts];
+  __shared__ int s_warp[3][kThreads / 32];
+  dispatch_chunk<true>(p.d, 0, blockIdx.x == 0 && blockIdx.y == 0, s_seg, s_chunk, s_base, s_warp, s_slot);
+  __syncthreads();
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int top_k = p.d.top_k;
+  const int64_t tokens = p.d.rows / top_k;
+  const int64_t token = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + warp;
+  if (token >= tokens) return;
+  const int col = blockIdx.y * 512 + lane * 16;
+  const bool col_ok = col < p.features;
+  int my_slot = -1, my_atom_row = 0, my_r = 0;
+  if (lane < top_k) {
+    const int pair = static_cast<int>(token) * top_k + lane;
+    my_slot = s_slot[pair];
+    if (my_slot >= 0) {
+      const int e = s_chunk[pair];
+      const int lo = s_base[e];
+      const int local = my_slot - lo;
+      my_atom_row = lo / 128 + e + local / 128;
+      my_r = local % 128;
+    }
+  }
+  const float pts = __ldg(p.scale_pair);
+  const float inv_pts = __ldg(p.scale_pair + 1);
+  Slice<__nv_bfloat16> v;
+  uint2 packed = make_uint2(0, 0);
+  uint32_t sf_byte = 0;
+  if (col_ok) {
+    v.load(p.x + token * p.features + col);
+    sf_byte = quantize_group(v, pts, inv_pts, true, &packed);
+  }
+  uint32_t word = sf_byte;
+  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 1) << 8;
+  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 2) << 16;
+  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 3) << 24;
+  const int atom_cols = p.features >> 6;
+  for (int j = 0; j < top_k; ++j) {
+    const int slot = __shfl_sync(0xFFFFFFFFu, my_slot, j);
+    const int atom_row = __shfl_sync(0xFFFFFFFFu, my_atom_row, j);
+    const int r = __shfl_sync(0xFFFFFFFFu, my_r, j);
+    if (slot < 0 || !col_ok) continue;
+    *reinterpret_cast<uint2*>(p.q + static_cast<int64_t>(slot) * (p.features >> 1) + (col >> 1)) = packed;
+    if ((lane & 3) == 0) {
+      uint8_t* dst = p.sf + (static_cast<int64_t>(atom_row) * atom_cols + (col >> 6)) * 512 +
+                     (r & 31) * 16 + (r >> 5) * 4;
+      *reinterpret_cast<uint32_t*>(dst) = word;
     }
   }
 }
@@ -269,6 +355,42 @@ extern "C" int lm_dispatch_static(const int32_t* topk_ids, const float* topk_wei
     LM_CUDA(cudaGetLastError());
     dispatch_scatter_kernel<false><<<chunks, kThreads, smem, s>>>(p);
   }
+  LM_CUDA(cudaGetLastError());
+  return LM_OK;
+}
+
+extern "C" int lm_dispatch_quantize_decode(const void* x, const int32_t* topk_ids,
+                                           const float* topk_weights, int64_t tokens, int top_k,
+                                           int experts, int features, int32_t* gather,
+                                           int32_t* m_indptr, float* probs, int32_t* slots,
+                                           int32_t* padded_offsets, int32_t* scratch,
+                                           int64_t scratch_elems, int plan_tile_rows,
+                                           const float* scale_pair, uint8_t* q, uint8_t* sf,
+                                           lm_stream_t stream) {
+  using namespace lm;
+  LM_REQUIRE(x && topk_ids && topk_weights && gather && m_indptr && probs && slots && padded_offsets &&
+                 scratch && scale_pair && q && sf,
+             "dispatch_quantize_decode: null pointer");
+  LM_REQUIRE(experts > 0 && experts <= kMaxExperts, "dispatch_quantize_decode: at most 256 experts");
+  LM_REQUIRE(top_k > 0 && top_k <= 32 && tokens > 0, "dispatch_quantize_decode: bad routing sizes");
+  LM_REQUIRE(features > 0 && features % 64 == 0, "dispatch_quantize_decode: features must be a multiple of 64");
+  LM_REQUIRE(plan_tile_rows > 0 && 128 % plan_tile_rows == 0,
+             "dispatch_quantize_decode: plan_tile_rows must divide 128");
+  const int64_t rows = tokens * top_k;
+  if (rows > kChunk) return set_error(LM_ERR_LIMIT, "dispatch_quantize_decode: at most 1024 assignments");
+  int64_t plan_need = 1 + (rows + plan_tile_rows - 1) / plan_tile_rows + experts + experts;
+  LM_REQUIRE(scratch_elems >= plan_need, "dispatch_quantize_decode: scratch too small for the decode plan");
+  DecodePrepareParams p{};
+  p.d = DispatchParams{topk_ids, topk_weights, rows,    top_k,         experts,        gather, m_indptr,
+                       probs,    slots,        padded_offsets, scratch, scratch_elems, plan_tile_rows, 1};
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.features = features;
+  p.scale_pair = scale_pair;
+  p.q = q;
+  p.sf = sf;
+  const size_t smem = sizeof(int) * (static_cast<size_t>(kSegments) * experts + 2 * kChunk);
+  dim3 grid(static_cast<unsigned>((tokens + kThreads / 32 - 1) / (kThreads / 32)), (features + 511) / 512);
+  dispatch_quantize_decode_kernel<<<grid, kThreads, smem, as_stream(stream)>>>(p);
   LM_CUDA(cudaGetLastError());
   return LM_OK;
 }

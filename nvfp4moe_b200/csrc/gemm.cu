@@ -379,7 +379,8 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // ------------------------------------------------------------------ kernel
 template <int kOut, int kAct>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64,
+            const __grid_constant__ CUtensorMap tmap_a32, const __grid_constant__ CUtensorMap tmap_b,
             const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -482,6 +483,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const Unit u = decode_unit(p, unit);
       const RowTile t = walker.at(misc, p, u.mt);
       const uint8_t* sfa_src = p.sfa + static_cast<int64_t>(t.sf_row) * p.atom_cols * 512;
+      // A row tile with few valid rows (decode, expert tails) is fetched with a shorter TMA
+      // box; the rest of the 128-row operand keeps stale bytes whose products are never stored
+      const CUtensorMap* a_map = t.valid <= 32 ? &tmap_a32 : (t.valid <= 64 ? &tmap_a64 : &tmap_a);
+      const uint32_t a_bytes = (t.valid <= 32 ? 32 : (t.valid <= 64 ? 64 : 128)) * kStageKBytes;
       for (int nt = u.n_begin; nt < u.n_end && ok; ++nt) {
         const int b_row = t.expert * p.n + nt * kTileN;
         const uint8_t* sfb_src =
@@ -498,8 +503,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             if (elect_one()) {
               const uint32_t bar = smem_u32(&misc->a_full[ks]);
               const uint32_t dst = smem_base + ks * kSlotBytes;
-              mbar_expect_tx(bar, kTileBytes + sf_bytes);
-              tma_load_2d(dst, &tmap_a, ks * kStageKBytes, t.row0, bar);
+              mbar_expect_tx(bar, a_bytes + sf_bytes);
+              tma_load_2d(dst, a_map, ks * kStageKBytes, t.row0, bar);
               bulk_load(dst + kTileBytes, sfa_src + static_cast<int64_t>(ks) * kSfBytes, sf_bytes, bar);
             }
             __syncwarp();
@@ -511,11 +516,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (elect_one()) {
             const uint32_t bar = smem_u32(&misc->full[stage]);
             const uint32_t dst = ring_base + stage * ring_stride;
-            mbar_expect_tx(bar, (kTileBytes + sf_bytes) * (resident ? 1 : 2));
+            mbar_expect_tx(bar, kTileBytes + sf_bytes + (resident ? 0u : a_bytes + sf_bytes));
             tma_load_2d(dst, &tmap_b, ks * kStageKBytes, b_row, bar);
             bulk_load(dst + kTileBytes, sfb_src + static_cast<int64_t>(ks) * kSfBytes, sf_bytes, bar);
             if (!resident) {
-              tma_load_2d(dst + kSlotBytes, &tmap_a, ks * kStageKBytes, t.row0, bar);
+              tma_load_2d(dst + kSlotBytes, a_map, ks * kStageKBytes, t.row0, bar);
               bulk_load(dst + kSlotBytes + kTileBytes, sfa_src + static_cast<int64_t>(ks) * kSfBytes,
                         sf_bytes, bar);
             }
@@ -828,6 +833,8 @@ struct PlanData {
   int32_t grid;
   GemmParams params;
   alignas(64) CUtensorMap map_a;
+  alignas(64) CUtensorMap map_a64;
+  alignas(64) CUtensorMap map_a32;
   alignas(64) CUtensorMap map_b;
 };
 static_assert(sizeof(PlanData) <= sizeof(lm_gemm_plan), "plan storage too small");
@@ -873,7 +880,8 @@ int launch_variant(const PlanData& pd, cudaStream_t stream) {
     LM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(kOut)));
     configured = true;
   }
-  kernel<<<pd.grid, kThreads, smem_bytes(kOut), stream>>>(pd.map_a, pd.map_b, pd.params);
+  kernel<<<pd.grid, kThreads, smem_bytes(kOut), stream>>>(pd.map_a, pd.map_a64, pd.map_a32, pd.map_b,
+                                                          pd.params);
   LM_CUDA(cudaGetLastError());
   return LM_OK;
 }
@@ -977,6 +985,10 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   const int64_t max_units = ((a->rows + kTileM - 1) / kTileM + a->experts) * p.units_per_mtile;
   if (pd.grid > max_units) pd.grid = static_cast<int>(max_units);
   int rc = encode_bytes_2d(&pd.map_a, a->a, static_cast<uint64_t>(a->k / 2), static_cast<uint64_t>(a->rows), kTileM);
+  if (rc != LM_OK) return rc;
+  rc = encode_bytes_2d(&pd.map_a64, a->a, static_cast<uint64_t>(a->k / 2), static_cast<uint64_t>(a->rows), 64);
+  if (rc != LM_OK) return rc;
+  rc = encode_bytes_2d(&pd.map_a32, a->a, static_cast<uint64_t>(a->k / 2), static_cast<uint64_t>(a->rows), 32);
   if (rc != LM_OK) return rc;
   rc = encode_bytes_2d(&pd.map_b, a->b, static_cast<uint64_t>(a->k / 2),
                        static_cast<uint64_t>(a->experts) * a->n, kTileN);

@@ -21,7 +21,7 @@ import torch
 from ._quantization import _DEN, quantize_expert_stack
 from .kernels.gated import GatedEpilogue
 from .kernels.grouped.runtime import GroupedNvfp4Gemm
-from .kernels.quantize.decode import nvfp4_quantize_decode
+from .kernels.quantize.decode import nvfp4_dispatch_quantize_decode, nvfp4_quantize_decode
 from .kernels.quantize.runtime import nvfp4_quantize_rowwise
 from .kernels.routing.combine import moe_finalize
 from .kernels.routing.dispatch import MAX_ASSIGNMENTS, moe_dispatch, scratch_elems
@@ -583,9 +583,16 @@ class InferenceMoE:
         rows = tokens * self.topk
         output = self._output_view(out, tokens, "out")
         execution = self._full_execution(tokens, decode=True)
-        self._dispatch(topk_ids, topk_weights, rows)
-        nvfp4_quantize_decode(x, topk_ids, self._slots[:rows], self._m_indptr,
-                              self._padded_offsets, self._x_scale, execution.qx, execution.sfx)
+        if rows <= 1024:
+            # one launch: dispatch + decode plan + quantize-once-and-scatter
+            nvfp4_dispatch_quantize_decode(x, topk_ids, topk_weights, self._parts,
+                                           self._gather[:rows], self._m_indptr, self._probs[:rows],
+                                           self._slots[:rows], self._padded_offsets, self._x_scale,
+                                           execution.qx, execution.sfx)
+        else:
+            self._dispatch(topk_ids, topk_weights, rows)
+            nvfp4_quantize_decode(x, topk_ids, self._slots[:rows], self._m_indptr,
+                                  self._padded_offsets, self._x_scale, execution.qx, execution.sfx)
         execution.fc1.launch()
         execution.fc2.launch()
         moe_finalize(execution.routed_out, self._slots[:rows], output, self.topk, tile_t=1,

@@ -400,3 +400,46 @@ def test_fused_epilogue_matches_oracle(activation, clamp):
     deq = O.dequantize_rows(q_got, sf_got, h_pts)
     deq_ref = O.dequantize_rows(q_ref, sf_ref, h_pts)
     assert O.rel_frobenius(deq, deq_ref) <= 2e-2
+
+
+# --------------------------------------------------------------------------
+# decode preparation: dispatch + plan + quantize in one launch
+# --------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize(("tokens", "experts", "k", "features"),
+                         ((1, 8, 2, 256), (17, 64, 4, 2048), (64, 256, 8, 6144), (128, 32, 8, 512)))
+def test_fused_decode_prepare_matches_oracle(tokens, experts, k, features):
+    from nvfp4moe_b200.kernels.quantize import nvfp4_dispatch_quantize_decode
+    from nvfp4moe_b200.kernels.routing.dispatch import scratch_elems
+
+    ids, w = _route(tokens, experts, k, "hot", tokens)
+    g = torch.Generator().manual_seed(tokens)
+    x = torch.randn(tokens, features, generator=g).to(torch.bfloat16)
+    rows = tokens * k
+    n = scratch_elems(rows, experts)
+    ref = O.dispatch(ids, w, experts, 8, n)
+    pts = O.tensor_scale(x)
+    q_ref, sf_ref = O.quantize_rows(x[ref[0].long()], pts, te_math=True)
+    tiles = -(-rows // 128) + experts
+    dev = "cuda"
+    gi = torch.empty(rows, dtype=torch.int32, device=dev)
+    cu = torch.empty(experts + 1, dtype=torch.int32, device=dev)
+    ps = torch.empty(rows, dtype=torch.float32, device=dev)
+    slots = torch.empty(rows, dtype=torch.int32, device=dev)
+    part = torch.zeros(n, dtype=torch.int32, device=dev)
+    off = torch.empty(experts, dtype=torch.int32, device=dev)
+    q = torch.empty(rows, features // 2, dtype=torch.uint8, device=dev)
+    sf = torch.full((1, tiles, features // 64, 32, 4, 4), 0x7F, dtype=torch.uint8, device=dev)
+    pair = torch.cat((pts, 1.0 / pts)).cuda()
+    nvfp4_dispatch_quantize_decode(x.cuda(), ids.cuda(), w.cuda(), part, gi, cu, ps, slots, off,
+                                   pair, q, sf, plan_tile_rows=8)
+    torch.cuda.synchronize()
+    for got, want in zip((gi, cu, ps, slots, off), ref[:5]):
+        assert torch.equal(got.cpu(), want)
+    plan = part.cpu()
+    count = int(ref[5][0])
+    assert torch.equal(plan[: 1 + count], ref[5][: 1 + count])
+    assert torch.equal(plan[-experts:], ref[5][-experts:])
+    assert torch.equal(q.cpu(), q_ref)
+    assert torch.equal(O.sf_from_varlen(sf.cpu(), ref[1], features // 16), sf_ref)
