@@ -1,0 +1,143 @@
+"""Latency of the MoE layer and its two grouped GEMMs on the named workloads.
+
+    python -m nvfp4moe_b200.bench_configs [name ...]
+
+Prints one JSON line per workload: median [IQR] of 21 CUDA-event samples after
+warm-up (the reference's protocol, BENCHMARKS.md:19-25), layer tokens/s, and
+grouped-GEMM TFLOP/s counted as 2 * rows * N * K without tile padding.  Decode
+workloads are timed as CUDA Graph replays.  Inputs are seeded synthetic draws:
+activations N(0,1), router logits N(0,1) -> softmax -> top-k -> renormalise,
+weights N(0,0.02) packed to NVFP4 on the GPU; the Zipf workload skews expert
+popularity with exponent 1.2 over a seeded permutation of the experts.
+"""
+
+from __future__ import annotations
+
+import json
+import statistics
+import sys
+
+import torch
+
+from nvfp4moe_b200 import InferenceMoE
+
+# name: (hidden, intermediate, experts, top_k, tokens, activation, clamp, routing, graph)
+WORKLOADS = {
+    "c2": (2048, 512, 256, 8, 8192, "swiglu", None, "uniform", False),
+    "c3_8192": (4096, 2048, 256, 6, 8192, "swiglu", 10.0, "uniform", False),
+    "c3_32768": (4096, 2048, 256, 6, 32768, "swiglu", 10.0, "uniform", False),
+    "c5_zipf": (6144, 3072, 128, 4, 16384, "swiglu_oai", None, "zipf", False),
+    "c4_decode_1": (6144, 2048, 256, 8, 1, "swiglu", None, "uniform", True),
+    "c4_decode_8": (6144, 2048, 256, 8, 8, "swiglu", None, "uniform", True),
+    "c4_decode_32": (6144, 2048, 256, 8, 32, "swiglu", None, "uniform", True),
+    "c4_decode_64": (6144, 2048, 256, 8, 64, "swiglu", None, "uniform", True),
+    # local expert-parallel shards the reference publishes (BENCHMARKS.md:92-97), 8192 tokens
+    "shard_qwen35_35b": (2048, 512, 16, 8, 8192, "swiglu", None, "uniform", False),
+    "shard_deepseek_v4_flash": (4096, 2048, 8, 6, 8192, "swiglu", 10.0, "uniform", False),
+    "shard_glm_5_2": (6144, 2048, 16, 8, 8192, "swiglu", None, "uniform", False),
+    "shard_minimax_m3": (6144, 3072, 8, 4, 8192, "swiglu_oai", None, "uniform", False),
+}
+
+
+def _routing(tokens, experts, k, kind, device):
+    g = torch.Generator(device=device).manual_seed(0)
+    if kind == "zipf":
+        perm = torch.randperm(experts, generator=g, device=device)
+        popularity = torch.empty(experts, device=device)
+        popularity[perm] = torch.arange(1, experts + 1, device=device, dtype=torch.float32) ** -1.2
+        # the 20 least popular experts receive nothing, as in the imbalanced-routing workload
+        popularity[perm[experts - 20:]] = 0.0
+        popularity /= popularity.sum()
+        # sampling without replacement by exponential keys: the k smallest of -log(U) / p
+        keys = -torch.log(torch.rand(tokens, experts, generator=g, device=device)) / popularity
+        ids = keys.topk(k, dim=1, largest=False).indices
+        weights = torch.rand(tokens, k, generator=g, device=device) + 0.1
+    else:
+        logits = torch.randn(tokens, experts, generator=g, device=device)
+        weights, ids = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+    weights = (weights / weights.sum(-1, keepdim=True)).float().contiguous()
+    return ids.to(torch.int32).contiguous(), weights
+
+
+def _samples(fn, count=21, warmup=5):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(count):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        stop.record()
+        stop.synchronize()
+        out.append(start.elapsed_time(stop) * 1e3)
+    return out
+
+
+def _stats(samples):
+    q = statistics.quantiles(samples, n=4)
+    return {"median_us": round(statistics.median(samples), 2), "iqr_us": round(q[2] - q[0], 2),
+            "min_us": round(min(samples), 2)}
+
+
+def run(name: str) -> dict:
+    hidden, inter, experts, k, tokens, act, clamp, routing, graph = WORKLOADS[name]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(1)
+    unary = act == "relu2"
+    plan = InferenceMoE(hidden, inter, experts, k, tokens, activation=act, activation_clamp=clamp,
+                        device=dev)
+    first = (torch.randn(experts, inter, hidden, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    down = (torch.randn(experts, hidden, inter, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    if unary:
+        plan.load_weights(first, down)
+    else:
+        second = (torch.randn(experts, inter, hidden, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        plan.load_weights(first, second, down)
+        del second
+    del first, down
+    torch.cuda.empty_cache()
+    x = torch.randn(tokens, hidden, generator=g, device=dev).to(torch.bfloat16)
+    ids, w = _routing(tokens, experts, k, routing, dev)
+    plan.calibrate(x, ids, w)
+    rows = tokens * k
+    counts = torch.bincount(ids.flatten().long(), minlength=experts)
+    result = {"workload": name, "hidden": hidden, "intermediate": inter, "experts": experts, "top_k": k,
+              "tokens": tokens, "rows": rows, "activation": act, "routing": routing,
+              "empty_experts": int((counts == 0).sum()), "max_expert_share": round(float(counts.max()) / rows, 4)}
+    plan.run(x, ids, w)
+    torch.cuda.synchronize()
+    if graph:
+        cuda_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cuda_graph):
+            plan.run(x, ids, w)
+        layer = _samples(cuda_graph.replay)
+        result["timed_as"] = "cuda graph replay"
+    else:
+        layer = _samples(lambda: plan.run(x, ids, w))
+        result["timed_as"] = "stream launches"
+    result["layer"] = _stats(layer)
+    result["tokens_per_s"] = round(tokens / (result["layer"]["median_us"] * 1e-6))
+    decode = rows <= 16 * experts
+    ex = plan._full_execution(tokens, decode=decode)
+    n1 = inter if unary else 2 * inter
+    for label, gemm, n, kk in (("fc1", ex.fc1, n1, hidden), ("fc2", ex.fc2, hidden, inter)):
+        stats = _stats(_samples(gemm.launch))
+        stats["tflops"] = round(2.0 * rows * n * kk / (stats["median_us"] * 1e-6) / 1e12, 1)
+        stats["pct_of_9000"] = round(stats["tflops"] / 90.0, 1)
+        result[label] = stats
+    from nvfp4moe_b200 import _lib
+
+    result["device_status"] = _lib.device_status()
+    return result
+
+
+def main(argv):
+    names = argv or list(WORKLOADS)
+    for name in names:
+        print(json.dumps(run(name)), flush=True)
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])

@@ -61,6 +61,11 @@ constexpr int kStoreBytes = kEpilogueWarps * kStoreBytesPerWarp;
 constexpr int kMiscBytes = 4096;
 constexpr int kSmemLimit = 232448;
 constexpr uint32_t kSfCol = 2 * kTileN;  // TMEM: two accumulators, then 32 columns per ring stage
+// TMEM with 256-column tiles: accumulator 0 at [0, 256), accumulator 1 at [160, 416), two
+// scale-factor slots of 48 columns from 416.  The accumulators share columns [160, 256).
+constexpr uint32_t kWideAcc1Col = 160;
+constexpr uint32_t kWideSfCol = 416;
+constexpr uint32_t kWideSfSlotCols = 48;
 static_assert(kSlotBytes % 1024 == 0, "operand slots must keep 1024-byte alignment");
 static_assert(kSfCol + kMaxRing * 32 <= kTmemCols, "TMEM budget");
 
@@ -252,6 +257,15 @@ __device__ __forceinline__ void tc_store32(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+__device__ __forceinline__ void tc_store16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -283,6 +297,7 @@ struct Misc {  // lives after the operand slots and the store staging
   uint64_t a_empty[kMaxResident];  // resident A stage no longer read
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t shared_cols_free;       // 256-column tiles: the columns both accumulators use are read out
   uint32_t tmem_base;
   int abort_flag;
   int total_m_tiles;
@@ -377,7 +392,16 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 // ------------------------------------------------------------------ kernel
-template <int kOut, int kAct>
+// kNB = 128-column blocks per tile.
+// 1: 128 x 128 tiles, two accumulators of 128 TMEM columns, one scale-factor slot per ring
+//    stage; epilogue group g drains accumulator g (every other tile).
+// 2: 128 x 256 tiles, which move a quarter less data through shared memory per FLOP (the
+//    resource that binds the main loop).  Two 256-column accumulators and the scale factors
+//    do not fit in 512 TMEM columns side by side, so the accumulators overlap in 96 columns:
+//    both epilogue groups work on every tile, read the 64-column slices that touch the
+//    overlap first and signal `shared_cols_free`; the MMAs of the next tile start then, while
+//    the rest of the tile is still being converted and stored.
+template <int kOut, int kAct, int kNB>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64,
             const __grid_constant__ CUtensorMap tmap_a32, const __grid_constant__ CUtensorMap tmap_b,
@@ -392,9 +416,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   volatile int* abort_flag = &misc->abort_flag;
 
   // operand slots: [resident A stages][ring stages]; a ring stage is B (+ A when streaming)
-  const bool resident = p.a_resident != 0;
+  const bool resident = kNB == 1 && p.a_resident != 0;
+  // ring stage: [B tile(s)][B scale factors][A tile][A scale factors]
   const uint32_t ring_base = smem_base + (resident ? p.k_stages * kSlotBytes : 0);
-  const uint32_t ring_stride = resident ? kSlotBytes : 2 * kSlotBytes;
+  const uint32_t ring_stride = (resident ? kNB : kNB + 1) * kSlotBytes;
+  constexpr uint32_t kSfbOffset = kNB * kTileBytes;   // within a ring stage
+  constexpr uint32_t kAOffset = kNB * kSlotBytes;     // streaming only
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -412,8 +439,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&misc->acc_full[s]), 1);
-      mbar_init(smem_u32(&misc->acc_empty[s]), 4);
+      mbar_init(smem_u32(&misc->acc_empty[s]), kNB == 1 ? 4 : 8);
     }
+    mbar_init(smem_u32(&misc->shared_cols_free), 8);
     misc->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -488,9 +516,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const CUtensorMap* a_map = t.valid <= 32 ? &tmap_a32 : (t.valid <= 64 ? &tmap_a64 : &tmap_a);
       const uint32_t a_bytes = (t.valid <= 32 ? 32 : (t.valid <= 64 ? 64 : 128)) * kStageKBytes;
       for (int nt = u.n_begin; nt < u.n_end && ok; ++nt) {
-        const int b_row = t.expert * p.n + nt * kTileN;
+        const int b_row = t.expert * p.n + nt * kNB * kTileN;
         const uint8_t* sfb_src =
-            p.sfb + static_cast<int64_t>(t.expert * p.sfb_atom_rows + nt) * p.atom_cols * 512;
+            p.sfb + static_cast<int64_t>(t.expert * p.sfb_atom_rows + nt * kNB) * p.atom_cols * 512;
+        // column blocks of this tile that exist (N need not be a multiple of the tile width)
+        const int b_blocks = min(kNB, p.sfb_atom_rows - nt * kNB);
         for (int ks = 0; ks < p.k_stages; ++ks) {
           const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
           const uint32_t sf_bytes = chunks * 512;
@@ -516,12 +546,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (elect_one()) {
             const uint32_t bar = smem_u32(&misc->full[stage]);
             const uint32_t dst = ring_base + stage * ring_stride;
-            mbar_expect_tx(bar, kTileBytes + sf_bytes + (resident ? 0u : a_bytes + sf_bytes));
+            mbar_expect_tx(bar, kNB * kTileBytes + b_blocks * sf_bytes + (resident ? 0u : a_bytes + sf_bytes));
             tma_load_2d(dst, &tmap_b, ks * kStageKBytes, b_row, bar);
-            bulk_load(dst + kTileBytes, sfb_src + static_cast<int64_t>(ks) * kSfBytes, sf_bytes, bar);
+            for (int j = 0; j < b_blocks; ++j)
+              bulk_load(dst + kSfbOffset + j * kSfBytes,
+                        sfb_src + (static_cast<int64_t>(j) * p.atom_cols + ks * kChunksPerStage) * 512,
+                        sf_bytes, bar);
             if (!resident) {
-              tma_load_2d(dst + kSlotBytes, a_map, ks * kStageKBytes, t.row0, bar);
-              bulk_load(dst + kSlotBytes + kTileBytes, sfa_src + static_cast<int64_t>(ks) * kSfBytes,
+              tma_load_2d(dst + kAOffset, a_map, ks * kStageKBytes, t.row0, bar);
+              bulk_load(dst + kAOffset + kTileBytes, sfa_src + static_cast<int64_t>(ks) * kSfBytes,
                         sf_bytes, bar);
             }
           }
@@ -535,10 +568,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else if (warp == 1) {
     // ===================================================== MMA issuer
 #ifdef LM_GEMM_PROFILE
-    const uint32_t idesc = (p.debug_flags >> 8) ? make_idesc(p.debug_flags >> 8) : make_idesc(kTileN);
+    const uint32_t idesc = (p.debug_flags >> 8) ? make_idesc(p.debug_flags >> 8) : make_idesc(kNB * kTileN);
 #else
-    constexpr uint32_t idesc = make_idesc(kTileN);
+    constexpr uint32_t idesc = make_idesc(kNB * kTileN);
 #endif
+    uint32_t sf_slot = 0;  // 256-column tiles: scale-factor slot, alternates per stage
     int stage = 0;
     uint32_t phase = 0;
     uint32_t a_phase = 0;
@@ -554,9 +588,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         LM_PROF_BEGIN();
         ok = mbar_wait(smem_u32(&misc->acc_empty[acc]), ((it >> 1) & 1u) ^ 1u, abort_flag, kStatusMmaTimeout);
         LM_PROF_END(prof_acc1);
+        if (ok && kNB == 2 && it > 0)  // the previous tile's accumulator overlaps this one
+          ok = mbar_wait(smem_u32(&misc->shared_cols_free), (it - 1) & 1u, abort_flag, kStatusMmaTimeout);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * kTileN;
+        const uint32_t d_tmem = tmem_base + acc * (kNB == 1 ? kTileN : kWideAcc1Col);
         for (int ks = 0; ks < p.k_stages; ++ks) {
           LM_PROF_BEGIN();
           ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusMmaTimeout);
@@ -570,9 +606,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           LM_PROF_BEGIN();
           const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
           const uint32_t b_smem = ring_base + stage * ring_stride;
-          const uint32_t a_smem = resident ? smem_base + ks * kSlotBytes : b_smem + kSlotBytes;
-          const uint32_t sfa_t = tmem_base + kSfCol + stage * 32;
+          const uint32_t a_smem = resident ? smem_base + ks * kSlotBytes : b_smem + kAOffset;
+          const uint32_t sfa_t =
+              tmem_base + (kNB == 1 ? kSfCol + stage * 32 : kWideSfCol + sf_slot * kWideSfSlotCols);
           const uint32_t sfb_t = sfa_t + 16;
+          sf_slot ^= 1u;
           const uint64_t a_desc = desc_sw128(a_smem);
           const uint64_t b_desc = desc_sw128(b_smem);
           if (elect_one()) {
@@ -581,7 +619,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #endif
             for (int c = 0; c < chunks; ++c) {
               // 64 FP4 values = 32 bytes along K: +2 in 16-byte descriptor units
-              tc_mma_nvf4(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 4,
+              tc_mma_nvf4(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 4 * kNB,
                           (ks > 0 || c > 0) ? 1u : 0u);
             }
             tc_commit(smem_u32(&misc->empty[stage]));
@@ -606,13 +644,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   } else if (warp >= kFirstSfWarp && warp < kFirstSfWarp + 4) {
     // ===================================================== scale factors -> TMEM
-    // Lane l of every quarter needs the same 32 words per stage: for each of the four
-    // 64-element chunks, the 16 bytes at (chunk * 512 + l * 16) of the A atoms (factors of
-    // rows l, l+32, l+64, l+96) and the same for the B atoms.
+    // Lane l of every quarter needs the same words per stage: for each of the four 64-element
+    // chunks, the 16 bytes at (chunk * 512 + l * 16) of the A atoms (factors of rows l, l+32,
+    // l+64, l+96) and the same for the B atoms of every 128-column block.
     const int quarter = warp & 3;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     int stage = 0;
     uint32_t phase = 0;
     uint32_t a_phase = 0;
+    // 256-column tiles keep two TMEM slots: the slot of stage iteration j was last read by
+    // the MMAs of iteration j - 2, whose completion the ring's `empty` barrier reports.
+    uint32_t sf_slot = 0;
+    int prev_stage[2] = {-1, -1};
+    uint32_t prev_phase[2] = {0, 0};
     bool ok = true;
     for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
       const Unit u = decode_unit(p, unit);
@@ -621,23 +665,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusSfTimeout);
           if (ok && resident && nt == u.n_begin)
             ok = mbar_wait(smem_u32(&misc->a_full[ks]), a_phase, abort_flag, kStatusSfTimeout);
+          if (kNB == 2) {
+            if (ok && prev_stage[0] >= 0)
+              ok = mbar_wait(smem_u32(&misc->empty[prev_stage[0]]), prev_phase[0], abort_flag, kStatusSfTimeout);
+            prev_stage[0] = prev_stage[1];
+            prev_phase[0] = prev_phase[1];
+            prev_stage[1] = stage;
+            prev_phase[1] = phase;
+          }
           if (!ok) break;
           const uint32_t b_smem = ring_base + stage * ring_stride;
-          const uint32_t a_smem = resident ? smem_base + ks * kSlotBytes : b_smem + kSlotBytes;
+          const uint32_t a_smem = resident ? smem_base + ks * kSlotBytes : b_smem + kAOffset;
           const uint32_t sfa_src = a_smem + kTileBytes + lane * 16;
-          const uint32_t sfb_src = b_smem + kTileBytes + lane * 16;
-          uint32_t w[32];
+          const uint32_t sfb_src = b_smem + kSfbOffset + lane * 16;
+          uint32_t w[16 + 16 * kNB];
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                          : "=r"(w[4 * c]), "=r"(w[4 * c + 1]), "=r"(w[4 * c + 2]), "=r"(w[4 * c + 3])
                          : "r"(sfa_src + c * 512));
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(w[16 + 4 * c]), "=r"(w[17 + 4 * c]), "=r"(w[18 + 4 * c]), "=r"(w[19 + 4 * c])
-                         : "r"(sfb_src + c * 512));
+#pragma unroll
+            for (int j = 0; j < kNB; ++j) {
+              const int o = 16 + 4 * (c * kNB + j);
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(w[o]), "=r"(w[o + 1]), "=r"(w[o + 2]), "=r"(w[o + 3])
+                           : "r"(sfb_src + j * kSfBytes + c * 512));
+            }
           }
-          const uint32_t dst = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kSfCol + stage * 32;
-          tc_store32(dst, w);
+          if (kNB == 1) {
+            tc_store32(lane_base + kSfCol + stage * 32, w);
+          } else {
+            const uint32_t dst = lane_base + kWideSfCol + sf_slot * kWideSfSlotCols;
+            tc_store32(dst, w);
+            tc_store16(dst + 32, w + 32);
+            sf_slot ^= 1u;
+          }
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
           tc_fence_before();
           __syncwarp();
@@ -649,14 +711,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   } else if (warp >= kFirstEpilogueWarp) {
     // ===================================================== epilogue
-    // Two groups of four warps; group g drains accumulator stage g, i.e. every other tile.
+    // Two groups of four warps.  The unit of work is a 64-column slice of an accumulator:
+    // 128-column tiles: group g drains accumulator g (every other tile), slices 0 and 1;
+    // 256-column tiles: both groups work on every tile, group g on slices g and g + 2, and
+    // take the slice that touches the columns shared with the other accumulator first.
     const int group = (warp - kFirstEpilogueWarp) >> 2;
     const int quarter = warp & 3;           // TMEM lanes this warp may read
     const int r = quarter * 32 + lane;      // row of the tile
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const uint32_t warp_store = store_base + (warp - kFirstEpilogueWarp) * kStoreBytesPerWarp;
     (void)warp_store;
     TileWalker walker;
-    uint32_t acc_phase = 0;
     int it = 0;
     bool ok = true;
     LM_PROF_DECL;
@@ -669,103 +734,107 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const bool row_ok = r < t.valid;
       const int64_t out_row = static_cast<int64_t>(t.row0) + r;
       for (int nt = u.n_begin; nt < u.n_end; ++nt, ++it) {
-        if ((it & 1) != group) continue;
+        if (kNB == 1 && (it & 1) != group) continue;
+        const int acc = it & 1;
         LM_PROF_END(prof_acc1);  // busy since the previous wait ended
         LM_PROF_BEGIN();
-        ok = mbar_wait(smem_u32(&misc->acc_full[group]), acc_phase, abort_flag, kStatusEpilogueTimeout);
+        ok = mbar_wait(smem_u32(&misc->acc_full[acc]), (it >> 1) & 1u, abort_flag, kStatusEpilogueTimeout);
         LM_PROF_END(prof_acc0);
         LM_PROF_BEGIN();
         if (!ok) break;
-        acc_phase ^= 1u;
         tc_fence_after();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + group * kTileN;
+        const uint32_t taddr = lane_base + acc * (kNB == 1 ? kTileN : kWideAcc1Col);
 
-        if (kOut == LM_OUT_NVFP4) {
-          constexpr bool kGated = kAct != LM_ACT_RELU2;
-          constexpr int kOutPerChunk = kGated ? 16 : 32;       // outputs per 32 accumulator columns
-          constexpr int kOutPerTile = kOutPerChunk * (kTileN / 32);
-          const int out_n = p.out_atom_cols * 64;
-          uint32_t qwords[kOutPerTile / 8];
-          uint32_t sfbytes[kOutPerTile / 16];
 #pragma unroll
-          for (int c = 0; c < kTileN / 32; ++c) {
-            uint32_t v[32];
-            tc_load32(taddr + c * 32, v);
-            tc_wait_ld();
-            if (kGated) {
-              float h[16];
-#pragma unroll
-              for (int i = 0; i < 16; ++i)
-                h[i] = gated_value<kAct>(__uint_as_float(v[2 * i]) * alpha,
-                                         __uint_as_float(v[2 * i + 1]) * alpha, p);
-              sfbytes[c] = requant16(h, inv_h, &qwords[2 * c]);
-            } else {
-              float h[32];
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                float x = fmaxf(__uint_as_float(v[i]) * alpha, 0.0f);
-                h[i] = x * x;
-              }
-              sfbytes[2 * c] = requant16(h, inv_h, &qwords[4 * c]);
-              sfbytes[2 * c + 1] = requant16(h + 16, inv_h, &qwords[4 * c + 2]);
-            }
-          }
-          // the accumulator is in registers: hand the TMEM stage back before storing
+        for (int step = 0; step < 2; ++step) {
+          // accumulator 0 shares its last columns, accumulator 1 its first
+          const int slice = kNB == 1 ? step : (((step == 0) == (acc == 0)) ? 2 + group : group);
+          const int col64 = nt * 2 * kNB + slice;  // 64-column slice of the output row
+          uint32_t v[64];
+          tc_load32(taddr + slice * 64, v);
+          tc_load32(taddr + slice * 64 + 32, v + 32);
+          tc_wait_ld();
+          // the slice is in registers: hand its TMEM columns back before converting
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[group]));
-          if (row_ok) {
-            uint8_t* q = static_cast<uint8_t*>(p.out) + out_row * (out_n >> 1) +
-                         static_cast<int64_t>(nt) * (kOutPerTile >> 1);
-#pragma unroll
-            for (int i = 0; i < kOutPerTile / 32; ++i)
-              reinterpret_cast<uint4*>(q)[i] =
-                  make_uint4(qwords[4 * i], qwords[4 * i + 1], qwords[4 * i + 2], qwords[4 * i + 3]);
-#pragma unroll
-            for (int w = 0; w < kOutPerTile / 64; ++w) {
-              uint32_t word = sfbytes[4 * w] | (sfbytes[4 * w + 1] << 8) | (sfbytes[4 * w + 2] << 16) |
-                              (sfbytes[4 * w + 3] << 24);
-              const int atom_col = nt * (kOutPerTile / 64) + w;
-              uint8_t* dst = p.out_sf + (static_cast<int64_t>(t.sf_row) * p.out_atom_cols + atom_col) * 512 +
-                             lane * 16 + quarter * 4;
-              *reinterpret_cast<uint32_t*>(dst) = word;
-            }
+          if (step == 1) {
+            if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[acc]));
+          } else if (kNB == 2) {
+            if (lane == 0) mbar_arrive(smem_u32(&misc->shared_cols_free));
           }
-        } else if (kOut == LM_OUT_BF16) {
-          // Lane = row while converting; the warp's 32 x 64 block is transposed through its
-          // shared-memory staging so that a global store covers four whole 128-byte row pieces.
-          const int col0 = nt * kTileN;
-          const int rows_here = t.valid - quarter * 32;  // valid rows among this warp's 32
-          __nv_bfloat16* warp_out =
-              static_cast<__nv_bfloat16*>(p.out) + (static_cast<int64_t>(t.row0) + quarter * 32) * p.n;
+          const bool cols_ok = col64 * 64 < p.n;
+
+          if (kOut == LM_OUT_NVFP4) {
+            constexpr bool kGated = kAct != LM_ACT_RELU2;
+            const int out_n = p.out_atom_cols * 64;
+            if (kGated) {
+              // 64 accumulator columns = 32 (gate, up) pairs -> 32 outputs: 16 bytes, 2 factors
+              uint32_t q[4];
+              uint32_t sf[2];
 #pragma unroll
-          for (int half = 0; half < kTileN / 64; ++half) {
-            uint32_t packed[32];
+              for (int c = 0; c < 2; ++c) {
+                float h[16];
 #pragma unroll
-            for (int part = 0; part < 2; ++part) {
-              uint32_t v[32];
-              tc_load32(taddr + half * 64 + part * 32, v);
-              tc_wait_ld();
+                for (int i = 0; i < 16; ++i)
+                  h[i] = gated_value<kAct>(__uint_as_float(v[32 * c + 2 * i]) * alpha,
+                                           __uint_as_float(v[32 * c + 2 * i + 1]) * alpha, p);
+                sf[c] = requant16(h, inv_h, &q[2 * c]);
+              }
+              if (row_ok && cols_ok) {
+                uint8_t* codes = static_cast<uint8_t*>(p.out) + out_row * (out_n >> 1) +
+                                 static_cast<int64_t>(col64) * 16;
+                *reinterpret_cast<uint4*>(codes) = make_uint4(q[0], q[1], q[2], q[3]);
+                uint8_t* dst = p.out_sf +
+                               (static_cast<int64_t>(t.sf_row) * p.out_atom_cols + (col64 >> 1)) * 512 +
+                               lane * 16 + quarter * 4 + (col64 & 1) * 2;
+                *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(sf[0] | (sf[1] << 8));
+              }
+            } else {
+              // 64 outputs: 32 bytes, 4 factors = one word of the scale-factor atom
+              uint32_t q[8];
+              uint32_t word = 0;
 #pragma unroll
-              for (int i = 0; i < 16; ++i)
-                packed[part * 16 + i] =
-                    pack_bf16x2(__uint_as_float(v[2 * i]) * alpha, __uint_as_float(v[2 * i + 1]) * alpha);
+              for (int c = 0; c < 4; ++c) {
+                float h[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  float x = fmaxf(__uint_as_float(v[16 * c + i]) * alpha, 0.0f);
+                  h[i] = x * x;
+                }
+                word |= requant16(h, inv_h, &q[2 * c]) << (8 * c);
+              }
+              if (row_ok && cols_ok) {
+                uint8_t* codes = static_cast<uint8_t*>(p.out) + out_row * (out_n >> 1) +
+                                 static_cast<int64_t>(col64) * 32;
+                reinterpret_cast<uint4*>(codes)[0] = make_uint4(q[0], q[1], q[2], q[3]);
+                reinterpret_cast<uint4*>(codes)[1] = make_uint4(q[4], q[5], q[6], q[7]);
+                uint8_t* dst = p.out_sf +
+                               (static_cast<int64_t>(t.sf_row) * p.out_atom_cols + col64) * 512 +
+                               lane * 16 + quarter * 4;
+                *reinterpret_cast<uint32_t*>(dst) = word;
+              }
             }
-            if (half == kTileN / 64 - 1) {
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[group]));
-            }
+          } else if (kOut == LM_OUT_BF16) {
+            // Lane = row while converting; the warp's 32 x 64 block is transposed through its
+            // shared-memory staging so that a global store covers four whole 128-byte row pieces.
+#ifdef LM_GEMM_PROFILE
+            if (p.debug_flags & 16) continue;
+#endif
+            const int rows_here = t.valid - quarter * 32;  // valid rows among this warp's 32
+            __nv_bfloat16* warp_out =
+                static_cast<__nv_bfloat16*>(p.out) + (static_cast<int64_t>(t.row0) + quarter * 32) * p.n;
 #pragma unroll
             for (int i = 0; i < 8; ++i)
               asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(warp_store + lane * kStoreRowPitch +
                                                                              i * 16),
-                           "r"(packed[4 * i]), "r"(packed[4 * i + 1]), "r"(packed[4 * i + 2]),
-                           "r"(packed[4 * i + 3])
+                           "r"(pack_bf16x2(__uint_as_float(v[8 * i]) * alpha, __uint_as_float(v[8 * i + 1]) * alpha)),
+                           "r"(pack_bf16x2(__uint_as_float(v[8 * i + 2]) * alpha, __uint_as_float(v[8 * i + 3]) * alpha)),
+                           "r"(pack_bf16x2(__uint_as_float(v[8 * i + 4]) * alpha, __uint_as_float(v[8 * i + 5]) * alpha)),
+                           "r"(pack_bf16x2(__uint_as_float(v[8 * i + 6]) * alpha, __uint_as_float(v[8 * i + 7]) * alpha))
                            : "memory");
             __syncwarp();
             const int piece = lane & 7;
-            const int col = col0 + half * 64 + piece * 8;
+            const int col = col64 * 64 + piece * 8;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int row = 4 * i + (lane >> 3);
@@ -773,31 +842,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                            : "=r"(d.x), "=r"(d.y), "=r"(d.z), "=r"(d.w)
                            : "r"(warp_store + row * kStoreRowPitch + piece * 16));
+#ifdef LM_GEMM_PROFILE
+              if (p.debug_flags & 8) continue;
+#endif
               if (row < rows_here && col < p.n)
                 *reinterpret_cast<uint4*>(warp_out + static_cast<int64_t>(row) * p.n + col) = d;
             }
             __syncwarp();
-          }
-        } else {
-          const int col0 = nt * kTileN;
-          float* out_base = static_cast<float*>(p.out) + out_row * p.n;
+          } else {
+            float* out_base = static_cast<float*>(p.out) + out_row * p.n + col64 * 64;
 #pragma unroll
-          for (int c = 0; c < kTileN / 32; ++c) {
-            uint32_t v[32];
-            tc_load32(taddr + c * 32, v);
-            tc_wait_ld();
-            const int col = col0 + c * 32;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              if (row_ok && col + 4 * i < p.n)  // N is a multiple of 8: groups of four never straddle the edge
-                reinterpret_cast<float4*>(out_base + col)[i] =
+            for (int i = 0; i < 16; ++i) {
+              // N is a multiple of 8: groups of four never straddle the edge
+              if (row_ok && col64 * 64 + 4 * i < p.n)
+                reinterpret_cast<float4*>(out_base)[i] =
                     make_float4(__uint_as_float(v[4 * i]) * alpha, __uint_as_float(v[4 * i + 1]) * alpha,
                                 __uint_as_float(v[4 * i + 2]) * alpha, __uint_as_float(v[4 * i + 3]) * alpha);
             }
           }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[group]));
         }
       }
     }
@@ -831,6 +893,7 @@ struct PlanData {
   int32_t out_kind;
   int32_t activation;
   int32_t grid;
+  int32_t n_blocks;  // 128-column blocks per tile: 1 or 2
   GemmParams params;
   alignas(64) CUtensorMap map_a;
   alignas(64) CUtensorMap map_a64;
@@ -857,6 +920,7 @@ EncodeFn encode_fn() {
   return fn;
 }
 
+// Box rows of at most 256 (the limit of a tensor-map box dimension).
 int encode_bytes_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows,
                     uint32_t box_rows) {
   EncodeFn fn = encode_fn();
@@ -872,9 +936,9 @@ int encode_bytes_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, ui
   return LM_OK;
 }
 
-template <int kOut, int kAct>
-int launch_variant(const PlanData& pd, cudaStream_t stream) {
-  auto kernel = gemm_kernel<kOut, kAct>;
+template <int kOut, int kAct, int kNB>
+int launch_kernel(const PlanData& pd, cudaStream_t stream) {
+  auto kernel = gemm_kernel<kOut, kAct, kNB>;
   static bool configured = false;
   if (!configured) {
     LM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(kOut)));
@@ -884,6 +948,11 @@ int launch_variant(const PlanData& pd, cudaStream_t stream) {
                                                           pd.params);
   LM_CUDA(cudaGetLastError());
   return LM_OK;
+}
+
+template <int kOut, int kAct>
+int launch_variant(const PlanData& pd, cudaStream_t stream) {
+  return pd.n_blocks == 2 ? launch_kernel<kOut, kAct, 2>(pd, stream) : launch_kernel<kOut, kAct, 1>(pd, stream);
 }
 
 int launch_plan(const PlanData& pd, cudaStream_t stream) {
@@ -936,7 +1005,9 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   }
   p.experts = a->experts;
   p.n = a->n;
-  p.n_tiles = (a->n + kTileN - 1) / kTileN;
+  // 256-column tiles on request, when N splits into them evenly
+  pd.n_blocks = (a->tile_n == 256 && a->n % 256 == 0) ? 2 : 1;
+  p.n_tiles = (a->n + pd.n_blocks * kTileN - 1) / (pd.n_blocks * kTileN);
   p.atom_cols = a->k / 64;
   p.k_stages = (p.atom_cols + kChunksPerStage - 1) / kChunksPerStage;
   p.sfb_atom_rows = (a->n + 127) / 128;
@@ -966,7 +1037,8 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   // Resident A halves the bytes an SM has to pull in per tile, but the ring that is left must
   // still hold enough bytes in flight to cover the load latency (measured: a 4-stage ring of B
   // tiles loses more than the halved traffic wins), so it needs at least six ring stages.
-  p.a_resident = (p.k_stages <= kMaxResident && slots - p.k_stages >= 6 && p.n_tiles >= 2) ? 1 : 0;
+  p.a_resident =
+      (pd.n_blocks == 1 && p.k_stages <= kMaxResident && slots - p.k_stages >= 6 && p.n_tiles >= 2) ? 1 : 0;
 #ifdef LM_GEMM_PROFILE
   if (p.debug_flags & 4) p.a_resident = 0;
 #endif
@@ -977,9 +1049,13 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
     while (run > 1 && m_tiles_est * ((p.n_tiles + run - 1) / run) < 8ll * pd.grid) run = (run + 1) / 2;
     p.n_per_unit = run;
   } else {
-    p.ring_stages = slots / 2 < kMaxRing ? slots / 2 : kMaxRing;
+    const int per_stage = pd.n_blocks + 1;  // B tile(s) and the A tile
+    p.ring_stages = slots / per_stage < kMaxRing ? slots / per_stage : kMaxRing;
     p.n_per_unit = 1;
   }
+#ifdef LM_GEMM_PROFILE
+  if (const char* ring = getenv("LM_GEMM_RING")) p.ring_stages = atoi(ring) < p.ring_stages ? atoi(ring) : p.ring_stages;
+#endif
   p.units_per_mtile = (p.n_tiles + p.n_per_unit - 1) / p.n_per_unit;
   // more CTAs than units would only idle: rows/128 + experts bounds the row tiles
   const int64_t max_units = ((a->rows + kTileM - 1) / kTileM + a->experts) * p.units_per_mtile;
@@ -991,7 +1067,7 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   rc = encode_bytes_2d(&pd.map_a32, a->a, static_cast<uint64_t>(a->k / 2), static_cast<uint64_t>(a->rows), 32);
   if (rc != LM_OK) return rc;
   rc = encode_bytes_2d(&pd.map_b, a->b, static_cast<uint64_t>(a->k / 2),
-                       static_cast<uint64_t>(a->experts) * a->n, kTileN);
+                       static_cast<uint64_t>(a->experts) * a->n, pd.n_blocks * kTileN);
   if (rc != LM_OK) return rc;
   memcpy(plan, &pd, sizeof(pd));
   return LM_OK;

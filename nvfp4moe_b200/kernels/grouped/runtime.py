@@ -156,6 +156,7 @@ class GroupedNvfp4Gemm:
             self.output_n = n // 2
         self.device = torch.cuda.current_device()
         self.stages = 6
+        self.max_ctas = 0  # 0 = one CTA per SM; tests lower it to run many tiles per CTA
         self._plan = None
 
     def prepare(
@@ -239,7 +240,7 @@ class GroupedNvfp4Gemm:
         args.alpha_per_expert = int(alpha.shape[0] == self.experts and self.experts > 1)
         args.dense = 0
         args.sf_tile_rows = 128
-        args.max_ctas = 0
+        args.max_ctas = int(self.max_ctas)
         args.rows = rows
         args.a = a.data_ptr()
         args.b = b.data_ptr()

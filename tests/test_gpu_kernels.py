@@ -244,7 +244,7 @@ def _device_scales(a, b):
     return _tensor_scale(a.cuda(), None).cpu(), _tensor_scale(b.cuda(), None).cpu()
 
 
-def _run_grouped(cu, a, b, alpha_scale=None, out_dtype=torch.bfloat16):
+def _run_grouped(cu, a, b, alpha_scale=None, out_dtype=torch.bfloat16, tile_n=128, max_ctas=0):
     from nvfp4moe_b200 import gemm
 
     experts, n, k = b.shape
@@ -254,7 +254,8 @@ def _run_grouped(cu, a, b, alpha_scale=None, out_dtype=torch.bfloat16):
     if alpha_scale is not None:
         alpha = alpha * alpha_scale.cuda()
     out = torch.full((a.shape[0], n), float("nan"), dtype=out_dtype, device="cuda")
-    plan = gemm.GroupedGemm(experts, n, k, 128, 128, output_dtype=out_dtype)
+    plan = gemm.GroupedGemm(experts, n, k, 128, tile_n, output_dtype=out_dtype)
+    plan.max_ctas = max_ctas
     plan(qa, qb, out, cu.cuda(), sfa, sfb, alpha)
     torch.cuda.synchronize()
     return out, (qa, qb, sfa, sfb, alpha)
@@ -318,6 +319,25 @@ def test_grouped_gemm_ragged_shapes(lens, n, k):
     assert O.rel_frobenius(out.cpu().float(), ref.to(torch.bfloat16).float()) <= GEMM_REL_TOL
 
 
+@pytest.mark.parametrize("out_dtype", (torch.bfloat16, torch.float32))
+@pytest.mark.parametrize("max_ctas", (0, 3))
+def test_grouped_gemm_wide_tiles_bit_identical(out_dtype, max_ctas):
+    """128 x 256 tiles accumulate every output in the same order as 128 x 128 tiles."""
+    lens = [130, 0, 257, 5, 128, 300, 0, 64]
+    cu, a, b = _grouped_case(lens, 1024, 1280, seed=77, b_std=0.05)
+    narrow, _ = _run_grouped(cu, a, b, out_dtype=out_dtype)
+    wide, _ = _run_grouped(cu, a, b, out_dtype=out_dtype, tile_n=256, max_ctas=max_ctas)
+    ref, _ = _oracle_grouped(cu, a, b)
+    assert torch.isfinite(wide).all()
+    assert torch.equal(wide, narrow)
+    tol = GEMM_REL_TOL if out_dtype == torch.bfloat16 else 1e-5
+    ref = ref.to(out_dtype).float()
+    assert O.rel_frobenius(wide.cpu().float(), ref) <= tol
+    from nvfp4moe_b200 import _lib
+
+    assert _lib.device_status() == 0
+
+
 def test_grouped_gemm_fp32_output_and_per_expert_alpha():
     lens = [3, 5, 2, 7]
     cu, a, b = _grouped_case(lens, 128, 256, seed=20260822, b_std=1.0)
@@ -359,7 +379,8 @@ def test_dense_gemm_matches_oracle():
     (("swiglu", None), ("swiglu", 10.0), ("swiglu_oai", None), ("geglu", None), ("reglu", None),
      ("relu2", None)),
 )
-def test_fused_epilogue_matches_oracle(activation, clamp):
+@pytest.mark.parametrize("tile_n", (128, 256))
+def test_fused_epilogue_matches_oracle(activation, clamp, tile_n):
     from nvfp4moe_b200 import gemm
     from nvfp4moe_b200.kernels.gated import GatedEpilogue
     from nvfp4moe_b200.kernels.unary import UnaryEpilogue
@@ -385,8 +406,9 @@ def test_fused_epilogue_matches_oracle(activation, clamp):
     qh = torch.zeros(rows, inter // 2, dtype=torch.uint8, device="cuda")
     sfh = torch.zeros(1, tiles, inter // 64, 32, 4, 4, dtype=torch.float8_e4m3fn, device="cuda")
     pair = torch.cat((h_pts, 1.0 / h_pts)).cuda()
-    plan = gemm.GroupedGemm(len(lens), n, hidden, 128, 128, output_dtype=torch.float4_e2m1fn_x2,
+    plan = gemm.GroupedGemm(len(lens), n, hidden, 128, tile_n, output_dtype=torch.float4_e2m1fn_x2,
                             epilogue=policy)
+    plan.max_ctas = 2 if tile_n == 256 else 0
     plan(qa, qb, qh.view(torch.float4_e2m1fn_x2), cu.cuda(), sfa, sfb, alpha, output_sf=sfh,
          output_scale=pair)
     torch.cuda.synchronize()
