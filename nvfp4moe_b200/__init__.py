@@ -8,6 +8,7 @@ __version__ = "0.1.0"
 _EXPORTS = {
     "InferenceMoE": (".inference", "InferenceMoE"),
     "InferenceWorkspace": (".inference", "InferenceWorkspace"),
+    "HostPipeline": (".host_pipeline", "HostPipeline"),
     "MoEDispatch": (".routing", "MoEDispatch"),
     "MoEExpertLayer": (".training", "MoEExpertLayer"),
 }

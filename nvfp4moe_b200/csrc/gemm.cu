@@ -83,13 +83,15 @@ __device__ uint32_t g_status = 0;
 // [0] producer waits on empty, [1] MMA waits on full, [2] MMA waits on acc_empty,
 // [3] epilogue (warp 2) waits on acc_full, [4] epilogue (warp 2) busy, [5] kernel cycles,
 // [6] tiles of CTA 0, [7] MMA issue cycles
-__device__ unsigned long long g_prof[8];
+__device__ unsigned long long g_prof[16];
 #define LM_PROF_DECL long long prof_t0 = clock64(), prof_acc0 = 0, prof_acc1 = 0, prof_acc2 = 0; (void)prof_t0; (void)prof_acc0; (void)prof_acc1; (void)prof_acc2
+#define LM_PROF_LAP(acc) { const long long now_ = clock64(); acc += now_ - prof_lap; prof_lap = now_; }
 #define LM_PROF_BEGIN() prof_t0 = clock64()
 #define LM_PROF_END(acc) acc += clock64() - prof_t0
 #define LM_PROF_STORE(idx, acc) if (blockIdx.x == 0) g_prof[idx] = static_cast<unsigned long long>(acc)
 #else
 #define LM_PROF_DECL
+#define LM_PROF_LAP(acc)
 #define LM_PROF_BEGIN()
 #define LM_PROF_END(acc)
 #define LM_PROF_STORE(idx, acc)
@@ -264,6 +266,19 @@ __device__ __forceinline__ void tc_store16(uint32_t taddr, const uint32_t* r) {
       "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
       "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
+}
+
+// Waits for the TMEM loads in flight.  The destination registers are operands, so no use
+// of them can be scheduled ahead of the wait.
+__device__ __forceinline__ void tc_wait_ld_regs(uint32_t* r) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
 }
 
 __device__ __forceinline__ void tc_wait_ld() {
@@ -725,6 +740,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     int it = 0;
     bool ok = true;
     LM_PROF_DECL;
+#ifdef LM_GEMM_PROFILE
+    long long lap[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long prof_lap = clock64();
+#endif
     float inv_h = 0.0f;
     if (kOut == LM_OUT_NVFP4) inv_h = __ldg(p.out_scale + 1);
     for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
@@ -737,73 +756,104 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (kNB == 1 && (it & 1) != group) continue;
         const int acc = it & 1;
         LM_PROF_END(prof_acc1);  // busy since the previous wait ended
+        LM_PROF_LAP(lap[6]);
         LM_PROF_BEGIN();
         ok = mbar_wait(smem_u32(&misc->acc_full[acc]), (it >> 1) & 1u, abort_flag, kStatusEpilogueTimeout);
         LM_PROF_END(prof_acc0);
         LM_PROF_BEGIN();
+#ifdef LM_GEMM_PROFILE
+        prof_lap = clock64();
+#endif
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = lane_base + acc * (kNB == 1 ? kTileN : kWideAcc1Col);
 
-#pragma unroll
-        for (int step = 0; step < 2; ++step) {
-          // accumulator 0 shares its last columns, accumulator 1 its first
-          const int slice = kNB == 1 ? step : (((step == 0) == (acc == 0)) ? 2 + group : group);
-          const int col64 = nt * 2 * kNB + slice;  // 64-column slice of the output row
-          uint32_t v[64];
-          tc_load32(taddr + slice * 64, v);
-          tc_load32(taddr + slice * 64 + 32, v + 32);
-          tc_wait_ld();
-          // the slice is in registers: hand its TMEM columns back before converting
-          tc_fence_before();
-          __syncwarp();
-          if (step == 1) {
-            if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[acc]));
-          } else if (kNB == 2) {
-            if (lane == 0) mbar_arrive(smem_u32(&misc->shared_cols_free));
-          }
-          const bool cols_ok = col64 * 64 < p.n;
+        // Software pipeline over the four 32-column chunks of the warp's two slices: while
+        // a chunk is converted, the load of the chunk after next is in flight (a TMEM load
+        // takes several hundred cycles from issue to data).
+        const int slice0 = kNB == 1 ? 0 : ((acc == 0) ? 2 + group : group);
+        const int slice1 = kNB == 1 ? 1 : ((acc == 0) ? group : 2 + group);
+        const bool rows_any = t.valid > quarter * 32;  // this warp owns at least one valid row
+        uint32_t va[32], vb[32];
+        LM_PROF_LAP(lap[7]);
+        tc_load32(taddr + slice0 * 64, va);
+        tc_load32(taddr + slice0 * 64 + 32, vb);
+        tc_wait_ld_regs(va);
+        tc_wait_ld_regs(vb);
+        // slice 0 is in registers: the columns shared with the other accumulator are free
+        tc_fence_before();
+        __syncwarp();
+        if (kNB == 2 && lane == 0) mbar_arrive(smem_u32(&misc->shared_cols_free));
+        LM_PROF_LAP(lap[0]);
 
+        // ---- per-slice state and the two halves of the work
+        constexpr bool kGated = kAct != LM_ACT_RELU2;
+        uint32_t q[8];   // NVFP4: packed codes of the slice
+        uint32_t sfw = 0;  // NVFP4: scale-factor bytes of the slice
+        (void)q;
+        (void)sfw;
+        auto convert = [&](const uint32_t* v, const int half, const int col64) {
           if (kOut == LM_OUT_NVFP4) {
-            constexpr bool kGated = kAct != LM_ACT_RELU2;
-            const int out_n = p.out_atom_cols * 64;
             if (kGated) {
-              // 64 accumulator columns = 32 (gate, up) pairs -> 32 outputs: 16 bytes, 2 factors
-              uint32_t q[4];
-              uint32_t sf[2];
+              // 32 accumulator columns = 16 (gate, up) pairs -> 16 outputs: 8 bytes, one factor
+              float h[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                h[i] = gated_value<kAct>(__uint_as_float(v[2 * i]) * alpha,
+                                         __uint_as_float(v[2 * i + 1]) * alpha, p);
+              const uint32_t sf = requant16(h, inv_h, &q[2 * half]);
+              sfw = half == 0 ? sf : (sfw | (sf << 8));
+            } else {
+              // 32 outputs: 16 bytes, two factors
 #pragma unroll
               for (int c = 0; c < 2; ++c) {
-                float h[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                  h[i] = gated_value<kAct>(__uint_as_float(v[32 * c + 2 * i]) * alpha,
-                                           __uint_as_float(v[32 * c + 2 * i + 1]) * alpha, p);
-                sf[c] = requant16(h, inv_h, &q[2 * c]);
-              }
-              if (row_ok && cols_ok) {
-                uint8_t* codes = static_cast<uint8_t*>(p.out) + out_row * (out_n >> 1) +
-                                 static_cast<int64_t>(col64) * 16;
-                *reinterpret_cast<uint4*>(codes) = make_uint4(q[0], q[1], q[2], q[3]);
-                uint8_t* dst = p.out_sf +
-                               (static_cast<int64_t>(t.sf_row) * p.out_atom_cols + (col64 >> 1)) * 512 +
-                               lane * 16 + quarter * 4 + (col64 & 1) * 2;
-                *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(sf[0] | (sf[1] << 8));
-              }
-            } else {
-              // 64 outputs: 32 bytes, 4 factors = one word of the scale-factor atom
-              uint32_t q[8];
-              uint32_t word = 0;
-#pragma unroll
-              for (int c = 0; c < 4; ++c) {
                 float h[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                   float x = fmaxf(__uint_as_float(v[16 * c + i]) * alpha, 0.0f);
                   h[i] = x * x;
                 }
-                word |= requant16(h, inv_h, &q[2 * c]) << (8 * c);
+                const uint32_t sf = requant16(h, inv_h, &q[4 * half + 2 * c]);
+                sfw = (half == 0 && c == 0) ? sf : (sfw | (sf << (8 * (2 * half + c))));
               }
-              if (row_ok && cols_ok) {
+            }
+          } else if (kOut == LM_OUT_BF16) {
+            // lane = row: the warp's 32 x 64 block goes to its shared-memory staging
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(warp_store + lane * kStoreRowPitch +
+                                                                             half * 64 + i * 16),
+                           "r"(pack_bf16x2(__uint_as_float(v[8 * i]) * alpha, __uint_as_float(v[8 * i + 1]) * alpha)),
+                           "r"(pack_bf16x2(__uint_as_float(v[8 * i + 2]) * alpha, __uint_as_float(v[8 * i + 3]) * alpha)),
+                           "r"(pack_bf16x2(__uint_as_float(v[8 * i + 4]) * alpha, __uint_as_float(v[8 * i + 5]) * alpha)),
+                           "r"(pack_bf16x2(__uint_as_float(v[8 * i + 6]) * alpha, __uint_as_float(v[8 * i + 7]) * alpha))
+                           : "memory");
+          } else {
+            float* out_base = static_cast<float*>(p.out) + out_row * p.n + col64 * 64 + half * 32;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              // N is a multiple of 8: groups of four never straddle the edge
+              if (row_ok && col64 * 64 + half * 32 + 4 * i < p.n)
+                reinterpret_cast<float4*>(out_base)[i] =
+                    make_float4(__uint_as_float(v[4 * i]) * alpha, __uint_as_float(v[4 * i + 1]) * alpha,
+                                __uint_as_float(v[4 * i + 2]) * alpha, __uint_as_float(v[4 * i + 3]) * alpha);
+            }
+          }
+        };
+        auto finish = [&](const int col64) {
+          const bool cols_ok = col64 * 64 < p.n;
+          if (kOut == LM_OUT_NVFP4) {
+            const int out_n = p.out_atom_cols * 64;
+            if (row_ok && cols_ok) {
+              if (kGated) {
+                uint8_t* codes = static_cast<uint8_t*>(p.out) + out_row * (out_n >> 1) +
+                                 static_cast<int64_t>(col64) * 16;
+                *reinterpret_cast<uint4*>(codes) = make_uint4(q[0], q[1], q[2], q[3]);
+                uint8_t* dst = p.out_sf +
+                               (static_cast<int64_t>(t.sf_row) * p.out_atom_cols + (col64 >> 1)) * 512 +
+                               lane * 16 + quarter * 4 + (col64 & 1) * 2;
+                *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(sfw);
+              } else {
                 uint8_t* codes = static_cast<uint8_t*>(p.out) + out_row * (out_n >> 1) +
                                  static_cast<int64_t>(col64) * 32;
                 reinterpret_cast<uint4*>(codes)[0] = make_uint4(q[0], q[1], q[2], q[3]);
@@ -811,62 +861,68 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 uint8_t* dst = p.out_sf +
                                (static_cast<int64_t>(t.sf_row) * p.out_atom_cols + col64) * 512 +
                                lane * 16 + quarter * 4;
-                *reinterpret_cast<uint32_t*>(dst) = word;
+                *reinterpret_cast<uint32_t*>(dst) = sfw;
               }
             }
           } else if (kOut == LM_OUT_BF16) {
-            // Lane = row while converting; the warp's 32 x 64 block is transposed through its
-            // shared-memory staging so that a global store covers four whole 128-byte row pieces.
-#ifdef LM_GEMM_PROFILE
-            if (p.debug_flags & 16) continue;
-#endif
-            const int rows_here = t.valid - quarter * 32;  // valid rows among this warp's 32
-            __nv_bfloat16* warp_out =
-                static_cast<__nv_bfloat16*>(p.out) + (static_cast<int64_t>(t.row0) + quarter * 32) * p.n;
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(warp_store + lane * kStoreRowPitch +
-                                                                             i * 16),
-                           "r"(pack_bf16x2(__uint_as_float(v[8 * i]) * alpha, __uint_as_float(v[8 * i + 1]) * alpha)),
-                           "r"(pack_bf16x2(__uint_as_float(v[8 * i + 2]) * alpha, __uint_as_float(v[8 * i + 3]) * alpha)),
-                           "r"(pack_bf16x2(__uint_as_float(v[8 * i + 4]) * alpha, __uint_as_float(v[8 * i + 5]) * alpha)),
-                           "r"(pack_bf16x2(__uint_as_float(v[8 * i + 6]) * alpha, __uint_as_float(v[8 * i + 7]) * alpha))
-                           : "memory");
+            // transposed read: a global store covers four whole 128-byte row pieces
             __syncwarp();
-            const int piece = lane & 7;
-            const int col = col64 * 64 + piece * 8;
+            if (rows_any && cols_ok) {
+              const int rows_here = t.valid - quarter * 32;  // valid rows among this warp's 32
+              __nv_bfloat16* warp_out =
+                  static_cast<__nv_bfloat16*>(p.out) + (static_cast<int64_t>(t.row0) + quarter * 32) * p.n;
+              const int piece = lane & 7;
+              const int col = col64 * 64 + piece * 8;
+              uint4 d[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int row = 4 * i + (lane >> 3);
-              uint4 d;
-              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(d.x), "=r"(d.y), "=r"(d.z), "=r"(d.w)
-                           : "r"(warp_store + row * kStoreRowPitch + piece * 16));
+              for (int i = 0; i < 8; ++i)
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(d[i].x), "=r"(d[i].y), "=r"(d[i].z), "=r"(d[i].w)
+                             : "r"(warp_store + (4 * i + (lane >> 3)) * kStoreRowPitch + piece * 16));
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int row = 4 * i + (lane >> 3);
 #ifdef LM_GEMM_PROFILE
-              if (p.debug_flags & 8) continue;
+                if (p.debug_flags & 8) continue;
 #endif
-              if (row < rows_here && col < p.n)
-                *reinterpret_cast<uint4*>(warp_out + static_cast<int64_t>(row) * p.n + col) = d;
+                if (row < rows_here && col < p.n)
+                  *reinterpret_cast<uint4*>(warp_out + static_cast<int64_t>(row) * p.n + col) = d[i];
+              }
             }
             __syncwarp();
-          } else {
-            float* out_base = static_cast<float*>(p.out) + out_row * p.n + col64 * 64;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              // N is a multiple of 8: groups of four never straddle the edge
-              if (row_ok && col64 * 64 + 4 * i < p.n)
-                reinterpret_cast<float4*>(out_base)[i] =
-                    make_float4(__uint_as_float(v[4 * i]) * alpha, __uint_as_float(v[4 * i + 1]) * alpha,
-                                __uint_as_float(v[4 * i + 2]) * alpha, __uint_as_float(v[4 * i + 3]) * alpha);
-            }
           }
-        }
+        };
+
+        const int col_a = nt * 2 * kNB + slice0;
+        const int col_b = nt * 2 * kNB + slice1;
+        convert(va, 0, col_a);
+        tc_load32(taddr + slice1 * 64, va);
+        convert(vb, 1, col_a);
+        tc_load32(taddr + slice1 * 64 + 32, vb);
+        LM_PROF_LAP(lap[1]);
+        finish(col_a);
+        LM_PROF_LAP(lap[2]);
+        tc_wait_ld_regs(va);
+        tc_wait_ld_regs(vb);
+        // the whole accumulator has been read
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[acc]));
+        LM_PROF_LAP(lap[3]);
+        convert(va, 0, col_b);
+        convert(vb, 1, col_b);
+        LM_PROF_LAP(lap[4]);
+        finish(col_b);
+        LM_PROF_LAP(lap[5]);
       }
     }
     LM_PROF_END(prof_acc1);
     if (warp == kFirstEpilogueWarp && lane == 0) {
       LM_PROF_STORE(3, prof_acc0);
       LM_PROF_STORE(4, prof_acc1);
+#ifdef LM_GEMM_PROFILE
+      for (int i = 0; i < 8; ++i) { LM_PROF_STORE(8 + i, lap[i]); }
+#endif
     }
   }
 

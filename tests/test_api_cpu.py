@@ -210,3 +210,17 @@ def test_product_package_never_imports_the_oracle():
         assert "oracle" not in text, path
     for path in (ROOT / "nvfp4moe_b200" / "csrc").glob("*.cu*"):
         assert "oracle" not in path.read_text(), path
+
+
+def test_host_pipeline_needs_cuda():
+    """The host-buffer pipeline has no CPU path: it refuses to build without a device."""
+    import torch
+
+    from nvfp4moe_b200 import HostPipeline
+
+    if torch.cuda.is_available():
+        pytest.skip("CUDA present")
+    with pytest.raises(RuntimeError, match="needs a CUDA device"):
+        HostPipeline(object(), 8, 128, 2)
+    with pytest.raises(ValueError, match="depth"):
+        HostPipeline(object(), 8, 128, 2, depth=0)

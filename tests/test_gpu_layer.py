@@ -319,3 +319,37 @@ def test_expert_parallel_layer_on_one_rank_equals_the_plain_layer():
     torch.cuda.synchronize()
     assert torch.equal(got, expected)
     assert torch.equal(got, again)
+
+
+def test_host_pipeline_matches_direct_steps():
+    """Overlapped host-buffer steps give the bits of plain device steps, batch by batch."""
+    from nvfp4moe_b200 import HostPipeline, InferenceMoE
+
+    hidden, inter, experts, k, tokens = 256, 128, 8, 2, 192
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(99)
+    layer = InferenceMoE(hidden, inter, experts, k, tokens, device=dev)
+    layer.load_weights((torch.randn(experts, inter, hidden, generator=g) * 0.05).to(torch.bfloat16).to(dev),
+                       (torch.randn(experts, inter, hidden, generator=g) * 0.05).to(torch.bfloat16).to(dev),
+                       (torch.randn(experts, hidden, inter, generator=g) * 0.05).to(torch.bfloat16).to(dev))
+    batches = []
+    for _ in range(5):
+        x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16).pin_memory()
+        scores = torch.rand(tokens, experts, generator=g)
+        w, ids = scores.topk(k, dim=-1)
+        batches.append((x, ids.to(torch.int32).pin_memory(), (w / w.sum(-1, keepdim=True)).pin_memory(),
+                        torch.zeros(tokens, hidden, dtype=torch.bfloat16).pin_memory()))
+    layer.calibrate(batches[0][0].to(dev), batches[0][1].to(dev), batches[0][2].to(dev))
+    direct = [layer.run(x.to(dev), ids.to(dev), w.to(dev)).clone().cpu() for x, ids, w, _ in batches]
+    pipe = HostPipeline(layer, tokens, hidden, k, depth=2, device=dev)
+    tickets = [pipe.submit(*batch) for batch in batches]
+    assert tickets == list(range(5))
+    pipe.wait(tickets[1])
+    assert torch.equal(batches[1][3], direct[1])
+    pipe.wait()
+    for batch, ref in zip(batches, direct):
+        assert torch.equal(batch[3], ref)
+    with pytest.raises(ValueError, match="pinned"):
+        pipe.submit(batches[0][0].clone(), *batches[0][1:])
+    with pytest.raises(ValueError, match="unknown ticket"):
+        pipe.wait(99)
