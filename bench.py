@@ -54,46 +54,63 @@ def _routing(tokens, experts, k, seed, device="cpu"):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons through NVML (read-only) while a region runs."""
 
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-             "clocks_event_reasons.sw_power_cap")
+    REASONS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"),
+               (0x4, "sw_power_cap"))
 
-    def __init__(self, index: int):
-        self.index = index
-        self.samples: list[list[str]] = []
+    def __init__(self, index: int, period_s: float = 0.002):
+        self.samples: list[tuple[int, int]] = []  # (SM MHz, reason bit mask)
+        self.max_mhz = None
+        self.period_s = period_s
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
+        self._nvml = None
+        self._handle = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            try:
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
+                self._handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+            self._nvml = pynvml
+        except Exception:
+            self._nvml = None
 
     def _run(self):
+        nvml = self._nvml
         while not self._stop.is_set():
             try:
-                out = subprocess.run(
-                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                     "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
-                if out.returncode == 0 and out.stdout.strip():
-                    self.samples.append([f.strip() for f in out.stdout.strip().split(",")])
+                mhz = nvml.nvmlDeviceGetClockInfo(self._handle, nvml.NVML_CLOCK_SM)
+                mask = nvml.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+                self.samples.append((int(mhz), int(mask)))
             except Exception:
                 pass
-            self._stop.wait(0.05)
+            self._stop.wait(self.period_s)
 
     def __enter__(self):
-        self._thread.start()
+        if self._nvml is not None:
+            self._thread.start()
         return self
 
     def __exit__(self, *exc):
         self._stop.set()
-        self._thread.join(timeout=10)
+        if self._thread.is_alive():
+            self._thread.join(timeout=10)
 
     def summary(self):
-        clocks = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
-        maxes = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = sorted({n for s in self.samples for n, v in zip(names, s[2:6]) if v == "Active"})
+        clocks = [mhz for mhz, _ in self.samples]
+        seen = 0
+        for _, mask in self.samples:
+            seen |= mask
+        reasons = [name for bit, name in self.REASONS if seen & bit]
         return {"sm_mhz": statistics.median(clocks) if clocks else None,
-                "sm_max_mhz": max(maxes) if maxes else None, "reasons": reasons,
-                "samples": len(self.samples)}
+                "sm_min_mhz": min(clocks) if clocks else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(self.samples), "source": "nvml"}
 
 
 # ------------------------------------------------------------------ CPU arm

@@ -224,6 +224,9 @@ typedef struct lm_gemm_args {
   const float* alpha;    /* (1) or (experts) */
   void* out_sf;          /* NVFP4 output: varlen atoms with out_n/64 atom columns */
   const float* out_scale; /* NVFP4 output: {pts, 1/pts} of the result */
+  const uint64_t* out_row_ptrs; /* BF16 output, optional: device table (rows) of 16-byte aligned
+                                   addresses, row i is written there instead of out + i*n; the
+                                   addresses may point into a peer GPU's memory */
 } lm_gemm_args;
 
 /* Caller-provided storage for a prepared GEMM (tensor maps + arguments). */
@@ -235,6 +238,56 @@ typedef struct lm_gemm_plan {
 int lm_gemm_prepare(const lm_gemm_args* args, lm_gemm_plan* plan);
 /* Launches a prepared GEMM.  Safe inside CUDA Graph capture. */
 int lm_gemm_launch(const lm_gemm_plan* plan, lm_stream_t stream);
+
+/* ---------------------------------------------------------------- expert parallel
+ * The reference has no communication code (README.md:227-228 leaves expert-parallel
+ * exchange to the host framework); these two entry points are that exchange for one
+ * NVLink domain, over peer pointers.  Rank r of `world` owns experts
+ * [r*experts/world, (r+1)*experts/world).
+ */
+#define LM_EP_MAX_RANKS 8
+
+/*
+ * Route plan, from the gathered row counts of all ranks, entirely on the device.
+ *   counts_all   (world, experts) int32, row g = rows rank g routed to every expert
+ *   return_base  HOST array (world) of the address of every rank's return buffer
+ *                (rows of `row_bytes` bytes in that rank's own expert-major order)
+ *   own_indptr   (experts/world + 1) bounds of the rows this rank receives, expert-major,
+ *                within an expert by source rank
+ *   dest_base    (experts) row on the owner where this rank's rows of expert e begin
+ *   owner_start  (experts) row on the owner where expert e begins
+ *   row_ptrs     (max_rows) address each received row's result goes to (lm_gemm_args.out_row_ptrs)
+ *   valid        1, or 0 when some rank would receive more than max_rows rows: then own_indptr
+ *                is all zero (the GEMMs compute nothing) and lm_ep_quantize_send sends nothing
+ */
+int lm_ep_plan(const int32_t* counts_all, int world, int rank, int experts, int64_t max_rows,
+               int64_t row_bytes, const uint64_t* return_base, int32_t* own_indptr,
+               int32_t* dest_base, int32_t* owner_start, uint64_t* row_ptrs, int32_t* valid,
+               lm_stream_t stream);
+
+/*
+ * lm_quantize_decode whose destinations are the owners' operand buffers: each token is
+ * quantized once and its packed row and scale factors are stored, through peer pointers, at
+ * the rows lm_ep_plan assigned.
+ *   slots, topk_ids, src_indptr  this rank's lm_dispatch outputs over the global experts
+ *   q_base, sf_base  HOST arrays (world) of the addresses of every rank's packed-row buffer
+ *                    (rows of features/2 bytes) and row-major scale factors (rows of
+ *                    features/16 bytes); the owner turns the latter into atoms with
+ *                    lm_ep_sf_swizzle once every source has finished
+ */
+int lm_ep_quantize_send(const void* x, int64_t tokens, int features, int top_k, int world,
+                        int experts, const int32_t* slots, const int32_t* topk_ids,
+                        const int32_t* src_indptr, const int32_t* dest_base,
+                        const int32_t* owner_start, const int32_t* valid, const float* scale_pair,
+                        const uint64_t* q_base, const uint64_t* sf_base, lm_stream_t stream);
+
+/*
+ * Row-major scale factors (max_rows, features/16) -> varlen atoms as LM_SF_VARLEN lays them
+ * out (expert e starts at atom row m_indptr[e]/128 + e).  Rows past an expert's last row in
+ * its last tile are written as zero.  features must be a multiple of 256.
+ */
+int lm_ep_sf_swizzle(const uint8_t* linear, int64_t max_rows, int features, const int32_t* m_indptr,
+                     int experts, uint8_t* atoms, lm_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -50,6 +50,7 @@ class GemmArgs(ctypes.Structure):
         ("alpha", c_ptr),
         ("out_sf", c_ptr),
         ("out_scale", c_ptr),
+        ("out_row_ptrs", c_ptr),
     ]
 
 
@@ -71,6 +72,17 @@ _SIGNATURES = {
         c_i32,
         [c_ptr, c_i64, c_i32, c_i32, c_ptr, c_ptr, c_ptr, c_i32, c_ptr, c_ptr, c_ptr, c_ptr],
     ),
+    "lm_ep_plan": (
+        c_i32,
+        [c_ptr, c_i32, c_i32, c_i32, c_i64, c_i64, ctypes.POINTER(ctypes.c_uint64), c_ptr, c_ptr, c_ptr,
+         c_ptr, c_ptr, c_ptr],
+    ),
+    "lm_ep_quantize_send": (
+        c_i32,
+        [c_ptr, c_i64, c_i32, c_i32, c_i32, c_i32, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
+         ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64), c_ptr],
+    ),
+    "lm_ep_sf_swizzle": (c_i32, [c_ptr, c_i64, c_i32, c_ptr, c_i32, c_ptr, c_ptr]),
     "lm_dispatch_scratch_elems": (c_i64, [c_i64, c_i32]),
     "lm_dispatch": (
         c_i32,

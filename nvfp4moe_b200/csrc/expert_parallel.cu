@@ -1,0 +1,325 @@
+// Expert-parallel step over peer memory: the route plan and the quantize-and-send kernel.
+//
+// Rank r of G owns experts [r*L, (r+1)*L).  After the ranks have gathered each other's
+// per-expert row counts (one small collective), every rank can compute on its own device
+// where each of its rows lands on the owner and where each row it computes has to go back:
+// no row count ever travels to the host.  The quantizer then writes packed rows straight into
+// the owners' GEMM operand buffers through peer pointers (plain stores over NVLink), and the
+// fc2 GEMM writes its BF16 rows straight into the source ranks' buffers through the per-row
+// pointer table built here.  Scale factors travel row-major (32 contiguous bytes per warp
+// store: the 4-byte pieces of the swizzled atoms cost three times as long on the link) and
+// the owner swizzles them into atoms with a local kernel.
+//
+// Row order on the owner: expert-major, within an expert by source rank, within a source in
+// the source's own (stable) expert-major order.
+#include "common.cuh"
+#include "quantize_math.cuh"
+
+namespace lm {
+namespace {
+
+constexpr int kMaxRanks = LM_EP_MAX_RANKS;
+constexpr int kMaxExperts = 256;
+constexpr int kPlanThreads = 256;
+
+struct PlanParams {
+  const int32_t* counts_all;  // [world, experts]: row g = rows rank g holds for every expert
+  int world;
+  int rank;
+  int experts;
+  int local_experts;
+  int64_t max_rows;       // rows the owners' operand buffers hold
+  int64_t row_bytes;      // bytes of one returned row
+  uint64_t return_base[kMaxRanks];  // address of every rank's return buffer
+  int32_t* own_indptr;    // [local_experts + 1] expert bounds of the rows this rank receives
+  int32_t* dest_base;     // [experts] owner row where this rank's rows of expert e begin
+  int32_t* owner_start;   // [experts] owner row where expert e begins
+  uint64_t* row_ptrs;     // [max_rows] where each received row's result goes
+  int32_t* valid;         // 1 when every owner's rows fit max_rows
+};
+
+// Every CTA rebuilds the (tiny) plan in shared memory; CTA 0 writes the tables, and the
+// CTAs share the (expert, source) segments of the row-pointer table.
+__global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(PlanParams p) {
+  __shared__ int s_cnt[kMaxRanks][kMaxExperts];
+  __shared__ int s_src_start[kMaxRanks][kMaxExperts];  // source g's own m_indptr
+  __shared__ int s_owner_start[kMaxExperts];
+  __shared__ int s_total[kMaxExperts];
+  __shared__ int s_owner_rows[kMaxRanks];
+  const int tid = threadIdx.x;
+  const int E = p.experts, G = p.world, L = p.local_experts;
+  for (int i = tid; i < G * E; i += kPlanThreads) s_cnt[i / E][i % E] = __ldg(p.counts_all + i);
+  __syncthreads();
+  if (tid < G) {  // exclusive prefix over the experts of source tid
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      s_src_start[tid][e] = run;
+      run += s_cnt[tid][e];
+    }
+  }
+  for (int e = tid; e < E; e += kPlanThreads) {
+    int total = 0;
+    for (int g = 0; g < G; ++g) total += s_cnt[g][e];
+    s_total[e] = total;
+  }
+  __syncthreads();
+  if (tid < G) {  // exclusive prefix over the local experts of owner tid
+    int run = 0;
+    for (int l = 0; l < L; ++l) {
+      s_owner_start[tid * L + l] = run;
+      run += s_total[tid * L + l];
+    }
+    s_owner_rows[tid] = run;
+  }
+  __syncthreads();
+  bool fits = true;
+  for (int g = 0; g < G; ++g) fits = fits && s_owner_rows[g] <= p.max_rows;
+
+  if (blockIdx.x == 0) {
+    for (int e = tid; e < E; e += kPlanThreads) {
+      int before = 0;
+      for (int g = 0; g < p.rank; ++g) before += s_cnt[g][e];
+      p.dest_base[e] = s_owner_start[e] + before;
+      p.owner_start[e] = s_owner_start[e];
+    }
+    // an oversized step computes nothing: empty experts, and the flag for the host
+    for (int l = tid; l <= L; l += kPlanThreads)
+      p.own_indptr[l] = !fits ? 0 : (l < L ? s_owner_start[p.rank * L + l] : s_owner_rows[p.rank]);
+    if (tid == 0) *p.valid = fits ? 1 : 0;
+  }
+  if (!fits) return;
+  for (int seg = blockIdx.x; seg < L * G; seg += gridDim.x) {
+    const int l = seg / G, g = seg % G;
+    const int e = p.rank * L + l;
+    int before = 0;
+    for (int h = 0; h < g; ++h) before += s_cnt[h][e];
+    const int first = s_owner_start[e] + before;
+    const int64_t src_row = s_src_start[g][e];
+    const int rows = s_cnt[g][e];
+    for (int i = tid; i < rows; i += kPlanThreads)
+      p.row_ptrs[first + i] = p.return_base[g] + static_cast<uint64_t>(src_row + i) * p.row_bytes;
+  }
+}
+
+// ------------------------------------------------ quantize once, send to the owners
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kTileRows = 128;
+constexpr int kTileCols = 512;  // 32 lanes x 16 elements
+
+struct SendParams {
+  const __nv_bfloat16* x;
+  int64_t tokens;
+  int features;
+  int top_k;
+  int local_experts;
+  const int32_t* slots;        // (tokens*top_k) row in this rank's expert-major order, -1 = dropped
+  const int32_t* topk_ids;     // global expert ids
+  const int32_t* src_indptr;   // this rank's dispatch bounds over the global experts
+  const int32_t* dest_base;
+  const int32_t* owner_start;
+  const int32_t* valid;
+  const float* scale_pair;
+  uint8_t* q[kMaxRanks];       // every rank's packed-row buffer
+  uint8_t* sf[kMaxRanks];      // every rank's row-major scale factors, features/16 bytes a row
+};
+
+// One warp per (token, 512-feature slice), as in the single-GPU scatter quantizer; only the
+// destination differs: the owner's buffer and the row the route plan assigns.
+__global__ void __launch_bounds__(kThreads) ep_quantize_send_kernel(SendParams p) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int64_t token = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  if (token >= p.tokens || __ldg(p.valid) == 0) return;
+  const int col = blockIdx.y * kTileCols + lane * 16;
+  const bool col_ok = col < p.features;
+  int my_row = -1, my_owner = 0;
+  if (lane < p.top_k) {
+    const int slot = __ldg(p.slots + token * p.top_k + lane);
+    if (slot >= 0) {
+      const int e = __ldg(p.topk_ids + token * p.top_k + lane);
+      my_owner = e / p.local_experts;
+      my_row = __ldg(p.dest_base + e) + (slot - __ldg(p.src_indptr + e));
+    }
+  }
+  const float pts = __ldg(p.scale_pair);
+  const float inv_pts = __ldg(p.scale_pair + 1);
+  Slice<__nv_bfloat16> v;
+  uint2 packed = make_uint2(0, 0);
+  uint32_t sf_byte = 0;
+  if (col_ok) {
+    v.load(p.x + token * p.features + col);
+    sf_byte = quantize_group(v, pts, inv_pts, true, &packed);
+  }
+  uint32_t word = sf_byte;
+  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 1) << 8;
+  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 2) << 16;
+  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 3) << 24;
+  for (int j = 0; j < p.top_k; ++j) {
+    const int row = __shfl_sync(0xFFFFFFFFu, my_row, j);
+    const int owner = __shfl_sync(0xFFFFFFFFu, my_owner, j);
+    if (row < 0 || !col_ok) continue;
+    *reinterpret_cast<uint2*>(p.q[owner] + static_cast<int64_t>(row) * (p.features >> 1) + (col >> 1)) = packed;
+    if ((lane & 3) == 0)
+      *reinterpret_cast<uint32_t*>(p.sf[owner] + static_cast<int64_t>(row) * (p.features >> 4) + (col >> 4)) = word;
+  }
+}
+
+// ------------------------------------------------ row-major scale factors -> atoms
+// One CTA per (128-row scale-factor tile, 2048-feature slice): the tile's rows are read
+// whole (coalesced) into shared memory and leave as 16-byte pieces of the 512-byte atoms,
+// piece (r % 32) of an atom holding the four factors of rows r, r+32, r+64, r+96.
+constexpr int kSwizzleCols = 128;  // scale-factor bytes of a row handled per CTA (2048 features)
+
+struct SwizzleParams {
+  const uint8_t* linear;   // (rows, features/16)
+  const int32_t* m_indptr;
+  int experts;
+  int features;
+  uint8_t* atoms;          // varlen atoms: expert e starts at atom row m_indptr[e]/128 + e
+};
+
+__global__ void __launch_bounds__(kThreads) ep_sf_swizzle_kernel(SwizzleParams p) {
+  __shared__ __align__(16) uint8_t s_rows[kTileRows][kSwizzleCols + 16];  // padded against bank conflicts
+  __shared__ int s_tile[3];  // first row, valid rows, found
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    // the expert whose atom rows contain this CTA's
+    s_tile[2] = 0;
+    const int atom_row = blockIdx.x;
+    for (int e = 0; e < p.experts; ++e) {
+      const int lo = __ldg(p.m_indptr + e), hi = __ldg(p.m_indptr + e + 1);
+      const int first = lo / kTileRows + e;
+      const int tiles = (hi - lo + kTileRows - 1) / kTileRows;
+      if (atom_row >= first && atom_row < first + tiles) {
+        const int local = atom_row - first;
+        s_tile[0] = lo + local * kTileRows;
+        s_tile[1] = min(kTileRows, hi - lo - local * kTileRows);
+        s_tile[2] = 1;
+        break;
+      }
+      if (atom_row < first) break;
+    }
+  }
+  __syncthreads();
+  if (s_tile[2] == 0) return;
+  const int row0 = s_tile[0], valid = s_tile[1];
+  const int row_bytes = p.features >> 4;
+  const int byte0 = blockIdx.y * kSwizzleCols;
+  const int bytes_here = min(kSwizzleCols, row_bytes - byte0);  // a multiple of 4
+  // coalesced load: 8 threads x 16 bytes per row
+  for (int i = tid; i < kTileRows * (kSwizzleCols / 16); i += kThreads) {
+    const int r = i / (kSwizzleCols / 16), piece = i % (kSwizzleCols / 16);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < valid && piece * 16 < bytes_here)
+      v = *reinterpret_cast<const uint4*>(p.linear + static_cast<int64_t>(row0 + r) * row_bytes + byte0 + piece * 16);
+    *reinterpret_cast<uint4*>(&s_rows[r][piece * 16]) = v;
+  }
+  __syncthreads();
+  const int atom_cols = p.features >> 6;
+  const int cols_here = bytes_here >> 2;
+  for (int i = tid; i < cols_here * 32; i += kThreads) {
+    const int c = i >> 5, rr = i & 31;
+    uint4 v;
+    v.x = *reinterpret_cast<const uint32_t*>(&s_rows[rr][c * 4]);
+    v.y = *reinterpret_cast<const uint32_t*>(&s_rows[rr + 32][c * 4]);
+    v.z = *reinterpret_cast<const uint32_t*>(&s_rows[rr + 64][c * 4]);
+    v.w = *reinterpret_cast<const uint32_t*>(&s_rows[rr + 96][c * 4]);
+    uint8_t* dst = p.atoms + (static_cast<int64_t>(blockIdx.x) * atom_cols + (byte0 >> 2) + c) * 512 + rr * 16;
+    *reinterpret_cast<uint4*>(dst) = v;
+  }
+}
+
+}  // namespace
+}  // namespace lm
+
+extern "C" int lm_ep_plan(const int32_t* counts_all, int world, int rank, int experts, int64_t max_rows,
+                          int64_t row_bytes, const uint64_t* return_base, int32_t* own_indptr,
+                          int32_t* dest_base, int32_t* owner_start, uint64_t* row_ptrs, int32_t* valid,
+                          lm_stream_t stream) {
+  using namespace lm;
+  LM_REQUIRE(counts_all && return_base && own_indptr && dest_base && owner_start && row_ptrs && valid,
+             "ep_plan: null pointer");
+  LM_REQUIRE(world >= 1 && world <= kMaxRanks, "ep_plan: 1..8 ranks");
+  LM_REQUIRE(rank >= 0 && rank < world, "ep_plan: rank out of range");
+  LM_REQUIRE(experts > 0 && experts <= kMaxExperts && experts % world == 0,
+             "ep_plan: 1..256 experts, divisible by the number of ranks");
+  LM_REQUIRE(max_rows > 0 && max_rows < (1ll << 31) && row_bytes > 0 && row_bytes % 16 == 0,
+             "ep_plan: bad buffer geometry");
+  PlanParams p{};
+  p.counts_all = counts_all;
+  p.world = world;
+  p.rank = rank;
+  p.experts = experts;
+  p.local_experts = experts / world;
+  p.max_rows = max_rows;
+  p.row_bytes = row_bytes;
+  for (int g = 0; g < world; ++g) p.return_base[g] = return_base[g];
+  p.own_indptr = own_indptr;
+  p.dest_base = dest_base;
+  p.owner_start = owner_start;
+  p.row_ptrs = row_ptrs;
+  p.valid = valid;
+  const int segments = p.local_experts * world;
+  ep_plan_kernel<<<segments < 296 ? segments : 296, kPlanThreads, 0, as_stream(stream)>>>(p);
+  LM_CUDA(cudaGetLastError());
+  return LM_OK;
+}
+
+extern "C" int lm_ep_quantize_send(const void* x, int64_t tokens, int features, int top_k, int world,
+                                   int experts, const int32_t* slots, const int32_t* topk_ids,
+                                   const int32_t* src_indptr, const int32_t* dest_base,
+                                   const int32_t* owner_start, const int32_t* valid,
+                                   const float* scale_pair, const uint64_t* q_base,
+                                   const uint64_t* sf_base, lm_stream_t stream) {
+  using namespace lm;
+  LM_REQUIRE(x && slots && topk_ids && src_indptr && dest_base && owner_start && valid && scale_pair &&
+                 q_base && sf_base,
+             "ep_quantize_send: null pointer");
+  LM_REQUIRE(features > 0 && features % 64 == 0, "ep_quantize_send: features must be a multiple of 64");
+  LM_REQUIRE(top_k > 0 && top_k <= 32 && tokens >= 0, "ep_quantize_send: bad sizes");
+  LM_REQUIRE(world >= 1 && world <= kMaxRanks && experts > 0 && experts % world == 0,
+             "ep_quantize_send: bad rank or expert count");
+  if (tokens == 0) return LM_OK;
+  SendParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.tokens = tokens;
+  p.features = features;
+  p.top_k = top_k;
+  p.local_experts = experts / world;
+  p.slots = slots;
+  p.topk_ids = topk_ids;
+  p.src_indptr = src_indptr;
+  p.dest_base = dest_base;
+  p.owner_start = owner_start;
+  p.valid = valid;
+  p.scale_pair = scale_pair;
+  for (int g = 0; g < world; ++g) {
+    LM_REQUIRE(q_base[g] != 0 && sf_base[g] != 0 && q_base[g] % 16 == 0 && sf_base[g] % 16 == 0,
+               "ep_quantize_send: peer buffers must be 16-byte aligned");
+    p.q[g] = reinterpret_cast<uint8_t*>(q_base[g]);
+    p.sf[g] = reinterpret_cast<uint8_t*>(sf_base[g]);
+  }
+  dim3 grid(static_cast<unsigned>((tokens + kWarps - 1) / kWarps), (features + kTileCols - 1) / kTileCols);
+  ep_quantize_send_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(p);
+  LM_CUDA(cudaGetLastError());
+  return LM_OK;
+}
+
+extern "C" int lm_ep_sf_swizzle(const uint8_t* linear, int64_t max_rows, int features,
+                                const int32_t* m_indptr, int experts, uint8_t* atoms,
+                                lm_stream_t stream) {
+  using namespace lm;
+  LM_REQUIRE(linear && m_indptr && atoms, "ep_sf_swizzle: null pointer");
+  LM_REQUIRE(features > 0 && features % 64 == 0, "ep_sf_swizzle: features must be a multiple of 64");
+  LM_REQUIRE(experts > 0 && experts <= kMaxExperts && max_rows > 0, "ep_sf_swizzle: bad sizes");
+  LM_REQUIRE((reinterpret_cast<uintptr_t>(linear) & 15) == 0 && (reinterpret_cast<uintptr_t>(atoms) & 15) == 0 &&
+                 (features / 16) % 16 == 0,
+             "ep_sf_swizzle: buffers and rows must be 16-byte aligned (features a multiple of 256)");
+  SwizzleParams p{linear, m_indptr, experts, features, atoms};
+  const int64_t atom_rows = (max_rows + kTileRows - 1) / kTileRows + experts;
+  dim3 grid(static_cast<unsigned>(atom_rows), (features / 16 + kSwizzleCols - 1) / kSwizzleCols);
+  ep_sf_swizzle_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(p);
+  LM_CUDA(cudaGetLastError());
+  return LM_OK;
+}

@@ -125,6 +125,7 @@ struct GemmParams {
   void* out;
   uint8_t* out_sf;
   const float* out_scale;
+  const uint64_t* out_row_ptrs;  // BF16 output: optional address of every output row
   int out_atom_cols;  // NVFP4 output: out_n / 64
   float clamp_limit;
   float sigmoid_alpha;
@@ -279,10 +280,6 @@ __device__ __forceinline__ void tc_wait_ld_regs(uint32_t* r) {
                  "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
                :
                : "memory");
-}
-
-__device__ __forceinline__ void tc_wait_ld() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 // Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of
@@ -774,6 +771,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int slice0 = kNB == 1 ? 0 : ((acc == 0) ? 2 + group : group);
         const int slice1 = kNB == 1 ? 1 : ((acc == 0) ? group : 2 + group);
         const bool rows_any = t.valid > quarter * 32;  // this warp owns at least one valid row
+        // rows may live anywhere (another GPU's buffer): lane l holds the address of row l
+        unsigned long long row_base = 0;
+        if (kOut == LM_OUT_BF16 && p.out_row_ptrs != nullptr && quarter * 32 + lane < t.valid)
+          row_base = __ldg(reinterpret_cast<const unsigned long long*>(p.out_row_ptrs) + t.row0 + quarter * 32 + lane);
         uint32_t va[32], vb[32];
         LM_PROF_LAP(lap[7]);
         tc_load32(taddr + slice0 * 64, va);
@@ -882,11 +883,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const int row = 4 * i + (lane >> 3);
+                __nv_bfloat16* dst = warp_out + static_cast<int64_t>(row) * p.n;
+                if (p.out_row_ptrs != nullptr)
+                  dst = reinterpret_cast<__nv_bfloat16*>(__shfl_sync(0xFFFFFFFFu, row_base, row));
 #ifdef LM_GEMM_PROFILE
                 if (p.debug_flags & 8) continue;
 #endif
-                if (row < rows_here && col < p.n)
-                  *reinterpret_cast<uint4*>(warp_out + static_cast<int64_t>(row) * p.n + col) = d[i];
+                if (row < rows_here && col < p.n) *reinterpret_cast<uint4*>(dst + col) = d[i];
               }
             }
             __syncwarp();
@@ -1077,6 +1080,11 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   p.out = a->out;
   p.out_sf = static_cast<uint8_t*>(a->out_sf);
   p.out_scale = a->out_scale;
+  if (a->out_row_ptrs != nullptr) {
+    LM_REQUIRE(a->out_kind == LM_OUT_BF16, "gemm: out_row_ptrs requires BF16 output");
+    LM_REQUIRE(a->n % 8 == 0, "gemm: out_row_ptrs requires N to be a multiple of 8");
+  }
+  p.out_row_ptrs = a->out_row_ptrs;
   p.clamp_limit = a->clamp_limit;
   p.sigmoid_alpha = a->sigmoid_alpha;
   p.up_bias = a->up_bias;

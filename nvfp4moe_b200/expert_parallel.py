@@ -84,6 +84,10 @@ class ExpertParallelExchange:
         return out
 
 
+def _align(value: int, to: int = 256) -> int:
+    return -(-value // to) * to
+
+
 class ExpertParallelMoE:
     """``InferenceMoE`` sharded expert-parallel across the ranks of ``group``.
 
@@ -91,33 +95,69 @@ class ExpertParallelMoE:
     a rank may receive in one step (default: ``world * max_tokens * top_k``, the
     worst case of every pair in the box landing on one rank, capped at the
     dispatch limit).
+
+    ``transport``:
+
+    * ``"peer"`` (default on CUDA with more than one rank): no row ever passes through a
+      collective.  The ranks gather each other's per-expert counts (1 KB), every rank derives
+      the whole route plan on its device, the quantizer stores packed rows and scale factors
+      straight into the owners' GEMM operand buffers and the fc2 GEMM stores its BF16 rows
+      straight into the source ranks' buffers, both through peer pointers over NVLink.  Two
+      4-byte all-reduces order the phases.  The host never reads a count: a step is a fixed
+      sequence of launches.
+    * ``"collective"``: BF16 rows travel through ``all_to_all_single`` both ways; one host
+      read per step sizes the exchange.  Works on any backend.
+
+    ``rank`` / ``world`` build a *virtual* rank that makes no ``torch.distributed`` call:
+    several of them in one process, joined by :func:`connect_virtual_ranks`, run the
+    peer transport on one GPU (tests, debugging).
     """
 
     def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top_k: int,
                  max_tokens: int, *, group=None, max_recv_rows: int | None = None,
-                 device: torch.device | str = "cuda", **plan_kwargs):
+                 device: torch.device | str = "cuda", transport: str | None = None,
+                 rank: int | None = None, world: int | None = None, **plan_kwargs):
         from .inference import InferenceMoE
         from .kernels.routing.dispatch import MAX_ASSIGNMENTS, MoEDispatch
 
-        self.exchange = ExpertParallelExchange(num_experts, group)
-        world = self.exchange.world
+        self.virtual = rank is not None
+        if self.virtual:
+            if world is None or not 0 <= rank < world or num_experts % world:
+                raise ValueError("a virtual rank needs 0 <= rank < world and experts divisible by world")
+            self.exchange = None
+            self.world, self.rank = world, rank
+        else:
+            self.exchange = ExpertParallelExchange(num_experts, group)
+            self.world, self.rank = self.exchange.world, self.exchange.rank
+        self.group = group
         self.hidden_size = hidden_size
         self.experts = num_experts
+        self.local_experts = num_experts // self.world
         self.topk = top_k
         self.max_tokens = max_tokens
         self.device = torch.device(device)
+        if transport is None:
+            transport = "peer" if (self.virtual or (self.world > 1 and self.device.type == "cuda")) else "collective"
+        if transport not in ("peer", "collective"):
+            raise ValueError("transport must be 'peer' or 'collective'")
+        if transport == "peer" and self.world > 8:
+            raise ValueError("the peer transport serves one NVLink domain of at most 8 ranks")
+        self.transport = transport
         rows = max_tokens * top_k
         if max_recv_rows is None:
-            max_recv_rows = min(world * rows, MAX_ASSIGNMENTS)
+            max_recv_rows = min(self.world * rows, MAX_ASSIGNMENTS)
         self.max_recv_rows = max_recv_rows
         # source side: sort local pairs by global expert
         self.source = MoEDispatch(max_tokens, num_experts, top_k, device=self.device)
         # owner side: a plan over the local experts whose "tokens" are received rows
-        self.local = InferenceMoE(hidden_size, intermediate_size, self.exchange.local_experts, 1,
+        self.local = InferenceMoE(hidden_size, intermediate_size, self.local_experts, 1,
                                   max_recv_rows, device=self.device, **plan_kwargs)
         self._out = torch.empty(max_tokens, hidden_size, dtype=torch.bfloat16, device=self.device)
         self._ones = torch.ones(max_recv_rows, 1, dtype=torch.float32, device=self.device)
         self.last_recv_rows = 0
+        self._peer = None
+        if transport == "peer":
+            self._build_peer_buffers()
 
     # weights and scales of the local expert shard: same calls as InferenceMoE
     def load_weights(self, *args):
@@ -136,17 +176,181 @@ class ExpertParallelMoE:
     def output(self) -> torch.Tensor:
         return self._out
 
+    # ------------------------------------------------------------ peer transport
+    def _build_peer_buffers(self):
+        """One arena per rank, at the same offsets on every rank: the packed rows and row-major
+        scale factors of the rows this rank computes (written by the sources) and the BF16 rows
+        this rank combines (written by the owners)."""
+        hidden, m, rows = self.hidden_size, self.max_recv_rows, self.max_tokens * self.topk
+        sf_rows = -(-m // 128) + self.local_experts
+        off_q = 0
+        off_sf = _align(m * (hidden // 2))
+        off_ret = off_sf + _align(m * (hidden // 16))
+        nbytes = off_ret + _align(rows * hidden * 2)
+        if self.virtual or self.world == 1:
+            arena = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+            bases = [arena.data_ptr()] * self.world  # rewritten by connect_virtual_ranks
+            handle = None
+        else:
+            import os
+
+            # plain peer mappings are all this path needs: no NVLink multicast binding
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm
+
+            group = self.group if self.group is not None else dist.group.WORLD
+            arena = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+            handle = symm.rendezvous(arena, group.group_name)
+            bases = [int(ptr) for ptr in handle.buffer_ptrs]
+            arena.zero_()
+        dev = self.device
+        peer = {
+            "arena": arena, "handle": handle, "offsets": (off_q, off_sf, off_ret),
+            "qx": arena[off_q : off_q + m * (hidden // 2)].view(m, hidden // 2).view(torch.float4_e2m1fn_x2),
+            # scale factors arrive row-major; the local swizzle kernel turns them into atoms
+            "sf_rows": arena[off_sf : off_sf + m * (hidden // 16)].view(m, hidden // 16),
+            "sfx": torch.zeros(1, sf_rows, hidden // 64, 32, 4, 4, dtype=torch.uint8, device=dev)
+            .view(torch.float8_e4m3fn),
+            "ret": arena[off_ret : off_ret + rows * hidden * 2].view(torch.bfloat16).view(rows, hidden),
+            "counts": torch.zeros(self.experts, dtype=torch.int32, device=dev),
+            "counts_all": torch.zeros(self.world, self.experts, dtype=torch.int32, device=dev),
+            "dest_base": torch.zeros(self.experts, dtype=torch.int32, device=dev),
+            "owner_start": torch.zeros(self.experts, dtype=torch.int32, device=dev),
+            "row_ptrs": torch.zeros(m, dtype=torch.int64, device=dev),
+            "valid": torch.ones(1, dtype=torch.int32, device=dev),
+            "token": torch.zeros(1, dtype=torch.int32, device=dev),
+            "gemms": None,
+        }
+        self._peer = peer
+        self._set_peer_bases(bases)
+
+    def _set_peer_bases(self, bases):
+        import ctypes
+
+        off_q, off_sf, off_ret = self._peer["offsets"]
+        array = ctypes.c_uint64 * self.world
+        self._peer["q_base"] = array(*[b + off_q for b in bases])
+        self._peer["sf_base"] = array(*[b + off_sf for b in bases])
+        self._peer["ret_base"] = array(*[b + off_ret for b in bases])
+
+    def _peer_gemms(self):
+        """fc1 reads the arena the sources fill; fc2 writes through the row-pointer table."""
+        peer, plan = self._peer, self.local
+        if peer["gemms"] is None:
+            m = self.max_recv_rows
+            _, qh, _, sfh = plan._views(m)
+            with torch.cuda.device(self.device):
+                fc1 = plan._new_gemm("fc1", m, torch.float4_e2m1fn_x2)
+                fc2 = plan._new_gemm("fc2", m)
+            fc1.prepare(peer["qx"], plan.qb1, qh, plan._m_indptr, peer["sfx"], plan.sfb1, plan._alpha1,
+                        output_sf=sfh, output_scale=plan._h_scale)
+            fc2.output_row_ptrs = peer["row_ptrs"]
+            fc2.prepare(qh, plan.qb2, plan._routed_out[:m], plan._m_indptr, sfh, plan.sfb2, plan._alpha2)
+            peer["gemms"] = (fc1, fc2)
+        return peer["gemms"]
+
+    def _phase_dispatch(self, topk_ids, topk_weights):
+        """Sort this rank's routes by global expert; returns the per-expert counts to gather."""
+        _, m_indptr, _, _ = self.source(topk_ids, topk_weights)
+        torch.sub(m_indptr[1:], m_indptr[:-1], out=self._peer["counts"])
+        return self._peer["counts"]
+
+    def _phase_send(self, x):
+        """Route plan from the gathered counts, then quantize once and store to the owners."""
+        from . import _lib
+
+        peer, plan, src = self._peer, self.local, self.source
+        plan._require_ready()
+        lib = _lib.lib()
+        stream = _lib.stream_handle()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.lm_ep_plan(peer["counts_all"].data_ptr(), self.world, self.rank, self.experts,
+                                      self.max_recv_rows, self.hidden_size * 2, peer["ret_base"],
+                                      plan._m_indptr.data_ptr(), peer["dest_base"].data_ptr(),
+                                      peer["owner_start"].data_ptr(), peer["row_ptrs"].data_ptr(),
+                                      peer["valid"].data_ptr(), stream))
+            _lib.check(lib.lm_ep_quantize_send(x.data_ptr(), x.shape[0], self.hidden_size, self.topk,
+                                               self.world, self.experts, src.slots.data_ptr(),
+                                               self._ids.data_ptr(), src.cu.data_ptr(),
+                                               peer["dest_base"].data_ptr(), peer["owner_start"].data_ptr(),
+                                               peer["valid"].data_ptr(), plan._x_scale.data_ptr(),
+                                               peer["q_base"], peer["sf_base"], stream))
+
+    def _phase_compute(self):
+        from . import _lib
+
+        fc1, fc2 = self._peer_gemms()
+        peer, plan = self._peer, self.local
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().lm_ep_sf_swizzle(peer["sf_rows"].data_ptr(), self.max_recv_rows,
+                                                   self.hidden_size, plan._m_indptr.data_ptr(),
+                                                   self.local_experts, peer["sfx"].data_ptr(),
+                                                   _lib.stream_handle()))
+        fc1.launch()
+        fc2.launch()
+
+    def _phase_combine(self, out):
+        from .kernels.routing.combine import moe_finalize
+
+        tokens = self._ids.shape[0]
+        output = self._out[:tokens] if out is None else out
+        moe_finalize(self._peer["ret"][: tokens * self.topk], self.source.slots, output, self.topk,
+                     weights=self.source.ps)
+        return output
+
+    def _fence(self):
+        """Every rank has finished the launches before this point (4-byte all-reduce)."""
+        if not self.virtual and self.world > 1:
+            dist.all_reduce(self._peer["token"], group=self.group)
+
+    def _check_inputs(self, x, topk_ids, topk_weights):
+        tokens = x.shape[0]
+        if tokens != self.source.num_tokens:
+            raise ValueError("the token count must match the configured per-rank batch")
+        if x.dtype != torch.bfloat16 or x.shape[1] != self.hidden_size or not x.is_contiguous():
+            raise ValueError(f"x must be contiguous BF16 with shape (tokens, {self.hidden_size})")
+        if topk_ids.dtype != torch.int32 or tuple(topk_ids.shape) != (tokens, self.topk):
+            raise ValueError(f"topk_ids must be int32 with shape ({tokens}, {self.topk})")
+        self._ids = topk_ids
+
+    @torch.no_grad()
+    def _run_peer(self, x, topk_ids, topk_weights, out):
+        self._check_inputs(x, topk_ids, topk_weights)
+        counts = self._phase_dispatch(topk_ids, topk_weights)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self._peer["counts_all"].view(-1), counts, group=self.group)
+        else:
+            self._peer["counts_all"].copy_(counts.view(1, -1))
+        self._phase_send(x)
+        self._fence()  # all packed rows have landed on their owners
+        self._phase_compute()
+        self._fence()  # all result rows have landed on their sources
+        return self._phase_combine(out)
+
+    def step_is_valid(self) -> bool:
+        """False when the last step was skipped because a rank would have received more than
+        ``max_recv_rows`` rows (reads one flag from the device: a synchronisation)."""
+        return self._peer is None or bool(self._peer["valid"].item())
+
     @torch.no_grad()
     def run(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
             *, out: torch.Tensor | None = None) -> torch.Tensor:
         """x [T, H] BF16, topk_ids [T, k] int32 global expert ids, topk_weights [T, k] FP32."""
+        if self.transport == "peer":
+            if self.virtual:
+                raise RuntimeError("virtual ranks are stepped together by run_virtual_ranks")
+            return self._run_peer(x, topk_ids, topk_weights, out)
+        return self._run_collective(x, topk_ids, topk_weights, out)
+
+    # ------------------------------------------------------ collective transport
+    @torch.no_grad()
+    def _run_collective(self, x, topk_ids, topk_weights, out):
         from .kernels.quantize.runtime import nvfp4_quantize_rowwise
         from .kernels.routing.combine import moe_finalize
         from .kernels.routing.dispatch import moe_dispatch
 
         ex = self.exchange
         tokens = x.shape[0]
-        rows = tokens * self.topk
         src = self.source
         if tokens != src.num_tokens:
             raise ValueError("the token count must match the configured per-rank batch")
@@ -193,6 +397,37 @@ class ExpertParallelMoE:
     __call__ = run
 
 
+def connect_virtual_ranks(layers) -> None:
+    """Join virtual ranks that live in one process (one GPU): each one's peer table points at
+    the others' arenas."""
+    layers = list(layers)
+    world = layers[0].world
+    if sorted(layer.rank for layer in layers) != list(range(world)) or any(not l.virtual for l in layers):
+        raise ValueError("connect_virtual_ranks needs one virtual rank per rank of the world")
+    ordered = sorted(layers, key=lambda layer: layer.rank)
+    bases = [layer._peer["arena"].data_ptr() for layer in ordered]
+    for layer in ordered:
+        layer._set_peer_bases(bases)
+
+
+@torch.no_grad()
+def run_virtual_ranks(layers, batches, outs=None):
+    """One expert-parallel step of all virtual ranks on the current stream, phase by phase;
+    stream order stands in for the cross-rank fences.  ``batches[r] = (x, topk_ids, topk_weights)``."""
+    ordered = sorted(layers, key=lambda layer: layer.rank)
+    counts = []
+    for layer, (x, ids, w) in zip(ordered, batches):
+        layer._check_inputs(x, ids, w)
+        counts.append(layer._phase_dispatch(ids, w))
+    gathered = torch.stack(counts)
+    for layer, (x, _, _) in zip(ordered, batches):
+        layer._peer["counts_all"].copy_(gathered)
+        layer._phase_send(x)
+    for layer in ordered:
+        layer._phase_compute()
+    return [layer._phase_combine(None if outs is None else outs[layer.rank]) for layer in ordered]
+
+
 def reference_step(x, topk_ids, topk_weights, compute_rows: Callable, exchange: ExpertParallelExchange):
     """The same exchange pattern on plain torch ops, for host-side (gloo) tests.
 
@@ -217,5 +452,5 @@ def reference_step(x, topk_ids, topk_weights, compute_rows: Callable, exchange: 
     return out
 
 
-__all__ = ["ExpertParallelExchange", "ExpertParallelMoE", "owner_splits", "received_expert_ids",
-           "reference_step"]
+__all__ = ["ExpertParallelExchange", "ExpertParallelMoE", "connect_virtual_ranks", "owner_splits",
+           "received_expert_ids", "reference_step", "run_virtual_ranks"]

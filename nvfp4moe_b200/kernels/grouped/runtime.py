@@ -157,6 +157,11 @@ class GroupedNvfp4Gemm:
         self.device = torch.cuda.current_device()
         self.stages = 6
         self.max_ctas = 0  # 0 = one CTA per SM; tests lower it to run many tiles per CTA
+        # Set before ``prepare``: int64 CUDA tensor with one 16-byte aligned address per row.
+        # Every BF16 output row is then written to its own address (which may lie in a peer
+        # GPU's memory) instead of ``out``; the expert-parallel layer returns rows to their
+        # source ranks this way.
+        self.output_row_ptrs = None
         self._plan = None
 
     def prepare(
@@ -251,12 +256,21 @@ class GroupedNvfp4Gemm:
         args.alpha = alpha.data_ptr()
         args.out_sf = output_sf.data_ptr() if nvfp4_out else None
         args.out_scale = output_scale.data_ptr() if nvfp4_out else None
+        output_row_ptrs = self.output_row_ptrs
+        if output_row_ptrs is not None:
+            if self.output_dtype != torch.bfloat16:
+                raise ValueError("output_row_ptrs requires BF16 output")
+            if (not output_row_ptrs.is_cuda or output_row_ptrs.dtype != torch.int64
+                    or output_row_ptrs.ndim != 1 or output_row_ptrs.shape[0] < rows
+                    or not output_row_ptrs.is_contiguous()):
+                raise ValueError(f"output_row_ptrs must be a contiguous int64 CUDA tensor of {rows} addresses")
+            args.out_row_ptrs = output_row_ptrs.data_ptr()
         plan = _lib.GemmPlan()
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().lm_gemm_prepare(ctypes.byref(args), ctypes.byref(plan)))
         self._plan = plan
         # keep operands alive for as long as the plan may launch
-        self._keepalive = (a, b, out, cu, sfa, sfb, alpha, output_sf, output_scale)
+        self._keepalive = (a, b, out, cu, sfa, sfb, alpha, output_sf, output_scale, output_row_ptrs)
 
     def launch(self):
         if self._plan is None:

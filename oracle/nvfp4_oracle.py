@@ -305,6 +305,50 @@ def dispatch(topk_ids: torch.Tensor, topk_weights: torch.Tensor, experts: int,
 
 
 # --------------------------------------------------------------------------
+# expert-parallel route plan (no reference code: the reference leaves the exchange to the
+# host framework, README.md:227-228; this states the row order the peer transport uses)
+# --------------------------------------------------------------------------
+
+
+def ep_route_plan(counts_all, rank: int):
+    """Where rows go when ``world`` ranks shard the experts contiguously.
+
+    ``counts_all[g][e]`` = rows rank ``g`` routed to global expert ``e``.  On its owner an
+    expert's rows are ordered by source rank, within a source in the source's own expert-major
+    order.  Returns for ``rank``: ``own_indptr`` (bounds of the rows it receives),
+    ``dest_base[e]`` (owner row where its rows of expert e begin), ``owner_start[e]`` (owner
+    row where expert e begins), ``origin`` (for every row it receives: source rank, source row)
+    and ``owner_rows`` (rows every rank receives).
+    """
+    counts = [[int(v) for v in row] for row in counts_all]
+    world, experts = len(counts), len(counts[0])
+    local = experts // world
+    src_start = []
+    for g in range(world):
+        run, starts = 0, []
+        for e in range(experts):
+            starts.append(run)
+            run += counts[g][e]
+        src_start.append(starts)
+    total = [sum(counts[g][e] for g in range(world)) for e in range(experts)]
+    owner_start, owner_rows = [0] * experts, []
+    for o in range(world):
+        run = 0
+        for l in range(local):
+            owner_start[o * local + l] = run
+            run += total[o * local + l]
+        owner_rows.append(run)
+    dest_base = [owner_start[e] + sum(counts[g][e] for g in range(rank)) for e in range(experts)]
+    own_indptr = [owner_start[rank * local + l] for l in range(local)] + [owner_rows[rank]]
+    origin = []
+    for l in range(local):
+        e = rank * local + l
+        for g in range(world):
+            origin += [(g, src_start[g][e] + i) for i in range(counts[g][e])]
+    return own_indptr, dest_base, owner_start, origin, owner_rows
+
+
+# --------------------------------------------------------------------------
 # grouped / dense GEMM on dequantized operands
 # --------------------------------------------------------------------------
 

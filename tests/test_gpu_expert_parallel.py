@@ -61,17 +61,24 @@ def _worker(rank: int, world: int, port: int, results):
 
         local = EXPERTS // world
         sl = slice(rank * local, (rank + 1) * local)
-        sharded = ExpertParallelMoE(HIDDEN, INTER, EXPERTS, TOPK, TOKENS, device=device)
-        # one weight scale for the whole layer, as the single-GPU plan derives it
-        sharded.local.load_packed_weights(plain.qb1[sl].contiguous(), plain.sfb1[sl].contiguous(),
-                                          plain.p_w1, plain.qb2[sl].contiguous(),
-                                          plain.sfb2[sl].contiguous(), plain.p_w2)
-        sharded.set_activation_scales(2e-3, 1e-3)
-        got = sharded(x, ids, w).clone()
-        again = sharded(x, ids, w).clone()
-        torch.cuda.synchronize()
-        results[rank] = (bool(torch.equal(got, expected)), bool(torch.equal(got, again)),
-                         int(sharded.last_recv_rows))
+        outcome = {}
+        for transport in ("peer", "collective"):
+            sharded = ExpertParallelMoE(HIDDEN, INTER, EXPERTS, TOPK, TOKENS, device=device,
+                                        transport=transport)
+            # one weight scale for the whole layer, as the single-GPU plan derives it
+            sharded.local.load_packed_weights(plain.qb1[sl].contiguous(), plain.sfb1[sl].contiguous(),
+                                              plain.p_w1, plain.qb2[sl].contiguous(),
+                                              plain.sfb2[sl].contiguous(), plain.p_w2)
+            sharded.set_activation_scales(2e-3, 1e-3)
+            got = sharded(x, ids, w).clone()
+            again = sharded(x, ids, w).clone()
+            torch.cuda.synchronize()
+            received = (int(sharded.last_recv_rows) if transport == "collective"
+                        else int(sharded.local._m_indptr[-1]))
+            outcome[transport] = (bool(torch.equal(got, expected)), bool(torch.equal(got, again)),
+                                  received, sharded.step_is_valid())
+            dist.barrier()
+        results[rank] = outcome
     finally:
         dist.destroy_process_group()
 
@@ -80,6 +87,8 @@ def test_two_rank_layer_equals_single_gpu_layer():
     world = 2
     results = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
-    assert results[0][:2] == (True, True)
-    assert results[1][:2] == (True, True)
-    assert results[0][2] + results[1][2] == 2 * TOKENS * TOPK
+    for transport in ("peer", "collective"):
+        first, second = results[0][transport], results[1][transport]
+        assert first[:2] == (True, True) and first[3], transport
+        assert second[:2] == (True, True) and second[3], transport
+        assert first[2] + second[2] == 2 * TOKENS * TOPK, transport
