@@ -262,7 +262,9 @@ def run_ours(args):
         layer.set_activation_scales(scales[0:1], scales[1:2])
         del probe
         step = lambda: layer.run(x, ids, w)
-        launches_per_step = 8  # 2x2 dispatch kernels, quantize, fc1, fc2, combine
+        # dispatch count + scatter, count exchange, route plan, quantize-and-send, fence,
+        # scale-factor swizzle, fc1, fc2, fence, combine
+        launches_per_step = 11
     del gate, up, down
     torch.cuda.empty_cache()
 

@@ -64,11 +64,12 @@ const char* lm_last_error_string(void);
 int lm_sm_count(int* out);
 
 /*
- * Device-side status word of the GEMM kernels.  A kernel whose bounded wait
- * on a barrier ran out sets a bit here and returns instead of hanging.
- * Synchronises the stream.  *out == 0 means no kernel has reported a problem
- * since the last lm_device_status_clear().
+ * Device-side status word.  A kernel whose bounded wait ran out sets a bit here and returns
+ * instead of hanging: bits 0-3 the GEMM's producer / MMA / epilogue / scale-factor roles,
+ * LM_STATUS_EP_TIMEOUT a cross-rank signal that never arrived.  Synchronises the stream.
+ * *out == 0 means no kernel has reported a problem since the last lm_device_status_clear().
  */
+#define LM_STATUS_EP_TIMEOUT 16
 int lm_device_status(uint32_t* out, lm_stream_t stream);
 int lm_device_status_clear(lm_stream_t stream);
 
@@ -280,6 +281,21 @@ int lm_ep_quantize_send(const void* x, int64_t tokens, int features, int top_k, 
                         const int32_t* src_indptr, const int32_t* dest_base,
                         const int32_t* owner_start, const int32_t* valid, const float* scale_pair,
                         const uint64_t* q_base, const uint64_t* sf_base, lm_stream_t stream);
+
+/*
+ * Cross-rank signal, one launch of one CTA per rank; the ranks must run on different GPUs.
+ * With m_indptr: first stores this rank's per-expert row counts (m_indptr[e+1] - m_indptr[e])
+ * as row `rank` of every rank's (world, experts) table.  Then every rank tells every rank that
+ * it has reached `epoch` and waits until all of them have; stores this rank made to peer memory
+ * in earlier launches of the stream are ordered before the signal.  `epoch` must grow by one
+ * with every call, identically on all ranks.  The wait gives up after timeout_ms (0 = ten
+ * seconds; counted in SM cycles at a nominal 2 GHz) and sets LM_STATUS_EP_TIMEOUT.
+ *   counts_all_base, signal_base  HOST arrays (world) of the addresses of every rank's count
+ *                                 table and signal pad (world uint32 words, zero at start)
+ */
+int lm_ep_signal(const int32_t* m_indptr, int experts, int world, int rank, uint32_t epoch,
+                 const uint64_t* counts_all_base, const uint64_t* signal_base, int timeout_ms,
+                 lm_stream_t stream);
 
 /*
  * Row-major scale factors (max_rows, features/16) -> varlen atoms as LM_SF_VARLEN lays them

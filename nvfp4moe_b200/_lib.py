@@ -82,6 +82,11 @@ _SIGNATURES = {
         [c_ptr, c_i64, c_i32, c_i32, c_i32, c_i32, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
          ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64), c_ptr],
     ),
+    "lm_ep_signal": (
+        c_i32,
+        [c_ptr, c_i32, c_i32, c_i32, ctypes.c_uint32, ctypes.POINTER(ctypes.c_uint64),
+         ctypes.POINTER(ctypes.c_uint64), c_i32, c_ptr],
+    ),
     "lm_ep_sf_swizzle": (c_i32, [c_ptr, c_i64, c_i32, c_ptr, c_i32, c_ptr, c_ptr]),
     "lm_dispatch_scratch_elems": (c_i64, [c_i64, c_i32]),
     "lm_dispatch": (

@@ -18,6 +18,9 @@
 namespace lm {
 namespace {
 
+// status word of this file's kernels (read and cleared together with the GEMM's)
+__device__ uint32_t g_ep_status = 0;
+
 constexpr int kMaxRanks = LM_EP_MAX_RANKS;
 constexpr int kMaxExperts = 256;
 constexpr int kPlanThreads = 256;
@@ -230,7 +233,67 @@ __global__ void __launch_bounds__(kThreads) ep_sf_swizzle_kernel(SwizzleParams p
   }
 }
 
+// ------------------------------------------------ cross-rank signal: exchange and barrier
+// One CTA per rank.  Optionally stores this rank's per-expert row counts into every rank's
+// gathered table, then tells every rank "I am at `epoch`" (one release store into each
+// rank's signal pad) and waits until every rank has said the same (acquire loads of its own
+// pad).  Everything this rank stored to peer memory in earlier launches of the stream is
+// ordered before the signal.  The wait is bounded (ten seconds unless the caller says
+// otherwise): when it runs out the kernel sets the status bit LM_STATUS_EP_TIMEOUT and
+// returns.  Ranks must run on different GPUs.
+constexpr long long kCyclesPerMs = 2000000ll;  // at about 2 GHz
+
+struct SignalParams {
+  const int32_t* m_indptr;  // nullptr: barrier only
+  int experts;
+  int world;
+  int rank;
+  uint32_t epoch;
+  long long wait_cycles;
+  int32_t* counts_all[kMaxRanks];  // every rank's (world, experts) table
+  uint32_t* signal[kMaxRanks];     // every rank's pad of `world` words
+};
+
+__global__ void __launch_bounds__(256) ep_signal_kernel(SignalParams p) {
+  const int tid = threadIdx.x;
+  if (p.m_indptr != nullptr) {
+    for (int i = tid; i < p.experts; i += blockDim.x) {
+      const int count = __ldg(p.m_indptr + i + 1) - __ldg(p.m_indptr + i);
+      for (int g = 0; g < p.world; ++g) p.counts_all[g][p.rank * p.experts + i] = count;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < p.world) {
+    uint32_t* theirs = p.signal[tid] + p.rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(p.epoch) : "memory");
+    const uint32_t* mine = p.signal[p.rank] + tid;
+    const long long start = clock64();
+    while (true) {
+      uint32_t seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+      if (static_cast<int32_t>(seen - p.epoch) >= 0) break;
+      if (clock64() - start > p.wait_cycles) {
+        atomicOr(&g_ep_status, static_cast<uint32_t>(LM_STATUS_EP_TIMEOUT));
+        break;
+      }
+    }
+  }
+}
+
 }  // namespace
+
+int ep_status_read(uint32_t* out) {
+  LM_CUDA(cudaMemcpyFromSymbol(out, g_ep_status, sizeof(uint32_t)));
+  return LM_OK;
+}
+
+int ep_status_clear() {
+  const uint32_t zero = 0;
+  LM_CUDA(cudaMemcpyToSymbol(g_ep_status, &zero, sizeof(uint32_t)));
+  return LM_OK;
+}
+
 }  // namespace lm
 
 extern "C" int lm_ep_plan(const int32_t* counts_all, int world, int rank, int experts, int64_t max_rows,
@@ -320,6 +383,35 @@ extern "C" int lm_ep_sf_swizzle(const uint8_t* linear, int64_t max_rows, int fea
   const int64_t atom_rows = (max_rows + kTileRows - 1) / kTileRows + experts;
   dim3 grid(static_cast<unsigned>(atom_rows), (features / 16 + kSwizzleCols - 1) / kSwizzleCols);
   ep_sf_swizzle_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(p);
+  LM_CUDA(cudaGetLastError());
+  return LM_OK;
+}
+
+extern "C" int lm_ep_signal(const int32_t* m_indptr, int experts, int world, int rank, uint32_t epoch,
+                            const uint64_t* counts_all_base, const uint64_t* signal_base, int timeout_ms,
+                            lm_stream_t stream) {
+  using namespace lm;
+  LM_REQUIRE(signal_base, "ep_signal: null pointer");
+  LM_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, "ep_signal: bad rank");
+  LM_REQUIRE(m_indptr == nullptr || (counts_all_base != nullptr && experts > 0 && experts <= kMaxExperts),
+             "ep_signal: the count exchange needs the gathered tables");
+  SignalParams p{};
+  p.m_indptr = m_indptr;
+  p.experts = experts;
+  p.world = world;
+  p.rank = rank;
+  p.epoch = epoch;
+  LM_REQUIRE(timeout_ms >= 0 && timeout_ms <= 60000, "ep_signal: timeout of 0 (default) to 60000 ms");
+  p.wait_cycles = (timeout_ms > 0 ? timeout_ms : 10000) * kCyclesPerMs;
+  for (int g = 0; g < world; ++g) {
+    LM_REQUIRE(signal_base[g] != 0 && signal_base[g] % 4 == 0, "ep_signal: bad signal pad");
+    p.signal[g] = reinterpret_cast<uint32_t*>(signal_base[g]);
+    if (m_indptr != nullptr) {
+      LM_REQUIRE(counts_all_base[g] != 0 && counts_all_base[g] % 4 == 0, "ep_signal: bad count table");
+      p.counts_all[g] = reinterpret_cast<int32_t*>(counts_all_base[g]);
+    }
+  }
+  ep_signal_kernel<<<1, 256, 0, as_stream(stream)>>>(p);
   LM_CUDA(cudaGetLastError());
   return LM_OK;
 }

@@ -1151,6 +1151,10 @@ extern "C" int lm_device_status(uint32_t* out, lm_stream_t stream) {
   LM_REQUIRE(out, "device_status: null pointer");
   LM_CUDA(cudaStreamSynchronize(as_stream(stream)));
   LM_CUDA(cudaMemcpyFromSymbol(out, g_status, sizeof(uint32_t)));
+  uint32_t ep = 0;
+  const int rc = ep_status_read(&ep);
+  if (rc != LM_OK) return rc;
+  *out |= ep;
   return LM_OK;
 }
 
@@ -1159,7 +1163,7 @@ extern "C" int lm_device_status_clear(lm_stream_t stream) {
   const uint32_t zero = 0;
   LM_CUDA(cudaStreamSynchronize(as_stream(stream)));
   LM_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(uint32_t)));
-  return LM_OK;
+  return ep_status_clear();
 }
 
 #ifdef LM_GEMM_PROFILE

@@ -102,9 +102,11 @@ class ExpertParallelMoE:
       collective.  The ranks gather each other's per-expert counts (1 KB), every rank derives
       the whole route plan on its device, the quantizer stores packed rows and scale factors
       straight into the owners' GEMM operand buffers and the fc2 GEMM stores its BF16 rows
-      straight into the source ranks' buffers, both through peer pointers over NVLink.  Two
-      4-byte all-reduces order the phases.  The host never reads a count: a step is a fixed
-      sequence of launches.
+      straight into the source ranks' buffers, both through peer pointers over NVLink.  The
+      counts and the two fences between the phases travel through signal pads in the same
+      peer memory (``signals="peer"``, one single-CTA kernel each, bounded waits) or through
+      NCCL (``signals="nccl"``).  The host never reads a count: a step is a fixed sequence of
+      launches.
     * ``"collective"``: BF16 rows travel through ``all_to_all_single`` both ways; one host
       read per step sizes the exchange.  Works on any backend.
 
@@ -116,7 +118,8 @@ class ExpertParallelMoE:
     def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top_k: int,
                  max_tokens: int, *, group=None, max_recv_rows: int | None = None,
                  device: torch.device | str = "cuda", transport: str | None = None,
-                 rank: int | None = None, world: int | None = None, **plan_kwargs):
+                 rank: int | None = None, world: int | None = None, signals: str = "peer",
+                 signal_timeout_ms: int = 0, **plan_kwargs):
         from .inference import InferenceMoE
         from .kernels.routing.dispatch import MAX_ASSIGNMENTS, MoEDispatch
 
@@ -143,6 +146,10 @@ class ExpertParallelMoE:
         if transport == "peer" and self.world > 8:
             raise ValueError("the peer transport serves one NVLink domain of at most 8 ranks")
         self.transport = transport
+        if signals not in ("peer", "nccl"):
+            raise ValueError("signals must be 'peer' or 'nccl'")
+        self.signals = signals
+        self.signal_timeout_ms = int(signal_timeout_ms)
         rows = max_tokens * top_k
         if max_recv_rows is None:
             max_recv_rows = min(self.world * rows, MAX_ASSIGNMENTS)
@@ -186,7 +193,9 @@ class ExpertParallelMoE:
         off_q = 0
         off_sf = _align(m * (hidden // 2))
         off_ret = off_sf + _align(m * (hidden // 16))
-        nbytes = off_ret + _align(rows * hidden * 2)
+        off_cnt = off_ret + _align(rows * hidden * 2)
+        off_sig = off_cnt + _align(self.world * self.experts * 4)
+        nbytes = off_sig + 256
         if self.virtual or self.world == 1:
             arena = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
             bases = [arena.data_ptr()] * self.world  # rewritten by connect_virtual_ranks
@@ -203,9 +212,12 @@ class ExpertParallelMoE:
             handle = symm.rendezvous(arena, group.group_name)
             bases = [int(ptr) for ptr in handle.buffer_ptrs]
             arena.zero_()
+            # no rank may signal into a pad that its owner has yet to clear
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
         dev = self.device
         peer = {
-            "arena": arena, "handle": handle, "offsets": (off_q, off_sf, off_ret),
+            "arena": arena, "handle": handle, "offsets": (off_q, off_sf, off_ret, off_cnt, off_sig),
             "qx": arena[off_q : off_q + m * (hidden // 2)].view(m, hidden // 2).view(torch.float4_e2m1fn_x2),
             # scale factors arrive row-major; the local swizzle kernel turns them into atoms
             "sf_rows": arena[off_sf : off_sf + m * (hidden // 16)].view(m, hidden // 16),
@@ -213,12 +225,14 @@ class ExpertParallelMoE:
             .view(torch.float8_e4m3fn),
             "ret": arena[off_ret : off_ret + rows * hidden * 2].view(torch.bfloat16).view(rows, hidden),
             "counts": torch.zeros(self.experts, dtype=torch.int32, device=dev),
-            "counts_all": torch.zeros(self.world, self.experts, dtype=torch.int32, device=dev),
+            "counts_all": arena[off_cnt : off_cnt + self.world * self.experts * 4].view(torch.int32)
+            .view(self.world, self.experts),
             "dest_base": torch.zeros(self.experts, dtype=torch.int32, device=dev),
             "owner_start": torch.zeros(self.experts, dtype=torch.int32, device=dev),
             "row_ptrs": torch.zeros(m, dtype=torch.int64, device=dev),
             "valid": torch.ones(1, dtype=torch.int32, device=dev),
             "token": torch.zeros(1, dtype=torch.int32, device=dev),
+            "epoch": 0,
             "gemms": None,
         }
         self._peer = peer
@@ -227,8 +241,10 @@ class ExpertParallelMoE:
     def _set_peer_bases(self, bases):
         import ctypes
 
-        off_q, off_sf, off_ret = self._peer["offsets"]
+        off_q, off_sf, off_ret, off_cnt, off_sig = self._peer["offsets"]
         array = ctypes.c_uint64 * self.world
+        self._peer["cnt_base"] = array(*[b + off_cnt for b in bases])
+        self._peer["sig_base"] = array(*[b + off_sig for b in bases])
         self._peer["q_base"] = array(*[b + off_q for b in bases])
         self._peer["sf_base"] = array(*[b + off_sf for b in bases])
         self._peer["ret_base"] = array(*[b + off_ret for b in bases])
@@ -298,10 +314,29 @@ class ExpertParallelMoE:
                      weights=self.source.ps)
         return output
 
-    def _fence(self):
-        """Every rank has finished the launches before this point (4-byte all-reduce)."""
-        if not self.virtual and self.world > 1:
-            dist.all_reduce(self._peer["token"], group=self.group)
+    def _signal(self, m_indptr=None):
+        """Every rank has finished the launches before this point; with ``m_indptr`` the ranks
+        also leave their per-expert counts in each other's tables.  One small kernel per rank
+        over the signal pads in peer memory (``signals="nccl"``: collectives instead)."""
+        if self.virtual or self.world == 1:
+            return
+        peer = self._peer
+        if self.signals == "nccl":
+            if m_indptr is not None:
+                torch.sub(m_indptr[1:], m_indptr[:-1], out=peer["counts"])
+                dist.all_gather_into_tensor(peer["counts_all"].view(-1), peer["counts"], group=self.group)
+            else:
+                dist.all_reduce(peer["token"], group=self.group)
+            return
+        from . import _lib
+
+        peer["epoch"] += 1
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().lm_ep_signal(None if m_indptr is None else m_indptr.data_ptr(),
+                                               self.experts, self.world, self.rank,
+                                               peer["epoch"] & 0xFFFFFFFF, peer["cnt_base"],
+                                               peer["sig_base"], self.signal_timeout_ms,
+                                               _lib.stream_handle()))
 
     def _check_inputs(self, x, topk_ids, topk_weights):
         tokens = x.shape[0]
@@ -316,15 +351,15 @@ class ExpertParallelMoE:
     @torch.no_grad()
     def _run_peer(self, x, topk_ids, topk_weights, out):
         self._check_inputs(x, topk_ids, topk_weights)
-        counts = self._phase_dispatch(topk_ids, topk_weights)
-        if self.world > 1:
-            dist.all_gather_into_tensor(self._peer["counts_all"].view(-1), counts, group=self.group)
+        if self.world == 1:
+            self._peer["counts_all"].copy_(self._phase_dispatch(topk_ids, topk_weights).view(1, -1))
         else:
-            self._peer["counts_all"].copy_(counts.view(1, -1))
+            _, m_indptr, _, _ = self.source(topk_ids, topk_weights)
+            self._signal(m_indptr)  # every rank's counts are in every rank's table
         self._phase_send(x)
-        self._fence()  # all packed rows have landed on their owners
+        self._signal()  # all packed rows have landed on their owners
         self._phase_compute()
-        self._fence()  # all result rows have landed on their sources
+        self._signal()  # all result rows have landed on their sources
         return self._phase_combine(out)
 
     def step_is_valid(self) -> bool:

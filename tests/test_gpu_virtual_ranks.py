@@ -182,3 +182,28 @@ def test_sf_swizzle_matches_varlen_layout(features):
     mask = used.repeat_interleave((features // 64) * 512)
     assert torch.equal(got[mask], want[mask])
     assert bool((got[~mask] == 0xEE).all())
+
+
+def test_signal_wait_runs_out_and_reports():
+    """A rank whose peer never signals gives up after the limit and sets the status bit; the
+    context stays usable.  (One launch on one GPU: nothing else waits on it.)"""
+    from nvfp4moe_b200 import _lib
+
+    dev = torch.device("cuda", 0)
+    _lib.check(_lib.lib().lm_device_status_clear(_lib.stream_handle()))
+    pads = torch.zeros(2, 64, dtype=torch.int32, device=dev)      # pad of rank 0 and of the absent rank 1
+    tables = torch.zeros(2, 2, 8, dtype=torch.int32, device=dev)  # both ranks' (world, experts) tables
+    m_indptr = torch.tensor([0, 3, 3, 4, 9, 9, 9, 10, 12], dtype=torch.int32, device=dev)
+    sig = (ctypes.c_uint64 * 2)(pads[0].data_ptr(), pads[1].data_ptr())
+    cnt = (ctypes.c_uint64 * 2)(tables[0].data_ptr(), tables[1].data_ptr())
+    _lib.check(_lib.lib().lm_ep_signal(m_indptr.data_ptr(), 8, 2, 0, 1, cnt, sig, 20, _lib.stream_handle()))
+    assert _lib.device_status() == 16  # LM_STATUS_EP_TIMEOUT
+    # its own part was done before the wait: counts in both tables, signals in both pads
+    assert tables[0, 0].tolist() == [3, 0, 1, 5, 0, 0, 1, 2] and tables[1, 0].tolist() == tables[0, 0].tolist()
+    assert int(pads[0, 0]) == 1 and int(pads[1, 0]) == 1 and int(pads[0, 1]) == 0
+    _lib.check(_lib.lib().lm_device_status_clear(_lib.stream_handle()))
+    assert _lib.device_status() == 0
+    # once the peer's word is there the same call returns at once
+    pads[0, 1] = 2
+    _lib.check(_lib.lib().lm_ep_signal(None, 8, 2, 0, 2, None, sig, 20, _lib.stream_handle()))
+    assert _lib.device_status() == 0
