@@ -207,6 +207,13 @@ def _stage_times(plan, x, ids, w, iters=20):
     return out
 
 
+# DRAM bytes (read + write) of one launch at the full workload, from the committed ncu capture
+# of the half-size case (128 experts, 4096 tokens) scaled by the units processed (x2).
+NCU_DRAM_BYTES = {"fc1": 2 * (189.9 + 8.6) * 1e6, "fc2": 2 * (85.3 + 80.1) * 1e6,
+                  "combine": 2 * (134.5 + 9.3) * 1e6, "quantize": 2 * 17.03 * 1e6,
+                  "dispatch": 2 * 0.44 * 1e6}
+
+
 def _algorithmic_bytes(rows, tokens, e_local):
     q = 0.5625  # packed FP4 + one scale byte per 16 values
     return {
@@ -345,14 +352,16 @@ def run_ours(args):
         peak, kind = _peaks()
         achieved = algo[top] / (stage_ms[top] * 1e-3) / 1e9
         line["roofline"] = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peak,
-                            "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                            "peak_source": kind}
+                            "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_DRAM_BYTES.get(top),
+                            "peak_source": kind,
+                            "traffic_source": "ncu capture of the half-size case, scaled by 2 (profiles/)"}
         line["stages_ms"] = stage_ms
         line["stages_gbs"] = {k: algo[k] / (v * 1e-3) / 1e9 for k, v in stage_ms.items()}
         flops = 2.0 * TOKENS * TOPK * HIDDEN * INTER * 3
         line["gemm_tflops"] = {"fc1": 2.0 * TOKENS * TOPK * 2 * INTER * HIDDEN / (stage_ms["fc1"] * 1e-3) / 1e12,
                                "fc2": 2.0 * TOKENS * TOPK * HIDDEN * INTER / (stage_ms["fc2"] * 1e-3) / 1e12,
                                "layer_flop": flops}
+        line["gemm_frac_of_9000_tflops"] = {k: line["gemm_tflops"][k] / 9000.0 for k in ("fc1", "fc2")}
         if not args.no_cpu:
             threads = os.cpu_count() or 1
             cpu_step, cpu_tokens, sample = _cpu_sample(threads)
