@@ -403,6 +403,201 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&b);
 }
 
+// ------------------------------------------------------------ epilogue of one tile
+// What an epilogue warp needs to drain its share of one accumulator.
+struct DrainContext {
+  uint32_t lane_base;        // TMEM address of the warp's 32 lanes, column 0
+  uint32_t warp_store;       // the warp's BF16 staging in shared memory
+  uint32_t bar_shared_cols;  // signalled when the columns both accumulators use are in registers
+  uint32_t bar_acc_empty;    // signalled when the whole accumulator is in registers
+  bool remote;               // the two barriers are cluster addresses (the pair leader's)
+  uint32_t acc1_col;         // 256-column tiles: first TMEM column of accumulator 1
+  bool wide_overlap;         // 256-column tiles: the accumulators share three 64-column slices
+  int group;                 // epilogue group of the warp (0 or 1)
+  int quarter;               // TMEM lane quarter of the warp
+  int lane;
+  float alpha;
+  float inv_h;               // NVFP4 output: reciprocal of the output's tensor scale
+};
+
+// Arrive on a barrier of this CTA or, `remote`, of the pair's leader (a cluster address).  The
+// remote form is relaxed: every use orders accesses to TMEM, which tcgen05.wait::ld/st and the
+// tcgen05 fences on both sides cover, and an arrive with cluster-scope release semantics took
+// thousands of cycles here (the MMAs then spent most of their time waiting for it).
+__device__ __forceinline__ void signal_barrier(uint32_t bar, bool remote) {
+  if (remote) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+  } else {
+    mbar_arrive(bar);
+  }
+}
+
+template <int kOut, int kAct, int kNB>
+__device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t, const DrainContext& c,
+                                           const int acc, const int nt) {
+  const uint32_t lane_base = c.lane_base;
+  const uint32_t warp_store = c.warp_store;
+  (void)warp_store;
+  const int group = c.group, quarter = c.quarter, lane = c.lane;
+  const float alpha = c.alpha, inv_h = c.inv_h;
+  (void)inv_h;
+  const bool row_ok = quarter * 32 + lane < t.valid;
+  const int64_t out_row = static_cast<int64_t>(t.row0) + quarter * 32 + lane;
+  const uint32_t taddr = lane_base + acc * (kNB == 1 ? kTileN : c.acc1_col);
+  // With three shared slices (accumulator 0: slices 1-3, accumulator 1: slices 0-2) one group
+  // holds two of them and can only let go after its second load.
+  const bool late_signal = kNB == 2 && c.wide_overlap && ((acc == 0) == (group == 1));
+
+  // Software pipeline over the four 32-column chunks of the warp's two slices: while
+  // a chunk is converted, the load of the chunk after next is in flight (a TMEM load
+  // takes several hundred cycles from issue to data).
+  const int slice0 = kNB == 1 ? 0 : ((acc == 0) ? 2 + group : group);
+  const int slice1 = kNB == 1 ? 1 : ((acc == 0) ? group : 2 + group);
+  const bool rows_any = t.valid > quarter * 32;  // this warp owns at least one valid row
+  // rows may live anywhere (another GPU's buffer): lane l holds the address of row l
+  unsigned long long row_base = 0;
+  if (kOut == LM_OUT_BF16 && p.out_row_ptrs != nullptr && quarter * 32 + lane < t.valid)
+    row_base = __ldg(reinterpret_cast<const unsigned long long*>(p.out_row_ptrs) + t.row0 + quarter * 32 + lane);
+  uint32_t va[32], vb[32];
+  tc_load32(taddr + slice0 * 64, va);
+  tc_load32(taddr + slice0 * 64 + 32, vb);
+  tc_wait_ld_regs(va);
+  tc_wait_ld_regs(vb);
+  // slice 0 is in registers: the columns shared with the other accumulator are free
+  tc_fence_before();
+  __syncwarp();
+  if (kNB == 2 && !late_signal && lane == 0) signal_barrier(c.bar_shared_cols, c.remote);
+
+  // ---- per-slice state and the two halves of the work
+  constexpr bool kGated = kAct != LM_ACT_RELU2;
+  uint32_t q[8];   // NVFP4: packed codes of the slice
+  uint32_t sfw = 0;  // NVFP4: scale-factor bytes of the slice
+  (void)q;
+  (void)sfw;
+  auto convert = [&](const uint32_t* v, const int half, const int col64) {
+    if (kOut == LM_OUT_NVFP4) {
+      if (kGated) {
+        // 32 accumulator columns = 16 (gate, up) pairs -> 16 outputs: 8 bytes, one factor
+        float h[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          h[i] = gated_value<kAct>(__uint_as_float(v[2 * i]) * alpha,
+                                   __uint_as_float(v[2 * i + 1]) * alpha, p);
+        const uint32_t sf = requant16(h, inv_h, &q[2 * half]);
+        sfw = half == 0 ? sf : (sfw | (sf << 8));
+      } else {
+        // 32 outputs: 16 bytes, two factors
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          float h[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float x = fmaxf(__uint_as_float(v[16 * c + i]) * alpha, 0.0f);
+            h[i] = x * x;
+          }
+          const uint32_t sf = requant16(h, inv_h, &q[4 * half + 2 * c]);
+          sfw = (half == 0 && c == 0) ? sf : (sfw | (sf << (8 * (2 * half + c))));
+        }
+      }
+    } else if (kOut == LM_OUT_BF16) {
+      // lane = row: the warp's 32 x 64 block goes to its shared-memory staging
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(warp_store + lane * kStoreRowPitch +
+                                                                       half * 64 + i * 16),
+                     "r"(pack_bf16x2(__uint_as_float(v[8 * i]) * alpha, __uint_as_float(v[8 * i + 1]) * alpha)),
+                     "r"(pack_bf16x2(__uint_as_float(v[8 * i + 2]) * alpha, __uint_as_float(v[8 * i + 3]) * alpha)),
+                     "r"(pack_bf16x2(__uint_as_float(v[8 * i + 4]) * alpha, __uint_as_float(v[8 * i + 5]) * alpha)),
+                     "r"(pack_bf16x2(__uint_as_float(v[8 * i + 6]) * alpha, __uint_as_float(v[8 * i + 7]) * alpha))
+                     : "memory");
+    } else {
+      float* out_base = static_cast<float*>(p.out) + out_row * p.n + col64 * 64 + half * 32;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        // N is a multiple of 8: groups of four never straddle the edge
+        if (row_ok && col64 * 64 + half * 32 + 4 * i < p.n)
+          reinterpret_cast<float4*>(out_base)[i] =
+              make_float4(__uint_as_float(v[4 * i]) * alpha, __uint_as_float(v[4 * i + 1]) * alpha,
+                          __uint_as_float(v[4 * i + 2]) * alpha, __uint_as_float(v[4 * i + 3]) * alpha);
+      }
+    }
+  };
+  auto finish = [&](const int col64) {
+    const bool cols_ok = col64 * 64 < p.n;
+    if (kOut == LM_OUT_NVFP4) {
+      const int out_n = p.out_atom_cols * 64;
+      if (row_ok && cols_ok) {
+        if (kGated) {
+          uint8_t* codes = static_cast<uint8_t*>(p.out) + out_row * (out_n >> 1) +
+                           static_cast<int64_t>(col64) * 16;
+          *reinterpret_cast<uint4*>(codes) = make_uint4(q[0], q[1], q[2], q[3]);
+          uint8_t* dst = p.out_sf +
+                         (static_cast<int64_t>(t.sf_row) * p.out_atom_cols + (col64 >> 1)) * 512 +
+                         lane * 16 + quarter * 4 + (col64 & 1) * 2;
+          *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(sfw);
+        } else {
+          uint8_t* codes = static_cast<uint8_t*>(p.out) + out_row * (out_n >> 1) +
+                           static_cast<int64_t>(col64) * 32;
+          reinterpret_cast<uint4*>(codes)[0] = make_uint4(q[0], q[1], q[2], q[3]);
+          reinterpret_cast<uint4*>(codes)[1] = make_uint4(q[4], q[5], q[6], q[7]);
+          uint8_t* dst = p.out_sf +
+                         (static_cast<int64_t>(t.sf_row) * p.out_atom_cols + col64) * 512 +
+                         lane * 16 + quarter * 4;
+          *reinterpret_cast<uint32_t*>(dst) = sfw;
+        }
+      }
+    } else if (kOut == LM_OUT_BF16) {
+      // transposed read: a global store covers four whole 128-byte row pieces
+      __syncwarp();
+      if (rows_any && cols_ok) {
+        const int rows_here = t.valid - quarter * 32;  // valid rows among this warp's 32
+        __nv_bfloat16* warp_out =
+            static_cast<__nv_bfloat16*>(p.out) + (static_cast<int64_t>(t.row0) + quarter * 32) * p.n;
+        const int piece = lane & 7;
+        const int col = col64 * 64 + piece * 8;
+        uint4 d[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(d[i].x), "=r"(d[i].y), "=r"(d[i].z), "=r"(d[i].w)
+                       : "r"(warp_store + (4 * i + (lane >> 3)) * kStoreRowPitch + piece * 16));
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int row = 4 * i + (lane >> 3);
+          __nv_bfloat16* dst = warp_out + static_cast<int64_t>(row) * p.n;
+          if (p.out_row_ptrs != nullptr)
+            dst = reinterpret_cast<__nv_bfloat16*>(__shfl_sync(0xFFFFFFFFu, row_base, row));
+#ifdef LM_GEMM_PROFILE
+          if (p.debug_flags & 8) continue;
+#endif
+          if (row < rows_here && col < p.n) *reinterpret_cast<uint4*>(dst + col) = d[i];
+        }
+      }
+      __syncwarp();
+    }
+  };
+
+  const int col_a = nt * 2 * kNB + slice0;
+  const int col_b = nt * 2 * kNB + slice1;
+  convert(va, 0, col_a);
+  tc_load32(taddr + slice1 * 64, va);
+  convert(vb, 1, col_a);
+  tc_load32(taddr + slice1 * 64 + 32, vb);
+  finish(col_a);
+  tc_wait_ld_regs(va);
+  tc_wait_ld_regs(vb);
+  // the whole accumulator has been read
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) {
+    if (late_signal) signal_barrier(c.bar_shared_cols, c.remote);
+    signal_barrier(c.bar_acc_empty, c.remote);
+  }
+  convert(va, 0, col_b);
+  convert(vb, 1, col_b);
+  finish(col_b);
+}
+
 // ------------------------------------------------------------------ kernel
 // kNB = 128-column blocks per tile.
 // 1: 128 x 128 tiles, two accumulators of 128 TMEM columns, one scale-factor slot per ring
@@ -629,10 +824,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #ifdef LM_GEMM_PROFILE
             if (!(p.debug_flags & 2))
 #endif
-            for (int c = 0; c < chunks; ++c) {
-              // 64 FP4 values = 32 bytes along K: +2 in 16-byte descriptor units
-              tc_mma_nvf4(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 4 * kNB,
-                          (ks > 0 || c > 0) ? 1u : 0u);
+            // 64 FP4 values = 32 bytes along K: +2 in 16-byte descriptor units
+            if (chunks == kChunksPerStage) {
+#pragma unroll
+              for (int c = 0; c < kChunksPerStage; ++c)
+                tc_mma_nvf4(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 4 * kNB,
+                            (ks > 0 || c > 0) ? 1u : 0u);
+            } else {
+              for (int c = 0; c < chunks; ++c)
+                tc_mma_nvf4(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 4 * kNB,
+                            (ks > 0 || c > 0) ? 1u : 0u);
             }
             tc_commit(smem_u32(&misc->empty[stage]));
             if (resident && nt == u.n_end - 1) tc_commit(smem_u32(&misc->a_empty[ks]));
@@ -728,204 +929,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // 256-column tiles: both groups work on every tile, group g on slices g and g + 2, and
     // take the slice that touches the columns shared with the other accumulator first.
     const int group = (warp - kFirstEpilogueWarp) >> 2;
-    const int quarter = warp & 3;           // TMEM lanes this warp may read
-    const int r = quarter * 32 + lane;      // row of the tile
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t warp_store = store_base + (warp - kFirstEpilogueWarp) * kStoreBytesPerWarp;
-    (void)warp_store;
+    DrainContext ctx;
+    ctx.group = group;
+    ctx.quarter = warp & 3;  // TMEM lanes this warp may read
+    ctx.lane = lane;
+    ctx.lane_base = tmem_base + (static_cast<uint32_t>(ctx.quarter * 32) << 16);
+    ctx.warp_store = store_base + (warp - kFirstEpilogueWarp) * kStoreBytesPerWarp;
+    ctx.bar_shared_cols = smem_u32(&misc->shared_cols_free);
+    ctx.remote = false;
+    ctx.acc1_col = kWideAcc1Col;
+    ctx.wide_overlap = false;
+    ctx.inv_h = kOut == LM_OUT_NVFP4 ? __ldg(p.out_scale + 1) : 0.0f;
     TileWalker walker;
     int it = 0;
     bool ok = true;
     LM_PROF_DECL;
-#ifdef LM_GEMM_PROFILE
-    long long lap[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    long long prof_lap = clock64();
-#endif
-    float inv_h = 0.0f;
-    if (kOut == LM_OUT_NVFP4) inv_h = __ldg(p.out_scale + 1);
     for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
       const Unit u = decode_unit(p, unit);
       const RowTile t = walker.at(misc, p, u.mt);
-      const float alpha = __ldg(p.alpha + (p.alpha_per_expert ? t.expert : 0));
-      const bool row_ok = r < t.valid;
-      const int64_t out_row = static_cast<int64_t>(t.row0) + r;
+      ctx.alpha = __ldg(p.alpha + (p.alpha_per_expert ? t.expert : 0));
       for (int nt = u.n_begin; nt < u.n_end; ++nt, ++it) {
         if (kNB == 1 && (it & 1) != group) continue;
         const int acc = it & 1;
         LM_PROF_END(prof_acc1);  // busy since the previous wait ended
-        LM_PROF_LAP(lap[6]);
         LM_PROF_BEGIN();
         ok = mbar_wait(smem_u32(&misc->acc_full[acc]), (it >> 1) & 1u, abort_flag, kStatusEpilogueTimeout);
         LM_PROF_END(prof_acc0);
         LM_PROF_BEGIN();
-#ifdef LM_GEMM_PROFILE
-        prof_lap = clock64();
-#endif
         if (!ok) break;
         tc_fence_after();
-        const uint32_t taddr = lane_base + acc * (kNB == 1 ? kTileN : kWideAcc1Col);
-
-        // Software pipeline over the four 32-column chunks of the warp's two slices: while
-        // a chunk is converted, the load of the chunk after next is in flight (a TMEM load
-        // takes several hundred cycles from issue to data).
-        const int slice0 = kNB == 1 ? 0 : ((acc == 0) ? 2 + group : group);
-        const int slice1 = kNB == 1 ? 1 : ((acc == 0) ? group : 2 + group);
-        const bool rows_any = t.valid > quarter * 32;  // this warp owns at least one valid row
-        // rows may live anywhere (another GPU's buffer): lane l holds the address of row l
-        unsigned long long row_base = 0;
-        if (kOut == LM_OUT_BF16 && p.out_row_ptrs != nullptr && quarter * 32 + lane < t.valid)
-          row_base = __ldg(reinterpret_cast<const unsigned long long*>(p.out_row_ptrs) + t.row0 + quarter * 32 + lane);
-        uint32_t va[32], vb[32];
-        LM_PROF_LAP(lap[7]);
-        tc_load32(taddr + slice0 * 64, va);
-        tc_load32(taddr + slice0 * 64 + 32, vb);
-        tc_wait_ld_regs(va);
-        tc_wait_ld_regs(vb);
-        // slice 0 is in registers: the columns shared with the other accumulator are free
-        tc_fence_before();
-        __syncwarp();
-        if (kNB == 2 && lane == 0) mbar_arrive(smem_u32(&misc->shared_cols_free));
-        LM_PROF_LAP(lap[0]);
-
-        // ---- per-slice state and the two halves of the work
-        constexpr bool kGated = kAct != LM_ACT_RELU2;
-        uint32_t q[8];   // NVFP4: packed codes of the slice
-        uint32_t sfw = 0;  // NVFP4: scale-factor bytes of the slice
-        (void)q;
-        (void)sfw;
-        auto convert = [&](const uint32_t* v, const int half, const int col64) {
-          if (kOut == LM_OUT_NVFP4) {
-            if (kGated) {
-              // 32 accumulator columns = 16 (gate, up) pairs -> 16 outputs: 8 bytes, one factor
-              float h[16];
-#pragma unroll
-              for (int i = 0; i < 16; ++i)
-                h[i] = gated_value<kAct>(__uint_as_float(v[2 * i]) * alpha,
-                                         __uint_as_float(v[2 * i + 1]) * alpha, p);
-              const uint32_t sf = requant16(h, inv_h, &q[2 * half]);
-              sfw = half == 0 ? sf : (sfw | (sf << 8));
-            } else {
-              // 32 outputs: 16 bytes, two factors
-#pragma unroll
-              for (int c = 0; c < 2; ++c) {
-                float h[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                  float x = fmaxf(__uint_as_float(v[16 * c + i]) * alpha, 0.0f);
-                  h[i] = x * x;
-                }
-                const uint32_t sf = requant16(h, inv_h, &q[4 * half + 2 * c]);
-                sfw = (half == 0 && c == 0) ? sf : (sfw | (sf << (8 * (2 * half + c))));
-              }
-            }
-          } else if (kOut == LM_OUT_BF16) {
-            // lane = row: the warp's 32 x 64 block goes to its shared-memory staging
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(warp_store + lane * kStoreRowPitch +
-                                                                             half * 64 + i * 16),
-                           "r"(pack_bf16x2(__uint_as_float(v[8 * i]) * alpha, __uint_as_float(v[8 * i + 1]) * alpha)),
-                           "r"(pack_bf16x2(__uint_as_float(v[8 * i + 2]) * alpha, __uint_as_float(v[8 * i + 3]) * alpha)),
-                           "r"(pack_bf16x2(__uint_as_float(v[8 * i + 4]) * alpha, __uint_as_float(v[8 * i + 5]) * alpha)),
-                           "r"(pack_bf16x2(__uint_as_float(v[8 * i + 6]) * alpha, __uint_as_float(v[8 * i + 7]) * alpha))
-                           : "memory");
-          } else {
-            float* out_base = static_cast<float*>(p.out) + out_row * p.n + col64 * 64 + half * 32;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              // N is a multiple of 8: groups of four never straddle the edge
-              if (row_ok && col64 * 64 + half * 32 + 4 * i < p.n)
-                reinterpret_cast<float4*>(out_base)[i] =
-                    make_float4(__uint_as_float(v[4 * i]) * alpha, __uint_as_float(v[4 * i + 1]) * alpha,
-                                __uint_as_float(v[4 * i + 2]) * alpha, __uint_as_float(v[4 * i + 3]) * alpha);
-            }
-          }
-        };
-        auto finish = [&](const int col64) {
-          const bool cols_ok = col64 * 64 < p.n;
-          if (kOut == LM_OUT_NVFP4) {
-            const int out_n = p.out_atom_cols * 64;
-            if (row_ok && cols_ok) {
-              if (kGated) {
-                uint8_t* codes = static_cast<uint8_t*>(p.out) + out_row * (out_n >> 1) +
-                                 static_cast<int64_t>(col64) * 16;
-                *reinterpret_cast<uint4*>(codes) = make_uint4(q[0], q[1], q[2], q[3]);
-                uint8_t* dst = p.out_sf +
-                               (static_cast<int64_t>(t.sf_row) * p.out_atom_cols + (col64 >> 1)) * 512 +
-                               lane * 16 + quarter * 4 + (col64 & 1) * 2;
-                *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(sfw);
-              } else {
-                uint8_t* codes = static_cast<uint8_t*>(p.out) + out_row * (out_n >> 1) +
-                                 static_cast<int64_t>(col64) * 32;
-                reinterpret_cast<uint4*>(codes)[0] = make_uint4(q[0], q[1], q[2], q[3]);
-                reinterpret_cast<uint4*>(codes)[1] = make_uint4(q[4], q[5], q[6], q[7]);
-                uint8_t* dst = p.out_sf +
-                               (static_cast<int64_t>(t.sf_row) * p.out_atom_cols + col64) * 512 +
-                               lane * 16 + quarter * 4;
-                *reinterpret_cast<uint32_t*>(dst) = sfw;
-              }
-            }
-          } else if (kOut == LM_OUT_BF16) {
-            // transposed read: a global store covers four whole 128-byte row pieces
-            __syncwarp();
-            if (rows_any && cols_ok) {
-              const int rows_here = t.valid - quarter * 32;  // valid rows among this warp's 32
-              __nv_bfloat16* warp_out =
-                  static_cast<__nv_bfloat16*>(p.out) + (static_cast<int64_t>(t.row0) + quarter * 32) * p.n;
-              const int piece = lane & 7;
-              const int col = col64 * 64 + piece * 8;
-              uint4 d[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(d[i].x), "=r"(d[i].y), "=r"(d[i].z), "=r"(d[i].w)
-                             : "r"(warp_store + (4 * i + (lane >> 3)) * kStoreRowPitch + piece * 16));
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const int row = 4 * i + (lane >> 3);
-                __nv_bfloat16* dst = warp_out + static_cast<int64_t>(row) * p.n;
-                if (p.out_row_ptrs != nullptr)
-                  dst = reinterpret_cast<__nv_bfloat16*>(__shfl_sync(0xFFFFFFFFu, row_base, row));
-#ifdef LM_GEMM_PROFILE
-                if (p.debug_flags & 8) continue;
-#endif
-                if (row < rows_here && col < p.n) *reinterpret_cast<uint4*>(dst + col) = d[i];
-              }
-            }
-            __syncwarp();
-          }
-        };
-
-        const int col_a = nt * 2 * kNB + slice0;
-        const int col_b = nt * 2 * kNB + slice1;
-        convert(va, 0, col_a);
-        tc_load32(taddr + slice1 * 64, va);
-        convert(vb, 1, col_a);
-        tc_load32(taddr + slice1 * 64 + 32, vb);
-        LM_PROF_LAP(lap[1]);
-        finish(col_a);
-        LM_PROF_LAP(lap[2]);
-        tc_wait_ld_regs(va);
-        tc_wait_ld_regs(vb);
-        // the whole accumulator has been read
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&misc->acc_empty[acc]));
-        LM_PROF_LAP(lap[3]);
-        convert(va, 0, col_b);
-        convert(vb, 1, col_b);
-        LM_PROF_LAP(lap[4]);
-        finish(col_b);
-        LM_PROF_LAP(lap[5]);
+        ctx.bar_acc_empty = smem_u32(&misc->acc_empty[acc]);
+        drain_tile<kOut, kAct, kNB>(p, t, ctx, acc, nt);
       }
     }
     LM_PROF_END(prof_acc1);
     if (warp == kFirstEpilogueWarp && lane == 0) {
       LM_PROF_STORE(3, prof_acc0);
       LM_PROF_STORE(4, prof_acc1);
-#ifdef LM_GEMM_PROFILE
-      for (int i = 0; i < 8; ++i) { LM_PROF_STORE(8 + i, lap[i]); }
-#endif
     }
   }
 
@@ -946,6 +986,450 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
 }
 
+// ------------------------------------------------------------- CTA-pair kernel
+// Two CTAs of a cluster (adjacent SMs) compute one 256 x 256 tile with
+// tcgen05.mma.cta_group::2: each CTA holds 128 rows of A, 128 of the 256 columns of B and
+// the accumulator of its own 128 rows, and the tensor cores of both read B from both shared
+// memories.  An SM then ingests 38 KB per K stage for 128 x 256 x 256 multiply-adds instead
+// of 54 KB: less of the L2-to-SM traffic that bounds the single-CTA kernel.  The ring holds
+// five stages (four with BF16 output).
+//
+// Roles per CTA as in gemm_kernel; only the leader (cluster rank 0) issues MMAs.  Barriers:
+//   full[s]     local.  Leader: the A and B tiles of both CTAs (the peer's TMA loads signal
+//               the leader's barrier) and the leader's scale factors.  Peer: its scale factors.
+//   sf_full[s]  leader's; the eight scale-factor warps of both CTAs arrive.
+//   empty[s], acc_full[a]  local in both CTAs, signalled by multicast tcgen05.commit.
+//   acc_empty[a], shared_cols_free  leader's; the sixteen epilogue warps of both CTAs arrive.
+constexpr int kPairStageBytes = 2 * kTileBytes + 3 * kSfBytes;  // B half, SFB x2, A, SFA = 38912
+// TMEM of a pair CTA: accumulator 0 at [0, 256), accumulator 1 at [64, 320), four scale-factor
+// slots of 48 columns from 320.  Signals between the CTAs take long enough that two slots
+// (the single-CTA layout) leave the MMAs waiting for scale factors most of the time.
+constexpr uint32_t kPairAcc1Col = 64;
+constexpr uint32_t kPairSfCol = 320;
+constexpr int kPairSfSlots = 4;
+static_assert(kPairStageBytes % 1024 == 0, "pair ring stages must keep 1024-byte alignment");
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// The shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// TMA load whose completion is counted on a barrier of the pair's other CTA.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                                 uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(c0), "r"(c1), "r"(cluster_bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_nvf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X "
+      "[%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+
+// Arrives on the barrier at this shared-memory offset in both CTAs of the pair once the
+// MMAs issued so far have completed.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"(mask)
+      : "memory");
+}
+
+__host__ __device__ constexpr uint32_t make_idesc_pair(int n) {
+  return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (0u << 23) |
+         (static_cast<uint32_t>(256 >> 4) << 24);
+}
+
+// Row tile of cluster rank `rank` inside the 256-row tile `mt` (prefix table built with 256-row
+// tiles).  `valid` may be zero: the expert ends before this CTA's half.
+__device__ __forceinline__ RowTile pair_row_tile(const Misc* m, const GemmParams& p, int& expert, int mt,
+                                                 int rank) {
+  while (expert + 1 < p.experts && m->prefix[expert + 1] <= mt) ++expert;
+  const int local = mt - m->prefix[expert];
+  const int begin = m->cu[expert];
+  const int count = m->cu[expert + 1] - begin;
+  RowTile t;
+  t.expert = expert;
+  t.row0 = begin + local * 2 * kTileM + rank * kTileM;
+  t.valid = max(0, min(kTileM, count - local * 2 * kTileM - rank * kTileM));
+  t.sf_row = begin / kTileM + expert + local * 2 + rank;
+  return t;
+}
+
+__device__ __forceinline__ uint32_t a_box_rows(int valid) {
+  return valid <= 0 ? 0u : (valid <= 32 ? 32u : (valid <= 64 ? 64u : 128u));
+}
+
+template <int kOut, int kAct>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64,
+                 const __grid_constant__ CUtensorMap tmap_a32, const __grid_constant__ CUtensorMap tmap_b,
+                 const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  constexpr int kSlots = data_slots(kOut);
+  const uint32_t store_base = smem_base + kSlots * kSlotBytes;
+  Misc* misc = reinterpret_cast<Misc*>(smem_gen + kSlots * kSlotBytes +
+                                       (kOut == LM_OUT_BF16 ? kStoreBytes : 0));
+  volatile int* abort_flag = &misc->abort_flag;
+
+  // ring stage: [B half tile][B scale factors of both column blocks][A tile][A scale factors]
+  constexpr uint32_t kOffB = 0;
+  constexpr uint32_t kOffSfb = kTileBytes;
+  constexpr uint32_t kOffA = kTileBytes + 2 * kSfBytes;
+  constexpr uint32_t kOffSfa = kOffA + kTileBytes;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  // ---- one-time setup
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kMaxRing; ++s) {
+      mbar_init(smem_u32(&misc->full[s]), 1);
+      mbar_init(smem_u32(&misc->empty[s]), 1);
+      mbar_init(smem_u32(&misc->sf_full[s]), 8);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&misc->acc_full[s]), 1);
+      mbar_init(smem_u32(&misc->acc_empty[s]), 16);
+    }
+    mbar_init(smem_u32(&misc->shared_cols_free), 16);
+    misc->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&misc->tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (p.dense) {
+    if (threadIdx.x == 0) {
+      misc->cu[0] = 0;
+      misc->cu[1] = static_cast<int>(p.rows);
+    }
+  } else {
+    for (int e = threadIdx.x; e <= p.experts; e += kThreads) misc->cu[e] = __ldg(p.m_indptr + e);
+  }
+  __syncthreads();
+  if (warp == 2) {
+    // exclusive prefix of 256-row tiles per expert; each lane owns 8 experts
+    int local[8];
+    int sum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      int e = lane * 8 + i;
+      int tiles = 0;
+      if (e < p.experts) tiles = (misc->cu[e + 1] - misc->cu[e] + 2 * kTileM - 1) / (2 * kTileM);
+      local[i] = sum;
+      sum += tiles;
+    }
+    int incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int t = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+      if (lane >= d) incl += t;
+    }
+    const int base = incl - sum;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      int e = lane * 8 + i;
+      if (e < p.experts) misc->prefix[e] = base + local[i];
+    }
+    if (lane == 31) {
+      misc->total_m_tiles = incl;
+      misc->prefix[p.experts] = incl;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // both CTAs' barriers exist before anything arrives on them
+  tc_fence_after();
+
+  const uint32_t tmem_base = misc->tmem_base;
+  const int total_units = misc->total_m_tiles * p.units_per_mtile;
+  const int first_unit = blockIdx.x >> 1;
+  const int unit_stride = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ===================================================== TMA producer (both CTAs)
+    int cursor = 0, peer_cursor = 0;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    LM_PROF_DECL;
+    for (int unit = first_unit; unit < total_units && ok; unit += unit_stride) {
+      const Unit u = decode_unit(p, unit);
+      const RowTile t = pair_row_tile(misc, p, cursor, u.mt, rank);
+      const uint32_t a_rows = a_box_rows(t.valid);
+      uint32_t peer_a_bytes = 0;
+      if (leader) peer_a_bytes = a_box_rows(pair_row_tile(misc, p, peer_cursor, u.mt, 1).valid) * kStageKBytes;
+      const CUtensorMap* a_map = a_rows == 32 ? &tmap_a32 : (a_rows == 64 ? &tmap_a64 : &tmap_a);
+      const uint8_t* sfa_src = p.sfa + static_cast<int64_t>(t.sf_row) * p.atom_cols * 512;
+      for (int nt = u.n_begin; nt < u.n_end && ok; ++nt) {
+        const int b_row = t.expert * p.n + nt * 2 * kTileN + rank * kTileN;
+        const uint8_t* sfb_src =
+            p.sfb + static_cast<int64_t>(t.expert * p.sfb_atom_rows + nt * 2) * p.atom_cols * 512;
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
+          const uint32_t sf_bytes = chunks * 512;
+          LM_PROF_BEGIN();
+          ok = mbar_wait(smem_u32(&misc->empty[stage]), phase ^ 1u, abort_flag, kStatusProducerTimeout);
+          LM_PROF_END(prof_acc0);
+          if (!ok) break;
+          if (elect_one()) {
+            const uint32_t bar = smem_u32(&misc->full[stage]);
+            const uint32_t dst = smem_base + stage * kPairStageBytes;
+            const uint32_t sf_tx = 3 * sf_bytes;  // A's and both column blocks of B's
+            if (leader) {
+              mbar_expect_tx(bar, sf_tx + 2 * kTileBytes + a_rows * kStageKBytes + peer_a_bytes);
+              tma_load_2d(dst + kOffB, &tmap_b, ks * kStageKBytes, b_row, bar);
+              if (a_rows) tma_load_2d(dst + kOffA, a_map, ks * kStageKBytes, t.row0, bar);
+            } else {
+              mbar_expect_tx(bar, sf_tx);
+              const uint32_t leader_bar = map_to_cta(bar, 0);
+              tma_load_2d_pair(dst + kOffB, &tmap_b, ks * kStageKBytes, b_row, leader_bar);
+              if (a_rows) tma_load_2d_pair(dst + kOffA, a_map, ks * kStageKBytes, t.row0, leader_bar);
+            }
+            for (int j = 0; j < 2; ++j)
+              bulk_load(dst + kOffSfb + j * kSfBytes,
+                        sfb_src + (static_cast<int64_t>(j) * p.atom_cols + ks * kChunksPerStage) * 512, sf_bytes,
+                        bar);
+            bulk_load(dst + kOffSfa, sfa_src + static_cast<int64_t>(ks) * kSfBytes, sf_bytes, bar);
+          }
+          __syncwarp();
+          if (++stage == p.ring_stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    if (lane == 0) { LM_PROF_STORE(0, prof_acc0); }
+  } else if (warp == 1) {
+    // ===================================================== MMA issuer (leader only)
+    if (leader) {
+      constexpr uint32_t idesc = make_idesc_pair(2 * kTileN);
+      uint32_t sf_slot = 0;
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      LM_PROF_DECL;
+      long long prof_sf = 0;
+      (void)prof_sf;
+      const long long prof_start = clock64();
+      (void)prof_start;
+      for (int unit = first_unit; unit < total_units && ok; unit += unit_stride) {
+        const Unit u = decode_unit(p, unit);
+        for (int nt = u.n_begin; nt < u.n_end && ok; ++nt, ++it) {
+          const int acc = it & 1;
+          LM_PROF_BEGIN();
+          ok = mbar_wait(smem_u32(&misc->acc_empty[acc]), ((it >> 1) & 1u) ^ 1u, abort_flag, kStatusMmaTimeout);
+          if (ok && it > 0)
+            ok = mbar_wait(smem_u32(&misc->shared_cols_free), (it - 1) & 1u, abort_flag, kStatusMmaTimeout);
+          LM_PROF_END(prof_acc1);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * kPairAcc1Col;
+          for (int ks = 0; ks < p.k_stages; ++ks) {
+            LM_PROF_BEGIN();
+            ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusMmaTimeout);
+            LM_PROF_END(prof_acc0);
+            LM_PROF_BEGIN();
+            if (ok) ok = mbar_wait(smem_u32(&misc->sf_full[stage]), phase, abort_flag, kStatusMmaTimeout);
+            LM_PROF_END(prof_sf);
+            if (!ok) break;
+            tc_fence_after();
+            LM_PROF_BEGIN();
+            const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
+            const uint32_t stage_smem = smem_base + stage * kPairStageBytes;
+            const uint32_t sfa_t = tmem_base + kPairSfCol + sf_slot * kWideSfSlotCols;
+            const uint32_t sfb_t = sfa_t + 16;
+            sf_slot = (sf_slot + 1) % kPairSfSlots;
+            const uint64_t a_desc = desc_sw128(stage_smem + kOffA);
+            const uint64_t b_desc = desc_sw128(stage_smem + kOffB);
+            if (elect_one()) {
+              if (chunks == kChunksPerStage) {
+#pragma unroll
+                for (int c = 0; c < kChunksPerStage; ++c)
+                  tc_mma_nvf4_pair(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 8,
+                                   (ks > 0 || c > 0) ? 1u : 0u);
+              } else {
+                for (int c = 0; c < chunks; ++c)
+                  tc_mma_nvf4_pair(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 8,
+                                   (ks > 0 || c > 0) ? 1u : 0u);
+              }
+              tc_commit_pair(smem_u32(&misc->empty[stage]));
+            }
+            __syncwarp();
+            LM_PROF_END(prof_acc2);
+            if (++stage == p.ring_stages) { stage = 0; phase ^= 1u; }
+          }
+          if (!ok) break;
+          if (elect_one()) tc_commit_pair(smem_u32(&misc->acc_full[acc]));
+          __syncwarp();
+        }
+      }
+      if (lane == 0) {
+        LM_PROF_STORE(1, prof_acc0);
+        LM_PROF_STORE(2, prof_acc1);
+        LM_PROF_STORE(7, prof_acc2);
+        LM_PROF_STORE(8, prof_sf);
+        LM_PROF_STORE(5, clock64() - prof_start);
+        LM_PROF_STORE(6, it);
+      }
+    }
+  } else if (warp >= kFirstSfWarp && warp < kFirstSfWarp + 4) {
+    // ===================================================== scale factors -> TMEM (both CTAs)
+    const int quarter = warp & 3;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t sf_slot = 0;
+    int prev_stage[kPairSfSlots];    // ring stage (and its phase) of the last four iterations
+    uint32_t prev_phase[kPairSfSlots];
+    for (int i = 0; i < kPairSfSlots; ++i) {
+      prev_stage[i] = -1;
+      prev_phase[i] = 0;
+    }
+    bool ok = true;
+    LM_PROF_DECL;
+    for (int unit = first_unit; unit < total_units && ok; unit += unit_stride) {
+      const Unit u = decode_unit(p, unit);
+      for (int nt = u.n_begin; nt < u.n_end && ok; ++nt) {
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          LM_PROF_BEGIN();
+          ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusSfTimeout);
+          LM_PROF_END(prof_acc0);
+          LM_PROF_BEGIN();
+          // the TMEM slot was last read by the MMAs of four stages ago
+          if (ok && prev_stage[0] >= 0)
+            ok = mbar_wait(smem_u32(&misc->empty[prev_stage[0]]), prev_phase[0], abort_flag, kStatusSfTimeout);
+#pragma unroll
+          for (int i = 0; i + 1 < kPairSfSlots; ++i) {
+            prev_stage[i] = prev_stage[i + 1];
+            prev_phase[i] = prev_phase[i + 1];
+          }
+          prev_stage[kPairSfSlots - 1] = stage;
+          prev_phase[kPairSfSlots - 1] = phase;
+          if (!ok) break;
+          LM_PROF_END(prof_acc1);
+          LM_PROF_BEGIN();
+          const uint32_t stage_smem = smem_base + stage * kPairStageBytes;
+          const uint32_t sfa_src = stage_smem + kOffSfa + lane * 16;
+          const uint32_t sfb_src = stage_smem + kOffSfb + lane * 16;
+          uint32_t w[48];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(w[4 * c]), "=r"(w[4 * c + 1]), "=r"(w[4 * c + 2]), "=r"(w[4 * c + 3])
+                         : "r"(sfa_src + c * 512));
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int o = 16 + 4 * (c * 2 + j);
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(w[o]), "=r"(w[o + 1]), "=r"(w[o + 2]), "=r"(w[o + 3])
+                           : "r"(sfb_src + j * kSfBytes + c * 512));
+            }
+          }
+          const uint32_t dst = lane_base + kPairSfCol + sf_slot * kWideSfSlotCols;
+          tc_store32(dst, w);
+          tc_store16(dst + 32, w + 32);
+          sf_slot = (sf_slot + 1) % kPairSfSlots;
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          tc_fence_before();
+          __syncwarp();
+          LM_PROF_END(prof_acc2);
+          if (lane == 0) {
+            const uint32_t bar = smem_u32(&misc->sf_full[stage]);
+            signal_barrier(leader ? bar : map_to_cta(bar, 0), !leader);
+          }
+          if (++stage == p.ring_stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    if (warp == kFirstSfWarp && lane == 0 && leader) {
+      LM_PROF_STORE(9, prof_acc0);
+      LM_PROF_STORE(10, prof_acc1);
+      LM_PROF_STORE(11, prof_acc2);
+    }
+  } else if (warp >= kFirstEpilogueWarp) {
+    // ===================================================== epilogue (both CTAs, own 128 rows)
+    DrainContext ctx;
+    ctx.group = (warp - kFirstEpilogueWarp) >> 2;
+    ctx.quarter = warp & 3;
+    ctx.lane = lane;
+    ctx.lane_base = tmem_base + (static_cast<uint32_t>(ctx.quarter * 32) << 16);
+    ctx.warp_store = store_base + (warp - kFirstEpilogueWarp) * kStoreBytesPerWarp;
+    ctx.remote = !leader;
+    ctx.acc1_col = kPairAcc1Col;
+    ctx.wide_overlap = true;
+    const uint32_t cols_bar = smem_u32(&misc->shared_cols_free);
+    ctx.bar_shared_cols = leader ? cols_bar : map_to_cta(cols_bar, 0);
+    ctx.inv_h = kOut == LM_OUT_NVFP4 ? __ldg(p.out_scale + 1) : 0.0f;
+    int cursor = 0;
+    int it = 0;
+    bool ok = true;
+    for (int unit = first_unit; unit < total_units && ok; unit += unit_stride) {
+      const Unit u = decode_unit(p, unit);
+      const RowTile t = pair_row_tile(misc, p, cursor, u.mt, rank);
+      ctx.alpha = __ldg(p.alpha + (p.alpha_per_expert ? t.expert : 0));
+      for (int nt = u.n_begin; nt < u.n_end; ++nt, ++it) {
+        const int acc = it & 1;
+        ok = mbar_wait(smem_u32(&misc->acc_full[acc]), (it >> 1) & 1u, abort_flag, kStatusEpilogueTimeout);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t empty_bar = smem_u32(&misc->acc_empty[acc]);
+        ctx.bar_acc_empty = leader ? empty_bar : map_to_cta(empty_bar, 0);
+        drain_tile<kOut, kAct, 2>(p, t, ctx, acc, nt);
+      }
+    }
+  }
+
+  // ---- teardown: neither CTA leaves while the other may still signal its barriers
+  __syncwarp();
+  if (*abort_flag) {
+    const long long start = clock64();
+    while (clock64() - start < 2000000ll) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
 // --------------------------------------------------------------- host side
 struct PlanData {
   uint32_t magic;
@@ -953,6 +1437,7 @@ struct PlanData {
   int32_t activation;
   int32_t grid;
   int32_t n_blocks;  // 128-column blocks per tile: 1 or 2
+  int32_t pair;      // 1: CTA pairs compute 256 x 256 tiles
   GemmParams params;
   alignas(64) CUtensorMap map_a;
   alignas(64) CUtensorMap map_a64;
@@ -1010,7 +1495,32 @@ int launch_kernel(const PlanData& pd, cudaStream_t stream) {
 }
 
 template <int kOut, int kAct>
+int launch_pair(const PlanData& pd, cudaStream_t stream) {
+  auto kernel = gemm_pair_kernel<kOut, kAct>;
+  static bool configured = false;
+  if (!configured) {
+    LM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(kOut)));
+    configured = true;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(pd.grid);
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = smem_bytes(kOut);
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  LM_CUDA(cudaLaunchKernelEx(&config, kernel, pd.map_a, pd.map_a64, pd.map_a32, pd.map_b, pd.params));
+  return LM_OK;
+}
+
+template <int kOut, int kAct>
 int launch_variant(const PlanData& pd, cudaStream_t stream) {
+  if (pd.pair) return launch_pair<kOut, kAct>(pd, stream);
   return pd.n_blocks == 2 ? launch_kernel<kOut, kAct, 2>(pd, stream) : launch_kernel<kOut, kAct, 1>(pd, stream);
 }
 
@@ -1066,6 +1576,8 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   p.n = a->n;
   // 256-column tiles on request, when N splits into them evenly
   pd.n_blocks = (a->tile_n == 256 && a->n % 256 == 0) ? 2 : 1;
+  // 256 x 256 tiles on CTA pairs when 256-row tiles are asked for as well
+  pd.pair = (pd.n_blocks == 2 && a->tile_m == 256) ? 1 : 0;
   p.n_tiles = (a->n + pd.n_blocks * kTileN - 1) / (pd.n_blocks * kTileN);
   p.atom_cols = a->k / 64;
   p.k_stages = (p.atom_cols + kChunksPerStage - 1) / kChunksPerStage;
@@ -1103,6 +1615,7 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   // tiles loses more than the halved traffic wins), so it needs at least six ring stages.
   p.a_resident =
       (pd.n_blocks == 1 && p.k_stages <= kMaxResident && slots - p.k_stages >= 6 && p.n_tiles >= 2) ? 1 : 0;
+  const int row_tile = pd.pair ? 2 * kTileM : kTileM;
 #ifdef LM_GEMM_PROFILE
   if (p.debug_flags & 4) p.a_resident = 0;
 #endif
@@ -1115,6 +1628,10 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   } else {
     const int per_stage = pd.n_blocks + 1;  // B tile(s) and the A tile
     p.ring_stages = slots / per_stage < kMaxRing ? slots / per_stage : kMaxRing;
+    if (pd.pair) {
+      const int stages = slots * kSlotBytes / kPairStageBytes;
+      p.ring_stages = stages < kMaxRing ? stages : kMaxRing;
+    }
     p.n_per_unit = 1;
   }
 #ifdef LM_GEMM_PROFILE
@@ -1122,8 +1639,15 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
 #endif
   p.units_per_mtile = (p.n_tiles + p.n_per_unit - 1) / p.n_per_unit;
   // more CTAs than units would only idle: rows/128 + experts bounds the row tiles
-  const int64_t max_units = ((a->rows + kTileM - 1) / kTileM + a->experts) * p.units_per_mtile;
-  if (pd.grid > max_units) pd.grid = static_cast<int>(max_units);
+  const int64_t max_units = ((a->rows + row_tile - 1) / row_tile + a->experts) * p.units_per_mtile;
+  if (pd.pair) {
+    // one cluster of two CTAs per unit in flight
+    if (pd.grid > 2 * max_units) pd.grid = static_cast<int>(2 * max_units);
+    pd.grid &= ~1;
+    LM_REQUIRE(pd.grid >= 2, "gemm: CTA pairs need at least two CTAs");
+  } else if (pd.grid > max_units) {
+    pd.grid = static_cast<int>(max_units);
+  }
   int rc = encode_bytes_2d(&pd.map_a, a->a, static_cast<uint64_t>(a->k / 2), static_cast<uint64_t>(a->rows), kTileM);
   if (rc != LM_OK) return rc;
   rc = encode_bytes_2d(&pd.map_a64, a->a, static_cast<uint64_t>(a->k / 2), static_cast<uint64_t>(a->rows), 64);
@@ -1131,7 +1655,7 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   rc = encode_bytes_2d(&pd.map_a32, a->a, static_cast<uint64_t>(a->k / 2), static_cast<uint64_t>(a->rows), 32);
   if (rc != LM_OK) return rc;
   rc = encode_bytes_2d(&pd.map_b, a->b, static_cast<uint64_t>(a->k / 2),
-                       static_cast<uint64_t>(a->experts) * a->n, pd.n_blocks * kTileN);
+                       static_cast<uint64_t>(a->experts) * a->n, pd.pair ? kTileN : pd.n_blocks * kTileN);
   if (rc != LM_OK) return rc;
   memcpy(plan, &pd, sizeof(pd));
   return LM_OK;

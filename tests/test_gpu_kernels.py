@@ -244,7 +244,7 @@ def _device_scales(a, b):
     return _tensor_scale(a.cuda(), None).cpu(), _tensor_scale(b.cuda(), None).cpu()
 
 
-def _run_grouped(cu, a, b, alpha_scale=None, out_dtype=torch.bfloat16, tile_n=128, max_ctas=0):
+def _run_grouped(cu, a, b, alpha_scale=None, out_dtype=torch.bfloat16, tile_n=128, max_ctas=0, tile_m=128):
     from nvfp4moe_b200 import gemm
 
     experts, n, k = b.shape
@@ -254,7 +254,7 @@ def _run_grouped(cu, a, b, alpha_scale=None, out_dtype=torch.bfloat16, tile_n=12
     if alpha_scale is not None:
         alpha = alpha * alpha_scale.cuda()
     out = torch.full((a.shape[0], n), float("nan"), dtype=out_dtype, device="cuda")
-    plan = gemm.GroupedGemm(experts, n, k, 128, tile_n, output_dtype=out_dtype)
+    plan = gemm.GroupedGemm(experts, n, k, tile_m, tile_n, output_dtype=out_dtype)
     plan.max_ctas = max_ctas
     plan(qa, qb, out, cu.cuda(), sfa, sfb, alpha)
     torch.cuda.synchronize()
@@ -338,6 +338,21 @@ def test_grouped_gemm_wide_tiles_bit_identical(out_dtype, max_ctas):
     assert _lib.device_status() == 0
 
 
+@pytest.mark.parametrize("out_dtype", (torch.bfloat16, torch.float32))
+@pytest.mark.parametrize("max_ctas", (0, 4))
+def test_grouped_gemm_cta_pairs_bit_identical(out_dtype, max_ctas):
+    """256 x 256 tiles on CTA pairs accumulate every output in the same order as 128 x 128 tiles."""
+    lens = [130, 0, 257, 5, 128, 300, 0, 64, 513, 256]
+    cu, a, b = _grouped_case(lens, 1024, 1280, seed=78, b_std=0.05)
+    narrow, _ = _run_grouped(cu, a, b, out_dtype=out_dtype)
+    pairs, _ = _run_grouped(cu, a, b, out_dtype=out_dtype, tile_n=256, tile_m=256, max_ctas=max_ctas)
+    assert torch.isfinite(pairs).all()
+    assert torch.equal(pairs, narrow)
+    from nvfp4moe_b200 import _lib
+
+    assert _lib.device_status() == 0
+
+
 def test_grouped_gemm_fp32_output_and_per_expert_alpha():
     lens = [3, 5, 2, 7]
     cu, a, b = _grouped_case(lens, 128, 256, seed=20260822, b_std=1.0)
@@ -379,8 +394,8 @@ def test_dense_gemm_matches_oracle():
     (("swiglu", None), ("swiglu", 10.0), ("swiglu_oai", None), ("geglu", None), ("reglu", None),
      ("relu2", None)),
 )
-@pytest.mark.parametrize("tile_n", (128, 256))
-def test_fused_epilogue_matches_oracle(activation, clamp, tile_n):
+@pytest.mark.parametrize(("tile_m", "tile_n"), ((128, 128), (128, 256), (256, 256)))
+def test_fused_epilogue_matches_oracle(activation, clamp, tile_m, tile_n):
     from nvfp4moe_b200 import gemm
     from nvfp4moe_b200.kernels.gated import GatedEpilogue
     from nvfp4moe_b200.kernels.unary import UnaryEpilogue
@@ -406,7 +421,7 @@ def test_fused_epilogue_matches_oracle(activation, clamp, tile_n):
     qh = torch.zeros(rows, inter // 2, dtype=torch.uint8, device="cuda")
     sfh = torch.zeros(1, tiles, inter // 64, 32, 4, 4, dtype=torch.float8_e4m3fn, device="cuda")
     pair = torch.cat((h_pts, 1.0 / h_pts)).cuda()
-    plan = gemm.GroupedGemm(len(lens), n, hidden, 128, tile_n, output_dtype=torch.float4_e2m1fn_x2,
+    plan = gemm.GroupedGemm(len(lens), n, hidden, tile_m, tile_n, output_dtype=torch.float4_e2m1fn_x2,
                             epilogue=policy)
     plan.max_ctas = 2 if tile_n == 256 else 0
     plan(qa, qb, qh.view(torch.float4_e2m1fn_x2), cu.cuda(), sfa, sfb, alpha, output_sf=sfh,
