@@ -55,8 +55,8 @@ constexpr int kSfBytes = kChunksPerStage * 512;          // 2048
 constexpr int kSlotBytes = kTileBytes + kSfBytes;        // 18432
 constexpr int kMaxRing = 8;      // ring stages (also TMEM scale-factor slots)
 constexpr int kMaxResident = 8;  // resident A stages: K <= 2048
-constexpr int kStoreRowPitch = 64 * 2 + 16;              // BF16 staging row: 64 columns + pad
-constexpr int kStoreBytesPerWarp = 32 * kStoreRowPitch;
+constexpr int kStoreRowPitch = 64 * 2;                   // BF16 staging row: 64 columns, 128-byte swizzled
+constexpr int kStoreBytesPerWarp = 32 * kStoreRowPitch;  // 4 KB: four swizzle atoms of 8 rows
 constexpr int kStoreBytes = kEpilogueWarps * kStoreBytesPerWarp;
 constexpr int kMiscBytes = 4096;
 constexpr int kSmemLimit = 232448;
@@ -126,6 +126,7 @@ struct GemmParams {
   uint8_t* out_sf;
   const float* out_scale;
   const uint64_t* out_row_ptrs;  // BF16 output: optional address of every output row
+  int tma_store;                 // BF16 output: whole 32-row blocks leave through TMA stores
   int out_atom_cols;  // NVFP4 output: out_n / 64
   float clamp_limit;
   float sigmoid_alpha;
@@ -208,6 +209,22 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
       "l"(src), "r"(bytes), "r"(bar)
       : "memory");
+}
+
+// 32 rows x 64 BF16 columns from swizzled shared memory to global memory; out-of-range columns
+// and rows are clipped by the tensor map.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// The stores issued so far have read their shared memory / have completed.
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() {
@@ -407,7 +424,8 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // What an epilogue warp needs to drain its share of one accumulator.
 struct DrainContext {
   uint32_t lane_base;        // TMEM address of the warp's 32 lanes, column 0
-  uint32_t warp_store;       // the warp's BF16 staging in shared memory
+  uint32_t warp_store;       // the warp's BF16 staging in shared memory (1024-byte aligned)
+  const CUtensorMap* out_map;  // BF16 output: tensor map of the output (32 x 64 boxes)
   uint32_t bar_shared_cols;  // signalled when the columns both accumulators use are in registers
   uint32_t bar_acc_empty;    // signalled when the whole accumulator is in registers
   bool remote;               // the two barriers are cluster addresses (the pair leader's)
@@ -500,11 +518,18 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
         }
       }
     } else if (kOut == LM_OUT_BF16) {
-      // lane = row: the warp's 32 x 64 block goes to its shared-memory staging
+      // lane = row: the warp's 32 x 64 block goes to its shared-memory staging, 16-byte chunk c
+      // of row r at chunk c ^ (r % 8) (the 128-byte swizzle the output tensor map expects; it
+      // also keeps these stores and the transposed loads free of bank conflicts)
+      if (half == 0) {
+        // the previous slice's TMA store must have read the staging
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
+      }
 #pragma unroll
       for (int i = 0; i < 4; ++i)
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(warp_store + lane * kStoreRowPitch +
-                                                                       half * 64 + i * 16),
+                                                                       (((half * 4 + i) ^ (lane & 7)) * 16)),
                      "r"(pack_bf16x2(__uint_as_float(v[8 * i]) * alpha, __uint_as_float(v[8 * i + 1]) * alpha)),
                      "r"(pack_bf16x2(__uint_as_float(v[8 * i + 2]) * alpha, __uint_as_float(v[8 * i + 3]) * alpha)),
                      "r"(pack_bf16x2(__uint_as_float(v[8 * i + 4]) * alpha, __uint_as_float(v[8 * i + 5]) * alpha)),
@@ -547,10 +572,21 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
         }
       }
     } else if (kOut == LM_OUT_BF16) {
+      const int rows_here = t.valid - quarter * 32;  // valid rows among this warp's 32
+      if (p.tma_store && p.out_row_ptrs == nullptr && rows_here >= 32) {
+        // the whole block belongs to this expert: one TMA store moves it
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+#ifdef LM_GEMM_PROFILE
+        if (!(p.debug_flags & 8))
+#endif
+        if (lane == 0 && cols_ok)
+          tma_store_2d(c.out_map, warp_store, col64 * 64, t.row0 + quarter * 32);
+        return;
+      }
       // transposed read: a global store covers four whole 128-byte row pieces
       __syncwarp();
       if (rows_any && cols_ok) {
-        const int rows_here = t.valid - quarter * 32;  // valid rows among this warp's 32
         __nv_bfloat16* warp_out =
             static_cast<__nv_bfloat16*>(p.out) + (static_cast<int64_t>(t.row0) + quarter * 32) * p.n;
         const int piece = lane & 7;
@@ -560,7 +596,8 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
         for (int i = 0; i < 8; ++i)
           asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                        : "=r"(d[i].x), "=r"(d[i].y), "=r"(d[i].z), "=r"(d[i].w)
-                       : "r"(warp_store + (4 * i + (lane >> 3)) * kStoreRowPitch + piece * 16));
+                       : "r"(warp_store + (4 * i + (lane >> 3)) * kStoreRowPitch +
+                             ((piece ^ ((4 * i + (lane >> 3)) & 7)) * 16)));
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int row = 4 * i + (lane >> 3);
@@ -612,7 +649,7 @@ template <int kOut, int kAct, int kNB>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64,
             const __grid_constant__ CUtensorMap tmap_a32, const __grid_constant__ CUtensorMap tmap_b,
-            const GemmParams p) {
+            const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -935,6 +972,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     ctx.lane = lane;
     ctx.lane_base = tmem_base + (static_cast<uint32_t>(ctx.quarter * 32) << 16);
     ctx.warp_store = store_base + (warp - kFirstEpilogueWarp) * kStoreBytesPerWarp;
+    ctx.out_map = &tmap_out;
     ctx.bar_shared_cols = smem_u32(&misc->shared_cols_free);
     ctx.remote = false;
     ctx.acc1_col = kWideAcc1Col;
@@ -963,6 +1001,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       }
     }
     LM_PROF_END(prof_acc1);
+    if (kOut == LM_OUT_BF16 && lane == 0) tma_store_wait_all();
     if (warp == kFirstEpilogueWarp && lane == 0) {
       LM_PROF_STORE(3, prof_acc0);
       LM_PROF_STORE(4, prof_acc1);
@@ -1088,7 +1127,7 @@ template <int kOut, int kAct>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64,
                  const __grid_constant__ CUtensorMap tmap_a32, const __grid_constant__ CUtensorMap tmap_b,
-                 const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -1388,6 +1427,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     ctx.lane = lane;
     ctx.lane_base = tmem_base + (static_cast<uint32_t>(ctx.quarter * 32) << 16);
     ctx.warp_store = store_base + (warp - kFirstEpilogueWarp) * kStoreBytesPerWarp;
+    ctx.out_map = &tmap_out;
     ctx.remote = !leader;
     ctx.acc1_col = kPairAcc1Col;
     ctx.wide_overlap = true;
@@ -1411,6 +1451,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         drain_tile<kOut, kAct, 2>(p, t, ctx, acc, nt);
       }
     }
+    if (kOut == LM_OUT_BF16 && lane == 0) tma_store_wait_all();
   }
 
   // ---- teardown: neither CTA leaves while the other may still signal its barriers
@@ -1443,6 +1484,7 @@ struct PlanData {
   alignas(64) CUtensorMap map_a64;
   alignas(64) CUtensorMap map_a32;
   alignas(64) CUtensorMap map_b;
+  alignas(64) CUtensorMap map_out;
 };
 static_assert(sizeof(PlanData) <= sizeof(lm_gemm_plan), "plan storage too small");
 constexpr uint32_t kPlanMagic = 0x4C4D4750u;
@@ -1480,6 +1522,21 @@ int encode_bytes_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, ui
   return LM_OK;
 }
 
+// BF16 output as 32-row x 64-column boxes in the 128-byte swizzle of the epilogue's staging.
+int encode_out_bf16(CUtensorMap* map, void* base, uint64_t cols, uint64_t rows) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return set_error(LM_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {64, 32};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(LM_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+  return LM_OK;
+}
+
 template <int kOut, int kAct, int kNB>
 int launch_kernel(const PlanData& pd, cudaStream_t stream) {
   auto kernel = gemm_kernel<kOut, kAct, kNB>;
@@ -1489,7 +1546,7 @@ int launch_kernel(const PlanData& pd, cudaStream_t stream) {
     configured = true;
   }
   kernel<<<pd.grid, kThreads, smem_bytes(kOut), stream>>>(pd.map_a, pd.map_a64, pd.map_a32, pd.map_b,
-                                                          pd.params);
+                                                          pd.map_out, pd.params);
   LM_CUDA(cudaGetLastError());
   return LM_OK;
 }
@@ -1514,7 +1571,8 @@ int launch_pair(const PlanData& pd, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   config.attrs = attr;
   config.numAttrs = 1;
-  LM_CUDA(cudaLaunchKernelEx(&config, kernel, pd.map_a, pd.map_a64, pd.map_a32, pd.map_b, pd.params));
+  LM_CUDA(cudaLaunchKernelEx(&config, kernel, pd.map_a, pd.map_a64, pd.map_a32, pd.map_b, pd.map_out,
+                             pd.params));
   return LM_OK;
 }
 
@@ -1657,6 +1715,13 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   rc = encode_bytes_2d(&pd.map_b, a->b, static_cast<uint64_t>(a->k / 2),
                        static_cast<uint64_t>(a->experts) * a->n, pd.pair ? kTileN : pd.n_blocks * kTileN);
   if (rc != LM_OK) return rc;
+  // whole 32-row blocks of a BF16 result leave through TMA stores (the SM's plain store path
+  // was the bottleneck of short-K GEMMs); rows through a pointer table cannot
+  p.tma_store = (a->out_kind == LM_OUT_BF16 && a->out_row_ptrs == nullptr && a->n >= 64) ? 1 : 0;
+  if (p.tma_store) {
+    rc = encode_out_bf16(&pd.map_out, a->out, static_cast<uint64_t>(a->n), static_cast<uint64_t>(a->rows));
+    if (rc != LM_OK) return rc;
+  }
   memcpy(plan, &pd, sizeof(pd));
   return LM_OK;
 }
