@@ -240,6 +240,19 @@ int lm_gemm_prepare(const lm_gemm_args* args, lm_gemm_plan* plan);
 /* Launches a prepared GEMM.  Safe inside CUDA Graph capture. */
 int lm_gemm_launch(const lm_gemm_plan* plan, lm_stream_t stream);
 
+/*
+ * Router step in front of lm_dispatch: softmax over the experts, top-k, renormalise, as the
+ * reference's tests and benchmarks prepare their routing inputs with torch
+ * (tests/test_training_gpu.py:23-27, benchmarks/moe.py: softmax -> topk -> divide by the sum).
+ * The reference leaves this step to the host framework and keeps it out of its timings
+ * (BENCHMARKS.md:15).
+ *   logits        (tokens, experts) BF16 or FP32 (LM_DTYPE_*), experts <= 256
+ *   topk_ids      (tokens, top_k) int32, larger probability first, lower id on a tie
+ *   topk_weights  (tokens, top_k) FP32, summing to 1 per token
+ */
+int lm_route_topk(const void* logits, int logits_dtype, int64_t tokens, int experts, int top_k,
+                  int32_t* topk_ids, float* topk_weights, lm_stream_t stream);
+
 /* ---------------------------------------------------------------- expert parallel
  * The reference has no communication code (README.md:227-228 leaves expert-parallel
  * exchange to the host framework); these two entry points are that exchange for one

@@ -72,6 +72,7 @@ _SIGNATURES = {
         c_i32,
         [c_ptr, c_i64, c_i32, c_i32, c_ptr, c_ptr, c_ptr, c_i32, c_ptr, c_ptr, c_ptr, c_ptr],
     ),
+    "lm_route_topk": (c_i32, [c_ptr, c_i32, c_i64, c_i32, c_i32, c_ptr, c_ptr, c_ptr]),
     "lm_ep_plan": (
         c_i32,
         [c_ptr, c_i32, c_i32, c_i32, c_i64, c_i64, ctypes.POINTER(ctypes.c_uint64), c_ptr, c_ptr, c_ptr,

@@ -262,6 +262,14 @@ def sf_from_varlen(buf: torch.Tensor, m_indptr, groups: int) -> torch.Tensor:
 # --------------------------------------------------------------------------
 
 
+def route_topk(logits: torch.Tensor, top_k: int):
+    """softmax -> topk -> renormalise, the recipe the reference's tests build their routing
+    inputs with (``tests/test_training_gpu.py:23-27``)."""
+    probs = torch.softmax(logits.float(), dim=-1)
+    topv, topi = torch.topk(probs, top_k, dim=-1)
+    return topi.to(torch.int32), (topv / topv.sum(-1, keepdim=True)).float()
+
+
 def dispatch(topk_ids: torch.Tensor, topk_weights: torch.Tensor, experts: int,
              plan_tile_rows: int = 128, plan_len: int | None = None):
     """Stable expert-major permutation of (token, route) pairs.

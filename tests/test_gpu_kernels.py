@@ -480,3 +480,47 @@ def test_fused_decode_prepare_matches_oracle(tokens, experts, k, features):
     assert torch.equal(plan[-experts:], ref[5][-experts:])
     assert torch.equal(q.cpu(), q_ref)
     assert torch.equal(O.sf_from_varlen(sf.cpu(), ref[1], features // 16), sf_ref)
+
+
+# --------------------------------------------------------------------------
+# router step: softmax -> top-k -> renormalise
+# --------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize(("tokens", "experts", "k", "dtype"),
+                         ((1, 8, 2, torch.float32), (333, 256, 8, torch.float32), (64, 128, 4, torch.bfloat16),
+                          (1000, 48, 6, torch.float32), (17, 5, 5, torch.float32)))
+def test_route_topk_matches_torch_recipe(tokens, experts, k, dtype):
+    from nvfp4moe_b200.routing import route_topk
+
+    g = torch.Generator().manual_seed(tokens + experts)
+    logits = (torch.randn(tokens, experts, generator=g) * 3.0).to(dtype)
+    ids_ref, w_ref = O.route_topk(logits, k)
+    ids, w = route_topk(logits.cuda(), k)
+    torch.cuda.synchronize()
+    assert ids.dtype == torch.int32 and w.dtype == torch.float32
+    if dtype == torch.float32:
+        assert torch.equal(ids.cpu(), ids_ref)
+    else:  # BF16 logits tie often: the winners must carry the same probabilities
+        probs = torch.softmax(logits.float(), -1)
+        assert torch.equal(probs.gather(1, ids.cpu().long()), probs.gather(1, ids_ref.long()))
+        assert (ids.cpu().sort(1).values[:, 1:] != ids.cpu().sort(1).values[:, :-1]).all()
+    assert torch.allclose(w.cpu(), w_ref, rtol=2e-6, atol=1e-8)
+    assert torch.allclose(w.cpu().sum(1), torch.ones(tokens), atol=1e-6)
+    # feeds the dispatch directly
+    from nvfp4moe_b200.kernels.routing.dispatch import MoEDispatch
+
+    _, m_indptr, _, _ = MoEDispatch(tokens, experts, k)(ids, w)
+    assert int(m_indptr[-1]) == tokens * k
+
+
+def test_route_topk_rejects_bad_arguments():
+    from nvfp4moe_b200.routing import route_topk
+
+    logits = torch.zeros(4, 300, device="cuda")
+    with pytest.raises(ValueError, match="at most 256 experts"):
+        route_topk(logits, 2)
+    with pytest.raises(ValueError, match="top_k"):
+        route_topk(torch.zeros(4, 8, device="cuda"), 9)
+    with pytest.raises(ValueError, match="BF16 or FP32"):
+        route_topk(torch.zeros(4, 8, device="cuda", dtype=torch.float16), 2)

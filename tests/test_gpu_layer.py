@@ -353,3 +353,44 @@ def test_host_pipeline_matches_direct_steps():
         pipe.submit(batches[0][0].clone(), *batches[0][1:])
     with pytest.raises(ValueError, match="unknown ticket"):
         pipe.wait(99)
+
+
+def test_packed_weights_with_per_expert_scales():
+    """Checkpoint-style weights: every expert packed on its own FP32 scale, passed as (E,)
+    tensors to ``load_packed_weights`` (reference ``inference.py:398-469``)."""
+    from nvfp4moe_b200 import InferenceMoE
+
+    tokens, hidden, inter, experts, k = 160, 256, 128, 6, 2
+    first, second, down = _weights(experts, hidden, inter, 31)
+    # make the experts' magnitudes differ so that a shared scale would not do
+    gain = torch.tensor([0.25, 1.0, 4.0, 0.5, 2.0, 8.0]).view(experts, 1, 1)
+    first, second, down = (first.float() * gain).to(torch.bfloat16), (second.float() * gain).to(torch.bfloat16), \
+        (down.float() * gain).to(torch.bfloat16)
+    gate_up = O.interleave_gate_up(first, second)
+    packed1 = [O.pack_weights(gate_up[e : e + 1]) for e in range(experts)]
+    packed2 = [O.pack_weights(down[e : e + 1]) for e in range(experts)]
+    q1 = torch.cat([p[0] for p in packed1]); sf1 = torch.cat([p[1] for p in packed1])
+    s1 = torch.cat([torch.as_tensor(p[2], dtype=torch.float32).reshape(1) for p in packed1])
+    q2 = torch.cat([p[0] for p in packed2]); sf2 = torch.cat([p[1] for p in packed2])
+    s2 = torch.cat([torch.as_tensor(p[2], dtype=torch.float32).reshape(1) for p in packed2])
+    assert float(s1.max() / s1.min()) > 8.0
+
+    g = torch.Generator().manual_seed(32)
+    x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16)
+    ids, w = _routing(tokens, experts, k, 33)
+    x_scale, h_scale = torch.tensor([2.0e-3]), torch.tensor([4.0e-3])
+    ref = O.moe_layer(x, ids, w, q1, sf1, s1, q2, sf2, s2, x_scale, h_scale)
+
+    def blocked(sf, rows, cols):  # (E, rows, cols/16) bytes -> the (E, rows/128, cols/64, 32, 4, 4) weight layout
+        return torch.stack([O.sf_to_blocked(sf[e]) for e in range(experts)]).view(
+            experts, -(-rows // 128), cols // 64, 32, 4, 4)
+
+    dev = torch.device("cuda", 0)
+    plan = InferenceMoE(hidden, inter, experts, k, tokens, device=dev)
+    plan.load_packed_weights(q1.to(dev).view(torch.float4_e2m1fn_x2), blocked(sf1, 2 * inter, hidden).to(dev).view(torch.float8_e4m3fn),
+                             s1.to(dev), q2.to(dev).view(torch.float4_e2m1fn_x2),
+                             blocked(sf2, hidden, inter).to(dev).view(torch.float8_e4m3fn), s2.to(dev))
+    plan.set_activation_scales(x_scale.to(dev), h_scale.to(dev))
+    out = plan.run(x.to(dev), ids.to(dev), w.to(dev)).cpu()
+    assert torch.isfinite(out).all()
+    assert O.rel_frobenius(out.float(), ref.float()) <= LAYER_REL_TOL
