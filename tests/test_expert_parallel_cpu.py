@@ -95,3 +95,39 @@ def test_expert_count_must_divide_over_ranks(monkeypatch):
     monkeypatch.setattr(dist, "get_rank", lambda group=None: 0)
     with pytest.raises(ValueError, match="divisible"):
         ExpertParallelExchange(EXPERTS)
+
+
+def test_route_plan_restatement_is_a_bijection():
+    """Every row a rank sends lands on exactly one owner row, and the owner's table of origins
+    points back at it: the two views the peer transport derives from the gathered counts agree."""
+    import random
+
+    from oracle import nvfp4_oracle as O
+
+    rng = random.Random(7)
+    for world, experts in ((1, 4), (2, 8), (4, 16), (8, 64)):
+        local = experts // world
+        counts = [[rng.choice((0, 0, 1, 3, 17, 130)) for _ in range(experts)] for _ in range(world)]
+        plans = [O.ep_route_plan(counts, rank) for rank in range(world)]
+        for owner in range(world):
+            own_indptr, _, _, origin, owner_rows = plans[owner]
+            assert own_indptr[0] == 0 and own_indptr[-1] == owner_rows[owner] == len(origin)
+            assert all(b >= a for a, b in zip(own_indptr, own_indptr[1:]))
+        landed = {}
+        for source in range(world):
+            _, dest_base, owner_start, _, _ = plans[source]
+            src_row = 0
+            for e in range(experts):
+                owner, l = divmod(e, local)
+                own_indptr = plans[owner][0]
+                assert owner_start[e] == own_indptr[l]
+                for j in range(counts[source][e]):
+                    key = (owner, dest_base[e] + j)
+                    assert key not in landed
+                    assert own_indptr[l] <= key[1] < own_indptr[l + 1]
+                    landed[key] = (source, src_row)
+                    src_row += 1
+        for owner in range(world):
+            for row, origin in enumerate(plans[owner][3]):
+                assert landed[(owner, row)] == origin
+        assert len(landed) == sum(map(sum, counts))
