@@ -127,44 +127,52 @@ struct SendParams {
   uint8_t* sf[kMaxRanks];      // every rank's row-major scale factors, features/16 bytes a row
 };
 
-// One warp per (token, 512-feature slice), as in the single-GPU scatter quantizer; only the
-// destination differs: the owner's buffer and the row the route plan assigns.
+// One warp per token, as in the single-GPU scatter quantizer; only the destinations differ:
+// the owner's buffers and the rows the route plan assigns.
 __global__ void __launch_bounds__(kThreads) ep_quantize_send_kernel(SendParams p) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int64_t token = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
   if (token >= p.tokens || __ldg(p.valid) == 0) return;
-  const int col = blockIdx.y * kTileCols + lane * 16;
-  const bool col_ok = col < p.features;
-  int my_row = -1, my_owner = 0;
+  uint8_t* my_q = nullptr;
+  uint8_t* my_sf = nullptr;
   if (lane < p.top_k) {
     const int slot = __ldg(p.slots + token * p.top_k + lane);
     if (slot >= 0) {
       const int e = __ldg(p.topk_ids + token * p.top_k + lane);
-      my_owner = e / p.local_experts;
-      my_row = __ldg(p.dest_base + e) + (slot - __ldg(p.src_indptr + e));
+      const int owner = e / p.local_experts;
+      const int64_t row = __ldg(p.dest_base + e) + (slot - __ldg(p.src_indptr + e));
+      my_q = p.q[owner] + row * (p.features >> 1);
+      my_sf = p.sf[owner] + row * (p.features >> 4);
     }
   }
   const float pts = __ldg(p.scale_pair);
   const float inv_pts = __ldg(p.scale_pair + 1);
-  Slice<__nv_bfloat16> v;
-  uint2 packed = make_uint2(0, 0);
-  uint32_t sf_byte = 0;
-  if (col_ok) {
-    v.load(p.x + token * p.features + col);
-    sf_byte = quantize_group(v, pts, inv_pts, true, &packed);
-  }
-  uint32_t word = sf_byte;
-  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 1) << 8;
-  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 2) << 16;
-  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 3) << 24;
-  for (int j = 0; j < p.top_k; ++j) {
-    const int row = __shfl_sync(0xFFFFFFFFu, my_row, j);
-    const int owner = __shfl_sync(0xFFFFFFFFu, my_owner, j);
-    if (row < 0 || !col_ok) continue;
-    *reinterpret_cast<uint2*>(p.q[owner] + static_cast<int64_t>(row) * (p.features >> 1) + (col >> 1)) = packed;
-    if ((lane & 3) == 0)
-      *reinterpret_cast<uint32_t*>(p.sf[owner] + static_cast<int64_t>(row) * (p.features >> 4) + (col >> 4)) = word;
+  const __nv_bfloat16* x_row = p.x + token * p.features;
+  Slice<__nv_bfloat16> cur, next;
+  int col = lane * 16;
+  if (col < p.features) cur.load(x_row + col);
+  for (; col - lane * 16 < p.features; col += kTileCols) {
+    const bool col_ok = col < p.features;
+    const int next_col = col + kTileCols;
+    if (next_col < p.features) next.load(x_row + next_col);
+    uint2 packed = make_uint2(0, 0);
+    uint32_t sf_byte = 0;
+    if (col_ok) sf_byte = quantize_group(cur, pts, inv_pts, true, &packed);
+    uint32_t word = sf_byte;
+    word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 1) << 8;
+    word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 2) << 16;
+    word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 3) << 24;
+    for (int j = 0; j < p.top_k; ++j) {
+      uint8_t* q_row = reinterpret_cast<uint8_t*>(
+          __shfl_sync(0xFFFFFFFFu, reinterpret_cast<unsigned long long>(my_q), j));
+      uint8_t* sf_row = reinterpret_cast<uint8_t*>(
+          __shfl_sync(0xFFFFFFFFu, reinterpret_cast<unsigned long long>(my_sf), j));
+      if (q_row == nullptr || !col_ok) continue;
+      *reinterpret_cast<uint2*>(q_row + (col >> 1)) = packed;
+      if ((lane & 3) == 0) *reinterpret_cast<uint32_t*>(sf_row + (col >> 4)) = word;
+    }
+    cur = next;
   }
 }
 
@@ -363,7 +371,7 @@ extern "C" int lm_ep_quantize_send(const void* x, int64_t tokens, int features, 
     p.q[g] = reinterpret_cast<uint8_t*>(q_base[g]);
     p.sf[g] = reinterpret_cast<uint8_t*>(sf_base[g]);
   }
-  dim3 grid(static_cast<unsigned>((tokens + kWarps - 1) / kWarps), (features + kTileCols - 1) / kTileCols);
+  dim3 grid(static_cast<unsigned>((tokens + kWarps - 1) / kWarps));
   ep_quantize_send_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(p);
   LM_CUDA(cudaGetLastError());
   return LM_OK;

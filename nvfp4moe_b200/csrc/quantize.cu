@@ -154,9 +154,10 @@ __global__ void __launch_bounds__(kThreads, 4) quantize_rowwise_kernel(QuantPara
 }
 
 // ------------------------------------------------- quantize once, scatter to slots
-// One warp per (token, 512-feature slice): the slice is quantized once and its packed codes
-// (256 B, one coalesced store) and scale factors (eight 4-byte words, one per 64-feature atom)
-// are written to every expert-major row the token was routed to.
+// One warp per token: its destinations (one row per route) are worked out once, then every
+// 512-feature slice is quantized once and its packed codes (256 B, one coalesced store) and
+// scale factors (eight 4-byte words, one per 64-feature atom) are written to every
+// expert-major row the token was routed to.
 struct ScatterQuantParams {
   const __nv_bfloat16* x;
   int64_t tokens;
@@ -175,46 +176,53 @@ __global__ void __launch_bounds__(kThreads) quantize_scatter_kernel(ScatterQuant
   const int lane = threadIdx.x & 31;
   const int64_t token = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
   if (token >= p.tokens) return;
-  const int col = blockIdx.y * kTileCols + lane * 16;
-  const bool col_ok = col < p.features;
-  // destination of route `lane` (lanes beyond top_k idle): row, then its scale-factor atom row
-  int my_slot = -1, my_atom_row = 0, my_r = 0;
+  // Destination of route `lane` (lanes beyond top_k idle), computed once per token: the
+  // row's packed bytes and the byte of its first scale-factor word (atom column 0).
+  const int atom_cols = p.features >> 6;
+  uint8_t* my_q = nullptr;
+  uint8_t* my_sf = nullptr;
   if (lane < p.top_k) {
-    my_slot = __ldg(p.slots + token * p.top_k + lane);
-    if (my_slot >= 0) {
+    const int slot = __ldg(p.slots + token * p.top_k + lane);
+    if (slot >= 0) {
       const int e = __ldg(p.topk_ids + token * p.top_k + lane);
       const int lo = __ldg(p.m_indptr + e);
-      const int local = my_slot - lo;
-      my_atom_row = lo / kTileRows + e + local / kTileRows;
-      my_r = local % kTileRows;
+      const int local = slot - lo;
+      const int atom_row = lo / kTileRows + e + local / kTileRows;
+      const int r = local % kTileRows;
+      my_q = p.q + static_cast<int64_t>(slot) * (p.features >> 1);
+      my_sf = p.sf + static_cast<int64_t>(atom_row) * atom_cols * 512 + (r & 31) * 16 + (r >> 5) * 4;
     }
   }
   const float pts = __ldg(p.scale_pair);
   const float inv_pts = __ldg(p.scale_pair + 1);
-  Slice<__nv_bfloat16> v;
-  uint2 packed = make_uint2(0, 0);
-  uint32_t sf_byte = 0;
-  if (col_ok) {
-    v.load(p.x + token * p.features + col);
-    sf_byte = quantize_group(v, pts, inv_pts, true, &packed);
-  }
-  // four neighbouring lanes hold the four factors of one atom word
-  uint32_t word = sf_byte;
-  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 1) << 8;
-  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 2) << 16;
-  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 3) << 24;
-  const int atom_cols = p.features >> 6;
-  for (int j = 0; j < p.top_k; ++j) {
-    const int slot = __shfl_sync(0xFFFFFFFFu, my_slot, j);
-    const int atom_row = __shfl_sync(0xFFFFFFFFu, my_atom_row, j);
-    const int r = __shfl_sync(0xFFFFFFFFu, my_r, j);
-    if (slot < 0 || !col_ok) continue;
-    *reinterpret_cast<uint2*>(p.q + static_cast<int64_t>(slot) * (p.features >> 1) + (col >> 1)) = packed;
-    if ((lane & 3) == 0) {
-      uint8_t* dst = p.sf + (static_cast<int64_t>(atom_row) * atom_cols + (col >> 6)) * 512 +
-                     (r & 31) * 16 + (r >> 5) * 4;
-      *reinterpret_cast<uint32_t*>(dst) = word;
+  const __nv_bfloat16* x_row = p.x + token * p.features;
+  // the warp walks the token's 512-feature slices; the next slice is loaded while this one
+  // is quantized and stored
+  Slice<__nv_bfloat16> cur, next;
+  int col = lane * 16;
+  if (col < p.features) cur.load(x_row + col);
+  for (; col - lane * 16 < p.features; col += kTileCols) {
+    const bool col_ok = col < p.features;
+    const int next_col = col + kTileCols;
+    if (next_col < p.features) next.load(x_row + next_col);
+    uint2 packed = make_uint2(0, 0);
+    uint32_t sf_byte = 0;
+    if (col_ok) sf_byte = quantize_group(cur, pts, inv_pts, true, &packed);
+    // four neighbouring lanes hold the four factors of one atom word
+    uint32_t word = sf_byte;
+    word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 1) << 8;
+    word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 2) << 16;
+    word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 3) << 24;
+    for (int j = 0; j < p.top_k; ++j) {
+      uint8_t* q_row = reinterpret_cast<uint8_t*>(
+          __shfl_sync(0xFFFFFFFFu, reinterpret_cast<unsigned long long>(my_q), j));
+      uint8_t* sf_row = reinterpret_cast<uint8_t*>(
+          __shfl_sync(0xFFFFFFFFu, reinterpret_cast<unsigned long long>(my_sf), j));
+      if (q_row == nullptr || !col_ok) continue;
+      *reinterpret_cast<uint2*>(q_row + (col >> 1)) = packed;
+      if ((lane & 3) == 0) *reinterpret_cast<uint32_t*>(sf_row + static_cast<int64_t>(col >> 6) * 512) = word;
     }
+    cur = next;
   }
 }
 
@@ -281,7 +289,7 @@ extern "C" int lm_quantize_decode(const void* x, int64_t tokens, int features, i
   LM_REQUIRE(top_k <= 32, "quantize_decode: top_k must be at most 32");
   ScatterQuantParams p{static_cast<const __nv_bfloat16*>(x), tokens, features, top_k, slots,
                        topk_ids, m_indptr, scale_pair, q, sf};
-  dim3 grid(static_cast<unsigned>((tokens + kWarps - 1) / kWarps), (features + kTileCols - 1) / kTileCols);
+  dim3 grid(static_cast<unsigned>((tokens + kWarps - 1) / kWarps));
   quantize_scatter_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(p);
   LM_CUDA(cudaGetLastError());
   return LM_OK;
