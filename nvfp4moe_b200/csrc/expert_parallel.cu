@@ -53,26 +53,58 @@ __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(PlanParams p) {
   const int E = p.experts, G = p.world, L = p.local_experts;
   for (int i = tid; i < G * E; i += kPlanThreads) s_cnt[i / E][i % E] = __ldg(p.counts_all + i);
   __syncthreads();
-  if (tid < G) {  // exclusive prefix over the experts of source tid
-    int run = 0;
-    for (int e = 0; e < E; ++e) {
-      s_src_start[tid][e] = run;
-      run += s_cnt[tid][e];
-    }
-  }
+  const int warp = tid >> 5, lane = tid & 31;
   for (int e = tid; e < E; e += kPlanThreads) {
     int total = 0;
     for (int g = 0; g < G; ++g) total += s_cnt[g][e];
     s_total[e] = total;
   }
   __syncthreads();
-  if (tid < G) {  // exclusive prefix over the local experts of owner tid
-    int run = 0;
-    for (int l = 0; l < L; ++l) {
-      s_owner_start[tid * L + l] = run;
-      run += s_total[tid * L + l];
+  // Warp w: exclusive prefix over the experts of source w, then over the local experts of
+  // owner w.  A lane owns a run of consecutive entries; a warp scan joins the runs.
+  for (int g = warp; g < G; g += kPlanThreads / 32) {
+    const int per_lane = (E + 31) / 32;
+    int sum = 0;
+    for (int i = 0; i < per_lane; ++i) {
+      const int e = lane * per_lane + i;
+      if (e < E) sum += s_cnt[g][e];
     }
-    s_owner_rows[tid] = run;
+    int incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int up = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+      if (lane >= d) incl += up;
+    }
+    int run = incl - sum;
+    for (int i = 0; i < per_lane; ++i) {
+      const int e = lane * per_lane + i;
+      if (e < E) {
+        s_src_start[g][e] = run;
+        run += s_cnt[g][e];
+      }
+    }
+    // owner g
+    const int per_lane_l = (L + 31) / 32;
+    sum = 0;
+    for (int i = 0; i < per_lane_l; ++i) {
+      const int l = lane * per_lane_l + i;
+      if (l < L) sum += s_total[g * L + l];
+    }
+    incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int up = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+      if (lane >= d) incl += up;
+    }
+    run = incl - sum;
+    for (int i = 0; i < per_lane_l; ++i) {
+      const int l = lane * per_lane_l + i;
+      if (l < L) {
+        s_owner_start[g * L + l] = run;
+        run += s_total[g * L + l];
+      }
+    }
+    if (lane == 31) s_owner_rows[g] = incl;
   }
   __syncthreads();
   bool fits = true;
@@ -194,22 +226,19 @@ __global__ void __launch_bounds__(kThreads) ep_sf_swizzle_kernel(SwizzleParams p
   __shared__ __align__(16) uint8_t s_rows[kTileRows][kSwizzleCols + 16];  // padded against bank conflicts
   __shared__ int s_tile[3];  // first row, valid rows, found
   const int tid = threadIdx.x;
-  if (tid == 0) {
-    // the expert whose atom rows contain this CTA's
-    s_tile[2] = 0;
+  if (tid == 0) s_tile[2] = 0;
+  __syncthreads();
+  // thread e checks whether expert e's atom rows contain this CTA's (at most one does)
+  for (int e = tid; e < p.experts; e += kThreads) {
+    const int lo = __ldg(p.m_indptr + e), hi = __ldg(p.m_indptr + e + 1);
+    const int first = lo / kTileRows + e;
+    const int tiles = (hi - lo + kTileRows - 1) / kTileRows;
     const int atom_row = blockIdx.x;
-    for (int e = 0; e < p.experts; ++e) {
-      const int lo = __ldg(p.m_indptr + e), hi = __ldg(p.m_indptr + e + 1);
-      const int first = lo / kTileRows + e;
-      const int tiles = (hi - lo + kTileRows - 1) / kTileRows;
-      if (atom_row >= first && atom_row < first + tiles) {
-        const int local = atom_row - first;
-        s_tile[0] = lo + local * kTileRows;
-        s_tile[1] = min(kTileRows, hi - lo - local * kTileRows);
-        s_tile[2] = 1;
-        break;
-      }
-      if (atom_row < first) break;
+    if (atom_row >= first && atom_row < first + tiles) {
+      const int local = atom_row - first;
+      s_tile[0] = lo + local * kTileRows;
+      s_tile[1] = min(kTileRows, hi - lo - local * kTileRows);
+      s_tile[2] = 1;
     }
   }
   __syncthreads();
