@@ -10,18 +10,19 @@
 //                ld.shared + tcgen05.st (one warp per TMEM lane quarter).  tcgen05.cp
 //                would do the same from the MMA thread, but measured here it holds the
 //                tensor pipe for ~90 cycles per 512-byte atom, serialised with the MMAs
-//   warps 8..15  epilogue in two groups of four: tcgen05.ld the accumulator, scale,
-//                (activate and requantize to NVFP4,) store; each warp owns one TMEM
-//                lane quarter; group g drains accumulator stage g
-// The accumulator is double-buffered in TMEM, so the epilogues of tiles i and i+1
-// overlap each other and the main loop of tile i+2.
+//   warps 8..15  epilogue in two groups of four: tcgen05.ld a 64-column slice of the
+//                accumulator, scale, (activate and requantize to NVFP4,) store; each warp
+//                owns one TMEM lane quarter.  BF16 blocks of 32 whole rows leave through a
+//                TMA store from swizzled staging
+// Tiles are 128 x 128 (two accumulators in TMEM, group g drains accumulator g) or 128 x 256
+// (two accumulators that overlap in TMEM, both groups on every tile): see gemm_kernel.
+// gemm_pair_kernel runs 256 x 256 tiles on pairs of CTAs with tcgen05.mma.cta_group::2.
 //
-// Work is cut into units of one 128-row tile times a run of 128-column tiles and dealt
-// round-robin to the CTAs.  When the contraction is short enough (K <= 2048) the A tile
-// and its scale factors stay resident in shared memory for the whole unit and only B
-// streams through the ring, which halves the L2 -> SM traffic; otherwise A and B stream
-// together and a unit is a single tile.  Every role derives the same unit list from
-// m_indptr in shared memory.
+// Work is cut into units of one row tile times a run of column tiles and dealt round-robin
+// to the CTAs.  With 128-column tiles and a short contraction (K <= 2048) the A tile and its
+// scale factors stay resident in shared memory for the whole unit and only B streams
+// through the ring; otherwise A and B stream together and a unit is a single tile.  Every
+// role derives the same unit list from m_indptr in shared memory.
 //
 // Rows of expert e are [m_indptr[e], m_indptr[e+1]).  A tile's A rows may run
 // into the next expert (or past the end, where TMA fills zeros); those rows are
