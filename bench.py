@@ -288,9 +288,16 @@ def run_ours(args):
     barrier()
 
     # ---- timed region: device-resident inputs; the working set (weights + workspace,
-    # > 700 MB per step) is far larger than the 126 MB L2, so no explicit flush is needed
+    # > 700 MB per step) is far larger than the 126 MB L2, so no explicit flush is needed.
+    # The step is a fixed sequence of launches (no host read, also across ranks), so it is
+    # captured once and replayed, as a serving loop would run it.
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for _ in range(3):
+        graph.replay()
     barrier()
-    times = _event_ms(step, args.steps)
+    times = _event_ms(graph.replay, args.steps)
     barrier()
     total_ms = torch.tensor([sum(times)], dtype=torch.float64, device=device)
     if world > 1:
@@ -339,7 +346,8 @@ def run_ours(args):
         "dtype": "nvfp4 (e2m1 x e4m3) with f32 accumulate", "data": "synthetic",
         "config": {"workload": WORKLOAD, "hidden": HIDDEN, "intermediate": INTER, "experts": EXPERTS,
                    "top_k": TOPK, "tokens_per_gpu": TOKENS, "activation": "swiglu",
-                   "parallelism": f"ep{world}", "l2": "working set per step exceeds L2; no flush"},
+                   "parallelism": f"ep{world}", "l2": "working set per step exceeds L2; no flush",
+                   "launch": "cuda graph replay of one step"},
         "clocks": sampler.summary(),
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "api": "HostPipeline.submit, depth 2, copies overlap compute"},

@@ -299,14 +299,16 @@ int lm_ep_quantize_send(const void* x, int64_t tokens, int features, int top_k, 
  * Cross-rank signal, one launch of one CTA per rank; the ranks must run on different GPUs.
  * With m_indptr: first stores this rank's per-expert row counts (m_indptr[e+1] - m_indptr[e])
  * as row `rank` of every rank's (world, experts) table.  Then every rank tells every rank that
- * it has reached `epoch` and waits until all of them have; stores this rank made to peer memory
- * in earlier launches of the stream are ordered before the signal.  `epoch` must grow by one
- * with every call, identically on all ranks.  The wait gives up after timeout_ms (0 = ten
- * seconds; counted in SM cycles at a nominal 2 GHz) and sets LM_STATUS_EP_TIMEOUT.
+ * it has made one more signal call and waits until all of them have; stores this rank made to
+ * peer memory in earlier launches of the stream are ordered before the signal.  Every rank
+ * must make the same sequence of calls.  The call count lives on the device (word `world` of
+ * the rank's own pad), so a captured CUDA graph of a step can be replayed.  The wait gives up
+ * after timeout_ms (0 = ten seconds; counted in SM cycles at a nominal 2 GHz) and sets
+ * LM_STATUS_EP_TIMEOUT.
  *   counts_all_base, signal_base  HOST arrays (world) of the addresses of every rank's count
- *                                 table and signal pad (world uint32 words, zero at start)
+ *                                 table and signal pad (world + 1 uint32 words, zero at start)
  */
-int lm_ep_signal(const int32_t* m_indptr, int experts, int world, int rank, uint32_t epoch,
+int lm_ep_signal(const int32_t* m_indptr, int experts, int world, int rank,
                  const uint64_t* counts_all_base, const uint64_t* signal_base, int timeout_ms,
                  lm_stream_t stream);
 

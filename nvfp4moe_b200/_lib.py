@@ -85,7 +85,7 @@ _SIGNATURES = {
     ),
     "lm_ep_signal": (
         c_i32,
-        [c_ptr, c_i32, c_i32, c_i32, ctypes.c_uint32, ctypes.POINTER(ctypes.c_uint64),
+        [c_ptr, c_i32, c_i32, c_i32, ctypes.POINTER(ctypes.c_uint64),
          ctypes.POINTER(ctypes.c_uint64), c_i32, c_ptr],
     ),
     "lm_ep_sf_swizzle": (c_i32, [c_ptr, c_i64, c_i32, c_ptr, c_i32, c_ptr, c_ptr]),

@@ -285,14 +285,24 @@ struct SignalParams {
   int experts;
   int world;
   int rank;
-  uint32_t epoch;
   long long wait_cycles;
   int32_t* counts_all[kMaxRanks];  // every rank's (world, experts) table
   uint32_t* signal[kMaxRanks];     // every rank's pad of `world` words
 };
 
 __global__ void __launch_bounds__(256) ep_signal_kernel(SignalParams p) {
+  __shared__ uint32_t s_epoch;
   const int tid = threadIdx.x;
+  // The epoch is this rank's count of signal calls, kept in word `world` of its own pad, so
+  // that a captured CUDA graph can be replayed: every rank makes the same calls in the same
+  // order, so the counts agree.
+  if (tid == 0) {
+    uint32_t* counter = p.signal[p.rank] + p.world;
+    s_epoch = *counter + 1;
+    *counter = s_epoch;
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
   if (p.m_indptr != nullptr) {
     for (int i = tid; i < p.experts; i += blockDim.x) {
       const int count = __ldg(p.m_indptr + i + 1) - __ldg(p.m_indptr + i);
@@ -303,13 +313,13 @@ __global__ void __launch_bounds__(256) ep_signal_kernel(SignalParams p) {
   __syncthreads();
   if (tid < p.world) {
     uint32_t* theirs = p.signal[tid] + p.rank;
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(p.epoch) : "memory");
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
     const uint32_t* mine = p.signal[p.rank] + tid;
     const long long start = clock64();
     while (true) {
       uint32_t seen;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-      if (static_cast<int32_t>(seen - p.epoch) >= 0) break;
+      if (static_cast<int32_t>(seen - epoch) >= 0) break;
       if (clock64() - start > p.wait_cycles) {
         atomicOr(&g_ep_status, static_cast<uint32_t>(LM_STATUS_EP_TIMEOUT));
         break;
@@ -424,7 +434,7 @@ extern "C" int lm_ep_sf_swizzle(const uint8_t* linear, int64_t max_rows, int fea
   return LM_OK;
 }
 
-extern "C" int lm_ep_signal(const int32_t* m_indptr, int experts, int world, int rank, uint32_t epoch,
+extern "C" int lm_ep_signal(const int32_t* m_indptr, int experts, int world, int rank,
                             const uint64_t* counts_all_base, const uint64_t* signal_base, int timeout_ms,
                             lm_stream_t stream) {
   using namespace lm;
@@ -437,7 +447,6 @@ extern "C" int lm_ep_signal(const int32_t* m_indptr, int experts, int world, int
   p.experts = experts;
   p.world = world;
   p.rank = rank;
-  p.epoch = epoch;
   LM_REQUIRE(timeout_ms >= 0 && timeout_ms <= 60000, "ep_signal: timeout of 0 (default) to 60000 ms");
   p.wait_cycles = (timeout_ms > 0 ? timeout_ms : 10000) * kCyclesPerMs;
   for (int g = 0; g < world; ++g) {

@@ -232,7 +232,6 @@ class ExpertParallelMoE:
             "row_ptrs": torch.zeros(m, dtype=torch.int64, device=dev),
             "valid": torch.ones(1, dtype=torch.int32, device=dev),
             "token": torch.zeros(1, dtype=torch.int32, device=dev),
-            "epoch": 0,
             "gemms": None,
         }
         self._peer = peer
@@ -330,11 +329,9 @@ class ExpertParallelMoE:
             return
         from . import _lib
 
-        peer["epoch"] += 1
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().lm_ep_signal(None if m_indptr is None else m_indptr.data_ptr(),
-                                               self.experts, self.world, self.rank,
-                                               peer["epoch"] & 0xFFFFFFFF, peer["cnt_base"],
+                                               self.experts, self.world, self.rank, peer["cnt_base"],
                                                peer["sig_base"], self.signal_timeout_ms,
                                                _lib.stream_handle()))
 

@@ -75,7 +75,19 @@ def _worker(rank: int, world: int, port: int, results):
             torch.cuda.synchronize()
             received = (int(sharded.last_recv_rows) if transport == "collective"
                         else int(sharded.local._m_indptr[-1]))
-            outcome[transport] = (bool(torch.equal(got, expected)), bool(torch.equal(got, again)),
+            replayed = True
+            if transport == "peer":
+                # the peer step is a fixed sequence of launches on every rank: capture it once,
+                # replay it (the signal epochs live on the device)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    captured = sharded(x, ids, w)
+                for _ in range(3):
+                    captured.zero_()
+                    graph.replay()
+                    torch.cuda.synchronize()
+                    replayed = replayed and bool(torch.equal(captured, expected))
+            outcome[transport] = (bool(torch.equal(got, expected)), bool(torch.equal(got, again)) and replayed,
                                   received, sharded.step_is_valid())
             dist.barrier()
         results[rank] = outcome

@@ -196,7 +196,7 @@ def test_signal_wait_runs_out_and_reports():
     m_indptr = torch.tensor([0, 3, 3, 4, 9, 9, 9, 10, 12], dtype=torch.int32, device=dev)
     sig = (ctypes.c_uint64 * 2)(pads[0].data_ptr(), pads[1].data_ptr())
     cnt = (ctypes.c_uint64 * 2)(tables[0].data_ptr(), tables[1].data_ptr())
-    _lib.check(_lib.lib().lm_ep_signal(m_indptr.data_ptr(), 8, 2, 0, 1, cnt, sig, 20, _lib.stream_handle()))
+    _lib.check(_lib.lib().lm_ep_signal(m_indptr.data_ptr(), 8, 2, 0, cnt, sig, 20, _lib.stream_handle()))
     assert _lib.device_status() == 16  # LM_STATUS_EP_TIMEOUT
     # its own part was done before the wait: counts in both tables, signals in both pads
     assert tables[0, 0].tolist() == [3, 0, 1, 5, 0, 0, 1, 2] and tables[1, 0].tolist() == tables[0, 0].tolist()
@@ -205,5 +205,6 @@ def test_signal_wait_runs_out_and_reports():
     assert _lib.device_status() == 0
     # once the peer's word is there the same call returns at once
     pads[0, 1] = 2
-    _lib.check(_lib.lib().lm_ep_signal(None, 8, 2, 0, 2, None, sig, 20, _lib.stream_handle()))
+    assert int(pads[0, 2]) == 1  # the rank's own call count
+    _lib.check(_lib.lib().lm_ep_signal(None, 8, 2, 0, None, sig, 20, _lib.stream_handle()))
     assert _lib.device_status() == 0
