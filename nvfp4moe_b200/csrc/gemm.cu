@@ -1034,16 +1034,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 // of 54 KB: less of the L2-to-SM traffic that bounds the single-CTA kernel.  The ring holds
 // five stages (four with BF16 output).
 //
-// Roles per CTA as in gemm_kernel; only the leader (cluster rank 0) issues MMAs.  Barriers:
-//   full[s]     local.  Leader: the A and B tiles of both CTAs (the peer's TMA loads signal
-//               the leader's barrier) and the leader's scale factors.  Peer: its scale factors.
-//   sf_full[s]  leader's; the eight scale-factor warps of both CTAs arrive.
+// Roles per CTA as in gemm_kernel, without scale-factor warps: the leader (cluster rank 0)
+// issues the MMAs of the pair and, in front of each, the tcgen05.cp copies that bring that
+// chunk's scale-factor atoms from each CTA's shared memory into its own TMEM.  Barriers:
+//   full[s]     leader's: the A, B and scale-factor loads of both CTAs complete on it (the
+//               peer's TMA loads name the leader's barrier), so scale factors come through
+//               tensor maps here as well (eight-byte elements, boxes of 2 KB per atom row).
 //   empty[s], acc_full[a]  local in both CTAs, signalled by multicast tcgen05.commit.
 //   acc_empty[a], shared_cols_free  leader's; the sixteen epilogue warps of both CTAs arrive.
 constexpr int kPairStageBytes = 2 * kTileBytes + 3 * kSfBytes;  // B half, SFB x2, A, SFA = 38912
 // TMEM of a pair CTA: accumulator 0 at [0, 256), accumulator 1 at [64, 320), four scale-factor
-// slots of 48 columns from 320.  Signals between the CTAs take long enough that two slots
-// (the single-CTA layout) leave the MMAs waiting for scale factors most of the time.
+// slots of 48 columns from 320, used in turn by the K stages.
 constexpr uint32_t kPairAcc1Col = 64;
 constexpr uint32_t kPairSfCol = 320;
 constexpr int kPairSfSlots = 4;
@@ -1099,6 +1100,23 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
       : "memory");
 }
 
+// Shared-memory descriptor of one 512-byte scale-factor atom: 32 rows of 16 bytes, no swizzle,
+// eight-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t desc_sf_atom(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);  // start address
+  d |= static_cast<uint64_t>(128 >> 4) << 32;               // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                      // descriptor version (sm_100)
+  return d;
+}
+
+// One scale-factor atom from the shared memory of each CTA of the pair into four TMEM columns
+// of that CTA, the 32 rows repeated in all four lane quarters (the layout the block-scaled MMA
+// reads).  Runs in issue order with the MMAs of the same thread.
+__device__ __forceinline__ void tc_copy_sf_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
 __host__ __device__ constexpr uint32_t make_idesc_pair(int n) {
   return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (0u << 23) |
          (static_cast<uint32_t>(256 >> 4) << 24);
@@ -1128,7 +1146,8 @@ template <int kOut, int kAct>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64,
                  const __grid_constant__ CUtensorMap tmap_a32, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_sfa,
+                 const __grid_constant__ CUtensorMap tmap_sfb, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -1154,7 +1173,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     for (int s = 0; s < kMaxRing; ++s) {
       mbar_init(smem_u32(&misc->full[s]), 1);
       mbar_init(smem_u32(&misc->empty[s]), 1);
-      mbar_init(smem_u32(&misc->sf_full[s]), 8);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&misc->acc_full[s]), 1);
@@ -1234,14 +1252,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t peer_a_bytes = 0;
       if (leader) peer_a_bytes = a_box_rows(pair_row_tile(misc, p, peer_cursor, u.mt, 1).valid) * kStageKBytes;
       const CUtensorMap* a_map = a_rows == 32 ? &tmap_a32 : (a_rows == 64 ? &tmap_a64 : &tmap_a);
-      const uint8_t* sfa_src = p.sfa + static_cast<int64_t>(t.sf_row) * p.atom_cols * 512;
       for (int nt = u.n_begin; nt < u.n_end && ok; ++nt) {
         const int b_row = t.expert * p.n + nt * 2 * kTileN + rank * kTileN;
-        const uint8_t* sfb_src =
-            p.sfb + static_cast<int64_t>(t.expert * p.sfb_atom_rows + nt * 2) * p.atom_cols * 512;
+        const int sfb_row = t.expert * p.sfb_atom_rows + nt * 2;
         for (int ks = 0; ks < p.k_stages; ++ks) {
-          const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
-          const uint32_t sf_bytes = chunks * 512;
           LM_PROF_BEGIN();
           ok = mbar_wait(smem_u32(&misc->empty[stage]), phase ^ 1u, abort_flag, kStatusProducerTimeout);
           LM_PROF_END(prof_acc0);
@@ -1249,22 +1263,26 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (elect_one()) {
             const uint32_t bar = smem_u32(&misc->full[stage]);
             const uint32_t dst = smem_base + stage * kPairStageBytes;
-            const uint32_t sf_tx = 3 * sf_bytes;  // A's and both column blocks of B's
+            // every byte of both CTAs is counted on the leader's barrier; a scale-factor box is
+            // always whole (columns past K read as zero)
             if (leader) {
-              mbar_expect_tx(bar, sf_tx + 2 * kTileBytes + a_rows * kStageKBytes + peer_a_bytes);
+              mbar_expect_tx(bar, 2 * (kTileBytes + 2 * kSfBytes) + a_rows * kStageKBytes + (a_rows ? kSfBytes : 0) +
+                                      peer_a_bytes + (peer_a_bytes ? kSfBytes : 0));
               tma_load_2d(dst + kOffB, &tmap_b, ks * kStageKBytes, b_row, bar);
-              if (a_rows) tma_load_2d(dst + kOffA, a_map, ks * kStageKBytes, t.row0, bar);
+              tma_load_2d(dst + kOffSfb, &tmap_sfb, ks * (kSfBytes / 8), sfb_row, bar);
+              if (a_rows) {
+                tma_load_2d(dst + kOffA, a_map, ks * kStageKBytes, t.row0, bar);
+                tma_load_2d(dst + kOffSfa, &tmap_sfa, ks * (kSfBytes / 8), t.sf_row, bar);
+              }
             } else {
-              mbar_expect_tx(bar, sf_tx);
               const uint32_t leader_bar = map_to_cta(bar, 0);
               tma_load_2d_pair(dst + kOffB, &tmap_b, ks * kStageKBytes, b_row, leader_bar);
-              if (a_rows) tma_load_2d_pair(dst + kOffA, a_map, ks * kStageKBytes, t.row0, leader_bar);
+              tma_load_2d_pair(dst + kOffSfb, &tmap_sfb, ks * (kSfBytes / 8), sfb_row, leader_bar);
+              if (a_rows) {  // a half tile past the expert's rows loads neither A nor its scale factors
+                tma_load_2d_pair(dst + kOffA, a_map, ks * kStageKBytes, t.row0, leader_bar);
+                tma_load_2d_pair(dst + kOffSfa, &tmap_sfa, ks * (kSfBytes / 8), t.sf_row, leader_bar);
+              }
             }
-            for (int j = 0; j < 2; ++j)
-              bulk_load(dst + kOffSfb + j * kSfBytes,
-                        sfb_src + (static_cast<int64_t>(j) * p.atom_cols + ks * kChunksPerStage) * 512, sf_bytes,
-                        bar);
-            bulk_load(dst + kOffSfa, sfa_src + static_cast<int64_t>(ks) * kSfBytes, sf_bytes, bar);
           }
           __syncwarp();
           if (++stage == p.ring_stages) { stage = 0; phase ^= 1u; }
@@ -1282,8 +1300,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int it = 0;
       bool ok = true;
       LM_PROF_DECL;
-      long long prof_sf = 0;
-      (void)prof_sf;
       const long long prof_start = clock64();
       (void)prof_start;
       for (int unit = first_unit; unit < total_units && ok; unit += unit_stride) {
@@ -1302,9 +1318,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             LM_PROF_BEGIN();
             ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusMmaTimeout);
             LM_PROF_END(prof_acc0);
-            LM_PROF_BEGIN();
-            if (ok) ok = mbar_wait(smem_u32(&misc->sf_full[stage]), phase, abort_flag, kStatusMmaTimeout);
-            LM_PROF_END(prof_sf);
             if (!ok) break;
             tc_fence_after();
             LM_PROF_BEGIN();
@@ -1315,16 +1328,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             sf_slot = (sf_slot + 1) % kPairSfSlots;
             const uint64_t a_desc = desc_sw128(stage_smem + kOffA);
             const uint64_t b_desc = desc_sw128(stage_smem + kOffB);
+            const uint64_t sfa_desc = desc_sf_atom(stage_smem + kOffSfa);
+            const uint64_t sfb_desc = desc_sf_atom(stage_smem + kOffSfb);
             if (elect_one()) {
+              // the atoms of a 64-element chunk go to TMEM right before its MMA; copies and MMAs
+              // of one thread run in issue order, so a slot is never overwritten while in use
+              auto chunk = [&](int c) {
+                tc_copy_sf_pair(sfa_t + c * 4, sfa_desc + c * (512 >> 4));
+                tc_copy_sf_pair(sfb_t + c * 8, sfb_desc + c * (512 >> 4));
+                tc_copy_sf_pair(sfb_t + c * 8 + 4, sfb_desc + (kSfBytes >> 4) + c * (512 >> 4));
+                tc_mma_nvf4_pair(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 8,
+                                 (ks > 0 || c > 0) ? 1u : 0u);
+              };
               if (chunks == kChunksPerStage) {
 #pragma unroll
-                for (int c = 0; c < kChunksPerStage; ++c)
-                  tc_mma_nvf4_pair(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 8,
-                                   (ks > 0 || c > 0) ? 1u : 0u);
+                for (int c = 0; c < kChunksPerStage; ++c) chunk(c);
               } else {
-                for (int c = 0; c < chunks; ++c)
-                  tc_mma_nvf4_pair(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 8,
-                                   (ks > 0 || c > 0) ? 1u : 0u);
+                for (int c = 0; c < chunks; ++c) chunk(c);
               }
               tc_commit_pair(smem_u32(&misc->empty[stage]));
             }
@@ -1341,84 +1361,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         LM_PROF_STORE(1, prof_acc0);
         LM_PROF_STORE(2, prof_acc1);
         LM_PROF_STORE(7, prof_acc2);
-        LM_PROF_STORE(8, prof_sf);
         LM_PROF_STORE(5, clock64() - prof_start);
         LM_PROF_STORE(6, it);
       }
-    }
-  } else if (warp >= kFirstSfWarp && warp < kFirstSfWarp + 4) {
-    // ===================================================== scale factors -> TMEM (both CTAs)
-    const int quarter = warp & 3;
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    int stage = 0;
-    uint32_t phase = 0;
-    uint32_t sf_slot = 0;
-    int prev_stage[kPairSfSlots];    // ring stage (and its phase) of the last four iterations
-    uint32_t prev_phase[kPairSfSlots];
-    for (int i = 0; i < kPairSfSlots; ++i) {
-      prev_stage[i] = -1;
-      prev_phase[i] = 0;
-    }
-    bool ok = true;
-    LM_PROF_DECL;
-    for (int unit = first_unit; unit < total_units && ok; unit += unit_stride) {
-      const Unit u = decode_unit(p, unit);
-      for (int nt = u.n_begin; nt < u.n_end && ok; ++nt) {
-        for (int ks = 0; ks < p.k_stages; ++ks) {
-          LM_PROF_BEGIN();
-          ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusSfTimeout);
-          LM_PROF_END(prof_acc0);
-          LM_PROF_BEGIN();
-          // the TMEM slot was last read by the MMAs of four stages ago
-          if (ok && prev_stage[0] >= 0)
-            ok = mbar_wait(smem_u32(&misc->empty[prev_stage[0]]), prev_phase[0], abort_flag, kStatusSfTimeout);
-#pragma unroll
-          for (int i = 0; i + 1 < kPairSfSlots; ++i) {
-            prev_stage[i] = prev_stage[i + 1];
-            prev_phase[i] = prev_phase[i + 1];
-          }
-          prev_stage[kPairSfSlots - 1] = stage;
-          prev_phase[kPairSfSlots - 1] = phase;
-          if (!ok) break;
-          LM_PROF_END(prof_acc1);
-          LM_PROF_BEGIN();
-          const uint32_t stage_smem = smem_base + stage * kPairStageBytes;
-          const uint32_t sfa_src = stage_smem + kOffSfa + lane * 16;
-          const uint32_t sfb_src = stage_smem + kOffSfb + lane * 16;
-          uint32_t w[48];
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(w[4 * c]), "=r"(w[4 * c + 1]), "=r"(w[4 * c + 2]), "=r"(w[4 * c + 3])
-                         : "r"(sfa_src + c * 512));
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              const int o = 16 + 4 * (c * 2 + j);
-              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(w[o]), "=r"(w[o + 1]), "=r"(w[o + 2]), "=r"(w[o + 3])
-                           : "r"(sfb_src + j * kSfBytes + c * 512));
-            }
-          }
-          const uint32_t dst = lane_base + kPairSfCol + sf_slot * kWideSfSlotCols;
-          tc_store32(dst, w);
-          tc_store16(dst + 32, w + 32);
-          sf_slot = (sf_slot + 1) % kPairSfSlots;
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-          tc_fence_before();
-          __syncwarp();
-          LM_PROF_END(prof_acc2);
-          if (lane == 0) {
-            const uint32_t bar = smem_u32(&misc->sf_full[stage]);
-            signal_barrier(leader ? bar : map_to_cta(bar, 0), !leader);
-          }
-          if (++stage == p.ring_stages) { stage = 0; phase ^= 1u; }
-        }
-      }
-    }
-    if (warp == kFirstSfWarp && lane == 0 && leader) {
-      LM_PROF_STORE(9, prof_acc0);
-      LM_PROF_STORE(10, prof_acc1);
-      LM_PROF_STORE(11, prof_acc2);
     }
   } else if (warp >= kFirstEpilogueWarp) {
     // ===================================================== epilogue (both CTAs, own 128 rows)
@@ -1486,6 +1431,8 @@ struct PlanData {
   alignas(64) CUtensorMap map_a32;
   alignas(64) CUtensorMap map_b;
   alignas(64) CUtensorMap map_out;
+  alignas(64) CUtensorMap map_sfa;  // CTA pairs: scale factors as 2 KB boxes per atom row
+  alignas(64) CUtensorMap map_sfb;
 };
 static_assert(sizeof(PlanData) <= sizeof(lm_gemm_plan), "plan storage too small");
 constexpr uint32_t kPlanMagic = 0x4C4D4750u;
@@ -1538,6 +1485,22 @@ int encode_out_bf16(CUtensorMap* map, void* base, uint64_t cols, uint64_t rows) 
   return LM_OK;
 }
 
+// Scale-factor atoms as a matrix of eight-byte words: one row per 128-row atom row
+// (`atom_cols` atoms of 512 bytes), boxes of one K stage (2 KB) by `box_rows`.
+int encode_sf(CUtensorMap* map, const void* base, uint64_t atom_cols, uint64_t atom_rows, uint32_t box_rows) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return set_error(LM_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t dims[2] = {atom_cols * 64, atom_rows};
+  cuuint64_t strides[1] = {atom_cols * 512};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kSfBytes / 8), box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_INT64, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(LM_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+  return LM_OK;
+}
+
 template <int kOut, int kAct, int kNB>
 int launch_kernel(const PlanData& pd, cudaStream_t stream) {
   auto kernel = gemm_kernel<kOut, kAct, kNB>;
@@ -1573,7 +1536,7 @@ int launch_pair(const PlanData& pd, cudaStream_t stream) {
   config.attrs = attr;
   config.numAttrs = 1;
   LM_CUDA(cudaLaunchKernelEx(&config, kernel, pd.map_a, pd.map_a64, pd.map_a32, pd.map_b, pd.map_out,
-                             pd.params));
+                             pd.map_sfa, pd.map_sfb, pd.params));
   return LM_OK;
 }
 
@@ -1721,6 +1684,17 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   p.tma_store = (a->out_kind == LM_OUT_BF16 && a->out_row_ptrs == nullptr && a->n >= 64) ? 1 : 0;
   if (p.tma_store) {
     rc = encode_out_bf16(&pd.map_out, a->out, static_cast<uint64_t>(a->n), static_cast<uint64_t>(a->rows));
+    if (rc != LM_OK) return rc;
+  }
+  if (pd.pair) {
+    // A's atom rows: every expert starts a new one (rows / 128 + experts bounds them)
+    const uint64_t a_atom_rows =
+        a->dense ? static_cast<uint64_t>((a->rows + kTileM - 1) / kTileM)
+                 : static_cast<uint64_t>(a->rows / kTileM + a->experts);
+    rc = encode_sf(&pd.map_sfa, a->sfa, static_cast<uint64_t>(p.atom_cols), a_atom_rows, 1);
+    if (rc != LM_OK) return rc;
+    rc = encode_sf(&pd.map_sfb, a->sfb, static_cast<uint64_t>(p.atom_cols),
+                   static_cast<uint64_t>(a->experts) * p.sfb_atom_rows, 2);
     if (rc != LM_OK) return rc;
   }
   memcpy(plan, &pd, sizeof(pd));

@@ -60,21 +60,41 @@ def _tile_n(n: int, k: int, decode: bool) -> int:
     return 128 if decode or n % 256 else 256
 
 
+def _expected_padded_rows(mean_rows: float, tile: int) -> float:
+    """Rows an expert occupies once padded to whole ``tile``-row tiles, averaged over a
+    per-expert row count drawn from N(mean, mean) (uniform routing)."""
+    sigma = max(math.sqrt(mean_rows), 1.0)
+
+    def cdf(v: float) -> float:
+        return 0.5 * (1.0 + math.erf((v - mean_rows) / (sigma * math.sqrt(2.0))))
+
+    first = max(0, int((mean_rows - 5.0 * sigma) // tile))
+    last = int((mean_rows + 5.0 * sigma) // tile) + 1
+    total = 0.0
+    for t in range(first, last + 1):
+        total += (cdf((t + 1) * tile) - cdf(t * tile)) * (t + 1) * tile
+    return total
+
+
 def _row_tile(policy_tile_m: int, rows: int, experts: int, n: int, k: int, decode: bool, nvfp4_out: bool) -> int:
     """Row-tile height handed to a grouped GEMM: 256 runs 256 x 256 tiles on CTA pairs.
 
-    A pair issues half as many MMAs per FLOP and pulls 30 % less data into each SM, but pads
-    every expert to 256 rows and hands its accumulators back later; measured, it wins 5-6 % on
-    the first projection of shards with thousands of rows per expert and K >= 4096 and loses
-    elsewhere, so that is where it is used.  ``NVFP4MOE_TILE_M`` (128 or 256) overrides the
-    choice for tuning.
+    A pair pulls 30 % less data into each SM and issues half as many MMAs per FLOP: measured
+    10-20 % faster per padded row than 128 x 256 tiles, on both projections.  It pads every
+    expert to 256 rows, though, so it is chosen when that padding costs less than the pair
+    wins: the expected padded rows of both tile heights are compared for the plan's mean
+    rows per expert (with about 256 rows per expert the taller tile pads 20 % more and
+    loses; with 192, or with 512 and more, it wins).  The reference's own table
+    (``_tile_m``) is not consulted.  ``NVFP4MOE_TILE_M`` (128 or 256) overrides the choice
+    for tuning.
     """
     forced = os.environ.get("NVFP4MOE_TILE_M")
     if forced:
         return int(forced)
-    if decode or n % 256:
+    if decode or n % 256 or rows < 128 * experts:
         return 128
-    return 256 if (policy_tile_m == 256 and nvfp4_out and k >= 4096 and rows >= 1024 * experts) else 128
+    mean_rows = rows / experts
+    return 256 if _expected_padded_rows(mean_rows, 256) <= 1.12 * _expected_padded_rows(mean_rows, 128) else 128
 
 
 def _tile_m(token_expert_assignments: int, experts: int, hidden: int, intermediate: int):
