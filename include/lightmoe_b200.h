@@ -65,7 +65,7 @@ int lm_sm_count(int* out);
 
 /*
  * Device-side status word.  A kernel whose bounded wait ran out sets a bit here and returns
- * instead of hanging: bits 0-3 the GEMM's producer / MMA / epilogue / scale-factor roles,
+ * instead of hanging: bits 0-2 the GEMM's producer / MMA / epilogue roles (bit 3 unused),
  * LM_STATUS_EP_TIMEOUT a cross-rank signal that never arrived.  Synchronises the stream.
  * *out == 0 means no kernel has reported a problem since the last lm_device_status_clear().
  */

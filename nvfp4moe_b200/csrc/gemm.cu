@@ -2,15 +2,15 @@
 //
 //   out[rows_e, :] = alpha_e * (A_e . SFA_e) (B_e . SFB_e)^T      FP32 accumulate
 //
-// Warp-specialised CTA of 512 threads, one CTA per SM:
+// Warp-specialised CTA of 384 threads, one CTA per SM:
 //   warp 0       TMA producer: A and B tiles (128-byte swizzle) with
 //                cp.async.bulk.tensor, scale-factor atoms with cp.async.bulk
-//   warp 1       allocates TMEM and issues tcgen05.mma kind::mxf4nvf4 block-scaled MMAs
-//   warps 4..7   move the scale factors of each stage from shared memory to TMEM with
-//                ld.shared + tcgen05.st (one warp per TMEM lane quarter).  tcgen05.cp
-//                would do the same from the MMA thread, but measured here it holds the
-//                tensor pipe for ~90 cycles per 512-byte atom, serialised with the MMAs
-//   warps 8..15  epilogue in two groups of four: tcgen05.ld a 64-column slice of the
+//   warp 1       allocates TMEM; one elected thread issues, per 64-element chunk, the
+//                tcgen05.cp copies that bring the chunk's scale-factor atoms from shared
+//                memory to TMEM and then the tcgen05.mma kind::mxf4nvf4 block-scaled MMA
+//                (copies and MMAs of one thread run in issue order)
+//   warp 2       tile prefix table at start-up
+//   warps 4..11  epilogue in two groups of four: tcgen05.ld a 64-column slice of the
 //                accumulator, scale, (activate and requantize to NVFP4,) store; each warp
 //                owns one TMEM lane quarter.  BF16 blocks of 32 whole rows leave through a
 //                TMA store from swizzled staging
@@ -43,8 +43,7 @@ constexpr int kTileN = 128;
 constexpr int kStageKBytes = 128;  // 256 FP4 values per row and stage: one swizzle span
 constexpr int kChunksPerStage = 4; // 64-element MMAs (= scale-factor atoms) per stage
 constexpr int kEpilogueWarps = 8;
-constexpr int kFirstSfWarp = 4;        // warps 4..7 write scale factors into TMEM
-constexpr int kFirstEpilogueWarp = 8;  // warps 8..15: two epilogue groups of four
+constexpr int kFirstEpilogueWarp = 4;  // warps 4..11: two epilogue groups of four (warp & 3 = TMEM lane quarter)
 constexpr int kThreads = 32 * (kFirstEpilogueWarp + kEpilogueWarps);
 constexpr int kMaxExperts = 256;
 constexpr uint32_t kTmemCols = 512;
@@ -101,8 +100,7 @@ __device__ unsigned long long g_prof[16];
 enum : uint32_t {
   kStatusProducerTimeout = 1u,
   kStatusMmaTimeout = 2u,
-  kStatusEpilogueTimeout = 4u,
-  kStatusSfTimeout = 8u,
+  kStatusEpilogueTimeout = 4u,  // (8 was the scale-factor warps' bit; 16 belongs to the cross-rank signal)
 };
 
 struct GemmParams {
@@ -266,29 +264,6 @@ __device__ __forceinline__ void tc_load32(uint32_t taddr, uint32_t* r) {
       : "memory");
 }
 
-__device__ __forceinline__ void tc_store32(uint32_t taddr, const uint32_t* r) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
-      "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
-      "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-
-__device__ __forceinline__ void tc_store16(uint32_t taddr, const uint32_t* r) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
-
-// Waits for the TMEM loads in flight.  The destination registers are operands, so no use
-// of them can be scheduled ahead of the wait.
 __device__ __forceinline__ void tc_wait_ld_regs(uint32_t* r) {
   asm volatile("tcgen05.wait::ld.sync.aligned;"
                : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
@@ -322,7 +297,6 @@ __host__ __device__ constexpr uint32_t make_idesc(int n) {
 struct Misc {  // lives after the operand slots and the store staging
   uint64_t full[kMaxRing];         // ring stage filled by TMA
   uint64_t empty[kMaxRing];        // ring stage drained by the MMAs
-  uint64_t sf_full[kMaxRing];      // scale factors of the ring stage are in TMEM
   uint64_t a_full[kMaxResident];   // resident A stage filled
   uint64_t a_empty[kMaxResident];  // resident A stage no longer read
   uint64_t acc_full[2];
@@ -431,7 +405,6 @@ struct DrainContext {
   uint32_t bar_acc_empty;    // signalled when the whole accumulator is in registers
   bool remote;               // the two barriers are cluster addresses (the pair leader's)
   uint32_t acc1_col;         // 256-column tiles: first TMEM column of accumulator 1
-  bool wide_overlap;         // 256-column tiles: the accumulators share three 64-column slices
   int group;                 // epilogue group of the warp (0 or 1)
   int quarter;               // TMEM lane quarter of the warp
   int lane;
@@ -463,9 +436,6 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
   const bool row_ok = quarter * 32 + lane < t.valid;
   const int64_t out_row = static_cast<int64_t>(t.row0) + quarter * 32 + lane;
   const uint32_t taddr = lane_base + acc * (kNB == 1 ? kTileN : c.acc1_col);
-  // With three shared slices (accumulator 0: slices 1-3, accumulator 1: slices 0-2) one group
-  // holds two of them and can only let go after its second load.
-  const bool late_signal = kNB == 2 && c.wide_overlap && ((acc == 0) == (group == 1));
 
   // Software pipeline over the four 32-column chunks of the warp's two slices: while
   // a chunk is converted, the load of the chunk after next is in flight (a TMEM load
@@ -485,7 +455,7 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
   // slice 0 is in registers: the columns shared with the other accumulator are free
   tc_fence_before();
   __syncwarp();
-  if (kNB == 2 && !late_signal && lane == 0) signal_barrier(c.bar_shared_cols, c.remote);
+  if (kNB == 2 && lane == 0) signal_barrier(c.bar_shared_cols, c.remote);
 
   // ---- per-slice state and the two halves of the work
   constexpr bool kGated = kAct != LM_ACT_RELU2;
@@ -627,10 +597,7 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
   // the whole accumulator has been read
   tc_fence_before();
   __syncwarp();
-  if (lane == 0) {
-    if (late_signal) signal_barrier(c.bar_shared_cols, c.remote);
-    signal_barrier(c.bar_acc_empty, c.remote);
-  }
+  if (lane == 0) signal_barrier(c.bar_acc_empty, c.remote);
   convert(va, 0, col_b);
   convert(vb, 1, col_b);
   finish(col_b);
@@ -646,6 +613,23 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
 //    both epilogue groups work on every tile, read the 64-column slices that touch the
 //    overlap first and signal `shared_cols_free`; the MMAs of the next tile start then, while
 //    the rest of the tile is still being converted and stored.
+// Shared-memory descriptor of one 512-byte scale-factor atom: 32 rows of 16 bytes, no swizzle,
+// eight-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t desc_sf_atom(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);  // start address
+  d |= static_cast<uint64_t>(128 >> 4) << 32;               // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                      // descriptor version (sm_100)
+  return d;
+}
+
+// One scale-factor atom from shared memory into four TMEM columns, the 32 rows repeated in all
+// four lane quarters (the layout the block-scaled MMA reads).  Runs in issue order with the
+// MMAs of the same thread.
+__device__ __forceinline__ void tc_copy_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
 template <int kOut, int kAct, int kNB>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64,
@@ -676,7 +660,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     for (int s = 0; s < kMaxRing; ++s) {
       mbar_init(smem_u32(&misc->full[s]), 1);
       mbar_init(smem_u32(&misc->empty[s]), 1);
-      mbar_init(smem_u32(&misc->sf_full[s]), 4);
     }
     for (int s = 0; s < kMaxResident; ++s) {
       mbar_init(smem_u32(&misc->a_full[s]), 1);
@@ -843,8 +826,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusMmaTimeout);
           if (ok && resident && nt == u.n_begin)
             ok = mbar_wait(smem_u32(&misc->a_full[ks]), a_phase, abort_flag, kStatusMmaTimeout);
-          // the scale factors of this stage sit in the TMEM slot of the same index
-          if (ok) ok = mbar_wait(smem_u32(&misc->sf_full[stage]), phase, abort_flag, kStatusMmaTimeout);
           LM_PROF_END(prof_acc0);
           if (!ok) break;
           tc_fence_after();
@@ -858,20 +839,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           sf_slot ^= 1u;
           const uint64_t a_desc = desc_sw128(a_smem);
           const uint64_t b_desc = desc_sw128(b_smem);
+          const uint64_t sfa_desc = desc_sf_atom(a_smem + kTileBytes);
+          const uint64_t sfb_desc = desc_sf_atom(b_smem + kSfbOffset);
           if (elect_one()) {
+            // The scale-factor atoms of a 64-element chunk go from shared memory to TMEM right
+            // before its MMA; copies and MMAs of one thread run in issue order, so a TMEM slot
+            // is never overwritten while an earlier MMA still reads it.
+            // 64 FP4 values = 32 bytes along K: +2 in 16-byte descriptor units
+            auto chunk = [&](int c) {
+              tc_copy_sf(sfa_t + c * 4, sfa_desc + c * (512 >> 4));
+#pragma unroll
+              for (int j = 0; j < kNB; ++j)
+                tc_copy_sf(sfb_t + (c * kNB + j) * 4, sfb_desc + j * (kSfBytes >> 4) + c * (512 >> 4));
+              tc_mma_nvf4(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 4 * kNB,
+                          (ks > 0 || c > 0) ? 1u : 0u);
+            };
 #ifdef LM_GEMM_PROFILE
             if (!(p.debug_flags & 2))
 #endif
-            // 64 FP4 values = 32 bytes along K: +2 in 16-byte descriptor units
             if (chunks == kChunksPerStage) {
 #pragma unroll
-              for (int c = 0; c < kChunksPerStage; ++c)
-                tc_mma_nvf4(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 4 * kNB,
-                            (ks > 0 || c > 0) ? 1u : 0u);
+              for (int c = 0; c < kChunksPerStage; ++c) chunk(c);
             } else {
-              for (int c = 0; c < chunks; ++c)
-                tc_mma_nvf4(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 4 * kNB,
-                            (ks > 0 || c > 0) ? 1u : 0u);
+              for (int c = 0; c < chunks; ++c) chunk(c);
             }
             tc_commit(smem_u32(&misc->empty[stage]));
             if (resident && nt == u.n_end - 1) tc_commit(smem_u32(&misc->a_empty[ks]));
@@ -893,73 +883,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       LM_PROF_STORE(5, clock64() - prof_start);
       LM_PROF_STORE(6, it);
     }
-  } else if (warp >= kFirstSfWarp && warp < kFirstSfWarp + 4) {
-    // ===================================================== scale factors -> TMEM
-    // Lane l of every quarter needs the same words per stage: for each of the four 64-element
-    // chunks, the 16 bytes at (chunk * 512 + l * 16) of the A atoms (factors of rows l, l+32,
-    // l+64, l+96) and the same for the B atoms of every 128-column block.
-    const int quarter = warp & 3;
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    int stage = 0;
-    uint32_t phase = 0;
-    uint32_t a_phase = 0;
-    // 256-column tiles keep two TMEM slots: the slot of stage iteration j was last read by
-    // the MMAs of iteration j - 2, whose completion the ring's `empty` barrier reports.
-    uint32_t sf_slot = 0;
-    int prev_stage[2] = {-1, -1};
-    uint32_t prev_phase[2] = {0, 0};
-    bool ok = true;
-    for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
-      const Unit u = decode_unit(p, unit);
-      for (int nt = u.n_begin; nt < u.n_end && ok; ++nt) {
-        for (int ks = 0; ks < p.k_stages; ++ks) {
-          ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusSfTimeout);
-          if (ok && resident && nt == u.n_begin)
-            ok = mbar_wait(smem_u32(&misc->a_full[ks]), a_phase, abort_flag, kStatusSfTimeout);
-          if (kNB == 2) {
-            if (ok && prev_stage[0] >= 0)
-              ok = mbar_wait(smem_u32(&misc->empty[prev_stage[0]]), prev_phase[0], abort_flag, kStatusSfTimeout);
-            prev_stage[0] = prev_stage[1];
-            prev_phase[0] = prev_phase[1];
-            prev_stage[1] = stage;
-            prev_phase[1] = phase;
-          }
-          if (!ok) break;
-          const uint32_t b_smem = ring_base + stage * ring_stride;
-          const uint32_t a_smem = resident ? smem_base + ks * kSlotBytes : b_smem + kAOffset;
-          const uint32_t sfa_src = a_smem + kTileBytes + lane * 16;
-          const uint32_t sfb_src = b_smem + kSfbOffset + lane * 16;
-          uint32_t w[16 + 16 * kNB];
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(w[4 * c]), "=r"(w[4 * c + 1]), "=r"(w[4 * c + 2]), "=r"(w[4 * c + 3])
-                         : "r"(sfa_src + c * 512));
-#pragma unroll
-            for (int j = 0; j < kNB; ++j) {
-              const int o = 16 + 4 * (c * kNB + j);
-              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(w[o]), "=r"(w[o + 1]), "=r"(w[o + 2]), "=r"(w[o + 3])
-                           : "r"(sfb_src + j * kSfBytes + c * 512));
-            }
-          }
-          if (kNB == 1) {
-            tc_store32(lane_base + kSfCol + stage * 32, w);
-          } else {
-            const uint32_t dst = lane_base + kWideSfCol + sf_slot * kWideSfSlotCols;
-            tc_store32(dst, w);
-            tc_store16(dst + 32, w + 32);
-            sf_slot ^= 1u;
-          }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&misc->sf_full[stage]));
-          if (++stage == p.ring_stages) { stage = 0; phase ^= 1u; }
-        }
-      }
-      a_phase ^= 1u;
-    }
   } else if (warp >= kFirstEpilogueWarp) {
     // ===================================================== epilogue
     // Two groups of four warps.  The unit of work is a 64-column slice of an accumulator:
@@ -977,7 +900,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     ctx.bar_shared_cols = smem_u32(&misc->shared_cols_free);
     ctx.remote = false;
     ctx.acc1_col = kWideAcc1Col;
-    ctx.wide_overlap = false;
     ctx.inv_h = kOut == LM_OUT_NVFP4 ? __ldg(p.out_scale + 1) : 0.0f;
     TileWalker walker;
     int it = 0;
@@ -1043,11 +965,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 //   empty[s], acc_full[a]  local in both CTAs, signalled by multicast tcgen05.commit.
 //   acc_empty[a], shared_cols_free  leader's; the sixteen epilogue warps of both CTAs arrive.
 constexpr int kPairStageBytes = 2 * kTileBytes + 3 * kSfBytes;  // B half, SFB x2, A, SFA = 38912
-// TMEM of a pair CTA: accumulator 0 at [0, 256), accumulator 1 at [64, 320), four scale-factor
-// slots of 48 columns from 320, used in turn by the K stages.
-constexpr uint32_t kPairAcc1Col = 64;
-constexpr uint32_t kPairSfCol = 320;
-constexpr int kPairSfSlots = 4;
+// TMEM of a pair CTA: as for 128 x 256 tiles (accumulators at 0 and kWideAcc1Col, two
+// scale-factor slots from kWideSfCol).
 static_assert(kPairStageBytes % 1024 == 0, "pair ring stages must keep 1024-byte alignment");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -1100,19 +1019,7 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
       : "memory");
 }
 
-// Shared-memory descriptor of one 512-byte scale-factor atom: 32 rows of 16 bytes, no swizzle,
-// eight-row groups 128 bytes apart.
-__device__ __forceinline__ uint64_t desc_sf_atom(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);  // start address
-  d |= static_cast<uint64_t>(128 >> 4) << 32;               // stride byte offset
-  d |= static_cast<uint64_t>(1) << 46;                      // descriptor version (sm_100)
-  return d;
-}
-
-// One scale-factor atom from the shared memory of each CTA of the pair into four TMEM columns
-// of that CTA, the 32 rows repeated in all four lane quarters (the layout the block-scaled MMA
-// reads).  Runs in issue order with the MMAs of the same thread.
+// The same copy in both CTAs of a pair: each from its own shared memory into its own TMEM.
 __device__ __forceinline__ void tc_copy_sf_pair(uint32_t taddr, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
@@ -1313,7 +1220,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           LM_PROF_END(prof_acc1);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base + acc * kPairAcc1Col;
+          const uint32_t d_tmem = tmem_base + acc * kWideAcc1Col;
           for (int ks = 0; ks < p.k_stages; ++ks) {
             LM_PROF_BEGIN();
             ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusMmaTimeout);
@@ -1323,9 +1230,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             LM_PROF_BEGIN();
             const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
             const uint32_t stage_smem = smem_base + stage * kPairStageBytes;
-            const uint32_t sfa_t = tmem_base + kPairSfCol + sf_slot * kWideSfSlotCols;
+            const uint32_t sfa_t = tmem_base + kWideSfCol + sf_slot * kWideSfSlotCols;
             const uint32_t sfb_t = sfa_t + 16;
-            sf_slot = (sf_slot + 1) % kPairSfSlots;
+            sf_slot ^= 1u;
             const uint64_t a_desc = desc_sw128(stage_smem + kOffA);
             const uint64_t b_desc = desc_sw128(stage_smem + kOffB);
             const uint64_t sfa_desc = desc_sf_atom(stage_smem + kOffSfa);
@@ -1375,8 +1282,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     ctx.warp_store = store_base + (warp - kFirstEpilogueWarp) * kStoreBytesPerWarp;
     ctx.out_map = &tmap_out;
     ctx.remote = !leader;
-    ctx.acc1_col = kPairAcc1Col;
-    ctx.wide_overlap = true;
+    ctx.acc1_col = kWideAcc1Col;
     const uint32_t cols_bar = smem_u32(&misc->shared_cols_free);
     ctx.bar_shared_cols = leader ? cols_bar : map_to_cta(cols_bar, 0);
     ctx.inv_h = kOut == LM_OUT_NVFP4 ? __ldg(p.out_scale + 1) : 0.0f;

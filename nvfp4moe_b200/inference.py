@@ -79,14 +79,15 @@ def _expected_padded_rows(mean_rows: float, tile: int) -> float:
 def _row_tile(policy_tile_m: int, rows: int, experts: int, n: int, k: int, decode: bool, nvfp4_out: bool) -> int:
     """Row-tile height handed to a grouped GEMM: 256 runs 256 x 256 tiles on CTA pairs.
 
-    A pair pulls 30 % less data into each SM and issues half as many MMAs per FLOP: measured
-    10-20 % faster per padded row than 128 x 256 tiles, on both projections.  It pads every
-    expert to 256 rows, though, so it is chosen when that padding costs less than the pair
-    wins: the expected padded rows of both tile heights are compared for the plan's mean
-    rows per expert (with about 256 rows per expert the taller tile pads 20 % more and
-    loses; with 192, or with 512 and more, it wins).  The reference's own table
-    (``_tile_m``) is not consulted.  ``NVFP4MOE_TILE_M`` (128 or 256) overrides the choice
-    for tuning.
+    A pair moves 30 % fewer bytes through each SM's shared memory per FLOP and issues half as
+    many MMAs.  Measured per padded row it is about 1.25x faster than 128 x 256 tiles on a
+    first projection with K >= 4096 and about 1.1x elsewhere (short contractions and BF16
+    output are bound by the epilogue, which a pair does not change).  It pads every expert to
+    256 rows, though, so it is chosen when that padding costs less than the pair wins: the
+    expected padded rows of both tile heights are compared for the plan's mean rows per
+    expert (with about 256 rows per expert the taller tile pads 20 % more and loses; with
+    192, or with 512 and more, it wins).  The reference's own table (``_tile_m``) is not
+    consulted.  ``NVFP4MOE_TILE_M`` (128 or 256) overrides the choice for tuning.
     """
     forced = os.environ.get("NVFP4MOE_TILE_M")
     if forced:
@@ -94,7 +95,8 @@ def _row_tile(policy_tile_m: int, rows: int, experts: int, n: int, k: int, decod
     if decode or n % 256 or rows < 128 * experts:
         return 128
     mean_rows = rows / experts
-    return 256 if _expected_padded_rows(mean_rows, 256) <= 1.12 * _expected_padded_rows(mean_rows, 128) else 128
+    gain = 1.22 if (nvfp4_out and k >= 4096) else 1.10
+    return 256 if _expected_padded_rows(mean_rows, 256) <= gain * _expected_padded_rows(mean_rows, 128) else 128
 
 
 def _tile_m(token_expert_assignments: int, experts: int, hidden: int, intermediate: int):
