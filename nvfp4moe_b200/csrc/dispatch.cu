@@ -120,11 +120,17 @@ __device__ __forceinline__ void dispatch_chunk(const DispatchParams& p, int chun
     if (kSingle) {
       total = in_chunk;
     } else {
-#pragma unroll 8
-      for (int b = 0; b < p.chunks; ++b) {
-        int c = __ldg(p.scratch + static_cast<int64_t>(b) * E + tid);
-        total += c;
-        if (b < chunk) before += c;
+      // sixteen independent loads in flight per round trip to L2
+      for (int b0 = 0; b0 < p.chunks; b0 += 16) {
+        int c[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          c[j] = b0 + j < p.chunks ? __ldg(p.scratch + static_cast<int64_t>(b0 + j) * E + tid) : 0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          total += c[j];
+          if (b0 + j < chunk) before += c[j];
+        }
       }
     }
   }
