@@ -353,6 +353,24 @@ def test_grouped_gemm_cta_pairs_bit_identical(out_dtype, max_ctas):
     assert _lib.device_status() == 0
 
 
+@pytest.mark.parametrize(("n", "k"), ((256, 2688), (512, 64), (768, 192)))
+def test_grouped_gemm_cta_pairs_ragged_k(n, k):
+    """CTA pairs when K is not a multiple of the 256-element stage: the last stage holds fewer
+    64-element chunks (its scale-factor box reaches past K and reads zeros), down to a single
+    chunk for the whole contraction."""
+    lens = [259, 0, 1, 128, 640]
+    cu, a, b = _grouped_case(lens, n, k, seed=n + k, b_std=0.05)
+    narrow, _ = _run_grouped(cu, a, b)
+    pairs, _ = _run_grouped(cu, a, b, tile_n=256, tile_m=256)
+    ref, _ = _oracle_grouped(cu, a, b)
+    assert torch.isfinite(pairs).all()
+    assert torch.equal(pairs, narrow)
+    assert O.rel_frobenius(pairs.cpu().float(), ref.to(torch.bfloat16).float()) <= GEMM_REL_TOL
+    from nvfp4moe_b200 import _lib
+
+    assert _lib.device_status() == 0
+
+
 def test_grouped_gemm_fp32_output_and_per_expert_alpha():
     lens = [3, 5, 2, 7]
     cu, a, b = _grouped_case(lens, 128, 256, seed=20260822, b_std=1.0)
