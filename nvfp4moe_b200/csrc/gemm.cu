@@ -815,9 +815,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int acc = it & 1;
         LM_PROF_BEGIN();
         ok = mbar_wait(smem_u32(&misc->acc_empty[acc]), ((it >> 1) & 1u) ^ 1u, abort_flag, kStatusMmaTimeout);
-        LM_PROF_END(prof_acc1);
         if (ok && kNB == 2 && it > 0)  // the previous tile's accumulator overlaps this one
           ok = mbar_wait(smem_u32(&misc->shared_cols_free), (it - 1) & 1u, abort_flag, kStatusMmaTimeout);
+        LM_PROF_END(prof_acc1);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * (kNB == 1 ? kTileN : kWideAcc1Col);
