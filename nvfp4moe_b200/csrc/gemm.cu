@@ -53,7 +53,7 @@ constexpr long long kWaitLimitCycles = 2000000000ll;  // about one second
 constexpr int kTileBytes = kTileM * kStageKBytes;        // 16384
 constexpr int kSfBytes = kChunksPerStage * 512;          // 2048
 constexpr int kSlotBytes = kTileBytes + kSfBytes;        // 18432
-constexpr int kMaxRing = 8;      // ring stages (also TMEM scale-factor slots)
+constexpr int kMaxRing = 8;      // ring stages (128-column tiles: also TMEM scale-factor slots)
 constexpr int kMaxResident = 8;  // resident A stages: K <= 2048
 constexpr int kStoreRowPitch = 64 * 2;                   // BF16 staging row: 64 columns, 128-byte swizzled
 constexpr int kStoreBytesPerWarp = 32 * kStoreRowPitch;  // 4 KB: four swizzle atoms of 8 rows
@@ -603,16 +603,6 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
   finish(col_b);
 }
 
-// ------------------------------------------------------------------ kernel
-// kNB = 128-column blocks per tile.
-// 1: 128 x 128 tiles, two accumulators of 128 TMEM columns, one scale-factor slot per ring
-//    stage; epilogue group g drains accumulator g (every other tile).
-// 2: 128 x 256 tiles, which move a quarter less data through shared memory per FLOP (the
-//    resource that binds the main loop).  Two 256-column accumulators and the scale factors
-//    do not fit in 512 TMEM columns side by side, so the accumulators overlap in 96 columns:
-//    both epilogue groups work on every tile, read the 64-column slices that touch the
-//    overlap first and signal `shared_cols_free`; the MMAs of the next tile start then, while
-//    the rest of the tile is still being converted and stored.
 // Shared-memory descriptor of one 512-byte scale-factor atom: 32 rows of 16 bytes, no swizzle,
 // eight-row groups 128 bytes apart.
 __device__ __forceinline__ uint64_t desc_sf_atom(uint32_t smem_addr) {
@@ -630,6 +620,16 @@ __device__ __forceinline__ void tc_copy_sf(uint32_t taddr, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 
+// ------------------------------------------------------------------ kernel
+// kNB = 128-column blocks per tile.
+// 1: 128 x 128 tiles, two accumulators of 128 TMEM columns, one scale-factor slot per ring
+//    stage; epilogue group g drains accumulator g (every other tile).
+// 2: 128 x 256 tiles, which move a quarter less data through shared memory per FLOP (the
+//    resource that binds the main loop).  Two 256-column accumulators and the scale factors
+//    do not fit in 512 TMEM columns side by side, so the accumulators overlap in 96 columns:
+//    both epilogue groups work on every tile, read the 64-column slices that touch the
+//    overlap first and signal `shared_cols_free`; the MMAs of the next tile start then, while
+//    the rest of the tile is still being converted and stored.
 template <int kOut, int kAct, int kNB>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64,
@@ -956,8 +956,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 // of 54 KB: less of the L2-to-SM traffic that bounds the single-CTA kernel.  The ring holds
 // five stages (four with BF16 output).
 //
-// Roles per CTA as in gemm_kernel, without scale-factor warps: the leader (cluster rank 0)
-// issues the MMAs of the pair and, in front of each, the tcgen05.cp copies that bring that
+// Roles per CTA as in gemm_kernel: the leader (cluster rank 0) issues the MMAs of the pair and, in front of each, the tcgen05.cp copies that bring that
 // chunk's scale-factor atoms from each CTA's shared memory into its own TMEM.  Barriers:
 //   full[s]     leader's: the A, B and scale-factor loads of both CTAs complete on it (the
 //               peer's TMA loads name the leader's barrier), so scale factors come through
