@@ -954,7 +954,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 // the accumulator of its own 128 rows, and the tensor cores of both read B from both shared
 // memories.  An SM then ingests 38 KB per K stage for 128 x 256 x 256 multiply-adds instead
 // of 54 KB: less of the L2-to-SM traffic that bounds the single-CTA kernel.  The ring holds
-// five stages (four with BF16 output).
+// five stages.
 //
 // Roles per CTA as in gemm_kernel: the leader (cluster rank 0) issues the MMAs of the pair and, in front of each, the tcgen05.cp copies that bring that
 // chunk's scale-factor atoms from each CTA's shared memory into its own TMEM.  Barriers:
@@ -967,6 +967,16 @@ constexpr int kPairStageBytes = 2 * kTileBytes + 3 * kSfBytes;  // B half, SFB x
 // TMEM of a pair CTA: as for 128 x 256 tiles (accumulators at 0 and kWideAcc1Col, two
 // scale-factor slots from kWideSfCol).
 static_assert(kPairStageBytes % 1024 == 0, "pair ring stages must keep 1024-byte alignment");
+// The pair's ring is cut from the raw shared-memory budget, not from 18 KB operand slots: five
+// stages fit with either output kind (with BF16 staging they fill the 227 KB exactly).
+__host__ __device__ constexpr int pair_ring_stages(int out_kind) {
+  return (kSmemLimit - 1024 - kMiscBytes - (out_kind == LM_OUT_BF16 ? kStoreBytes : 0)) / kPairStageBytes;
+}
+__host__ __device__ constexpr int pair_smem_bytes(int out_kind) {
+  return 1024 + kMiscBytes + (out_kind == LM_OUT_BF16 ? kStoreBytes : 0) +
+         pair_ring_stages(out_kind) * kPairStageBytes;
+}
+static_assert(pair_ring_stages(LM_OUT_BF16) >= 4 && pair_ring_stages(LM_OUT_NVFP4) <= kMaxRing, "pair ring");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -1057,10 +1067,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  constexpr int kSlots = data_slots(kOut);
-  const uint32_t store_base = smem_base + kSlots * kSlotBytes;
-  Misc* misc = reinterpret_cast<Misc*>(smem_gen + kSlots * kSlotBytes +
-                                       (kOut == LM_OUT_BF16 ? kStoreBytes : 0));
+  constexpr int kRingBytes = pair_ring_stages(kOut) * kPairStageBytes;
+  const uint32_t store_base = smem_base + kRingBytes;
+  Misc* misc = reinterpret_cast<Misc*>(smem_gen + kRingBytes + (kOut == LM_OUT_BF16 ? kStoreBytes : 0));
   volatile int* abort_flag = &misc->abort_flag;
 
   // ring stage: [B half tile][B scale factors of both column blocks][A tile][A scale factors]
@@ -1425,13 +1434,13 @@ int launch_pair(const PlanData& pd, cudaStream_t stream) {
   auto kernel = gemm_pair_kernel<kOut, kAct>;
   static bool configured = false;
   if (!configured) {
-    LM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(kOut)));
+    LM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes(kOut)));
     configured = true;
   }
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(pd.grid);
   config.blockDim = dim3(kThreads);
-  config.dynamicSmemBytes = smem_bytes(kOut);
+  config.dynamicSmemBytes = pair_smem_bytes(kOut);
   config.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1555,10 +1564,7 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   } else {
     const int per_stage = pd.n_blocks + 1;  // B tile(s) and the A tile
     p.ring_stages = slots / per_stage < kMaxRing ? slots / per_stage : kMaxRing;
-    if (pd.pair) {
-      const int stages = slots * kSlotBytes / kPairStageBytes;
-      p.ring_stages = stages < kMaxRing ? stages : kMaxRing;
-    }
+    if (pd.pair) p.ring_stages = pair_ring_stages(a->out_kind);
     p.n_per_unit = 1;
   }
 #ifdef LM_GEMM_PROFILE
