@@ -127,6 +127,45 @@ def test_virtual_ranks_match_single_gpu(world, skew):
     assert _lib.device_status() == 0
 
 
+def test_virtual_ranks_on_cta_pairs():
+    """Enough rows per expert that both projections run 256 x 256 tiles on CTA pairs, fc2
+    writing every row through the row-pointer table; still bit-identical to one GPU."""
+    from nvfp4moe_b200 import InferenceMoE, _lib
+    from nvfp4moe_b200.expert_parallel import (ExpertParallelMoE, connect_virtual_ranks,
+                                               run_virtual_ranks)
+
+    tokens, hidden, inter, experts, k, world = 1024, 256, 128, 4, 2, 2
+    dev = torch.device("cuda", 0)
+    gate, up, down = (t.to(dev) for t in _weights(experts, hidden, inter, 9))
+    batches = []
+    for rank in range(world):
+        g = torch.Generator().manual_seed(300 + rank)
+        x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16).to(dev)
+        ids, w = _routing(tokens, experts, k, 400 + rank)
+        batches.append((x, ids.to(dev), w.to(dev)))
+    plain = InferenceMoE(hidden, inter, experts, k, tokens, device=dev)
+    plain.load_weights(gate, up, down)
+    plain.calibrate(*batches[0])
+    expected = [plain.run_prefill(*batch).clone() for batch in batches]
+    layers = []
+    for rank in range(world):
+        layer = ExpertParallelMoE(hidden, inter, experts, k, tokens, device=dev, rank=rank, world=world)
+        shard = slice(rank * 2, rank * 2 + 2)
+        layer.load_packed_weights(plain.qb1[shard].contiguous(), plain.sfb1[shard].contiguous(), plain.p_w1,
+                                  plain.qb2[shard].contiguous(), plain.sfb2[shard].contiguous(), plain.p_w2)
+        layer.set_activation_scales(plain._x_scale[:1], plain._h_scale[:1])
+        layers.append(layer)
+    connect_virtual_ranks(layers)
+    outs = [out.clone() for out in run_virtual_ranks(layers, batches)]
+    torch.cuda.synchronize()
+    for rank in range(world):
+        fc1, fc2 = layers[rank]._peer_gemms()
+        assert (fc1.tile_m, fc1.tile_n, fc2.tile_m, fc2.tile_n) == (256, 256, 256, 256)
+        assert layers[rank].step_is_valid()
+        assert torch.equal(outs[rank], expected[rank]), f"rank {rank}"
+    assert _lib.device_status() == 0
+
+
 def test_virtual_ranks_skip_an_oversized_step():
     from nvfp4moe_b200.expert_parallel import (ExpertParallelMoE, connect_virtual_ranks,
                                                run_virtual_ranks)
