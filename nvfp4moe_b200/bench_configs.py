@@ -1,6 +1,13 @@
 """Latency of the MoE layer and its two grouped GEMMs on the named workloads.
 
     python -m nvfp4moe_b200.bench_configs [name ...]
+    python -m nvfp4moe_b200.bench_configs --steps 3 [--virtual-ranks] name
+
+The second form runs ``--steps`` plain steps of one workload and times nothing: the command
+line a profiler wraps (the ``*_half`` workloads keep the per-expert shapes of their parents at
+half the size, so that operands still exceed the L2 while a capture that replays every launch
+dozens of times ends in a minute or two).  ``--virtual-ranks`` sends the batch through two
+expert-parallel ranks that live in this process (peer-memory transport on one GPU).
 
 Prints one JSON line per workload: median [IQR] of 21 CUDA-event samples after
 warm-up (the reference's protocol, BENCHMARKS.md:19-25), layer tokens/s, and
@@ -36,6 +43,9 @@ WORKLOADS = {
     "shard_deepseek_v4_flash": (4096, 2048, 8, 6, 8192, "swiglu", 10.0, "uniform", False),
     "shard_glm_5_2": (6144, 2048, 16, 8, 8192, "swiglu", None, "uniform", False),
     "shard_minimax_m3": (6144, 3072, 8, 4, 8192, "swiglu_oai", None, "uniform", False),
+    # half-size cases for profiler captures
+    "c2_half": (2048, 512, 128, 8, 4096, "swiglu", None, "uniform", False),
+    "shard_deepseek_v4_flash_half": (4096, 2048, 8, 6, 4096, "swiglu", 10.0, "uniform", False),
 }
 
 
@@ -109,7 +119,8 @@ def _timed(fn):
     return stats
 
 
-def run(name: str) -> dict:
+def build(name: str):
+    """The workload's layer with random weights, calibrated on its own batch."""
     hidden, inter, experts, k, tokens, act, clamp, routing, graph = WORKLOADS[name]
     dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator(device=dev).manual_seed(1)
@@ -129,6 +140,42 @@ def run(name: str) -> dict:
     x = torch.randn(tokens, hidden, generator=g, device=dev).to(torch.bfloat16)
     ids, w = _routing(tokens, experts, k, routing, dev)
     plan.calibrate(x, ids, w)
+    return plan, x, ids, w
+
+
+def run_steps(name: str, steps: int, virtual_ranks: bool = False) -> None:
+    """``steps`` untimed steps of one workload (for profiler captures)."""
+    hidden, inter, experts, k, tokens, act, clamp, _, _ = WORKLOADS[name]
+    plan, x, ids, w = build(name)
+    if virtual_ranks:
+        from nvfp4moe_b200.expert_parallel import (ExpertParallelMoE, connect_virtual_ranks,
+                                                   run_virtual_ranks)
+
+        ranks = []
+        for rank in range(2):
+            shard = slice(rank * experts // 2, (rank + 1) * experts // 2)
+            layer = ExpertParallelMoE(hidden, inter, experts, k, tokens, device=plan.device, rank=rank,
+                                      world=2, activation=act, activation_clamp=clamp)
+            layer.load_packed_weights(plan.qb1[shard].contiguous(), plan.sfb1[shard].contiguous(), plan.p_w1,
+                                      plan.qb2[shard].contiguous(), plan.sfb2[shard].contiguous(), plan.p_w2)
+            layer.set_activation_scales(plan._x_scale[:1], plan._h_scale[:1])
+            ranks.append(layer)
+        connect_virtual_ranks(ranks)
+        for _ in range(steps):
+            outs = run_virtual_ranks(ranks, [(x, ids, w), (x, ids, w)])
+        torch.cuda.synchronize()
+        print("ok", float(outs[0].float().abs().mean()))
+        return
+    for _ in range(steps):
+        plan.run(x, ids, w)
+    torch.cuda.synchronize()
+    print("ok", float(plan.output[:tokens].float().abs().mean()))
+
+
+def run(name: str) -> dict:
+    hidden, inter, experts, k, tokens, act, clamp, routing, graph = WORKLOADS[name]
+    unary = act == "relu2"
+    plan, x, ids, w = build(name)
     rows = tokens * k
     counts = torch.bincount(ids.flatten().long(), minlength=experts)
     result = {"workload": name, "hidden": hidden, "intermediate": inter, "experts": experts, "top_k": k,
@@ -158,7 +205,18 @@ def run(name: str) -> dict:
 
 
 def main(argv):
-    names = argv or list(WORKLOADS)
+    argv = list(argv)
+    if "--steps" in argv:
+        at = argv.index("--steps")
+        steps = int(argv[at + 1])
+        del argv[at : at + 2]
+        virtual = "--virtual-ranks" in argv
+        names = [a for a in argv if not a.startswith("--")]
+        if len(names) != 1:
+            raise SystemExit("--steps takes exactly one workload name")
+        run_steps(names[0], steps, virtual)
+        return
+    names = argv or [n for n in WORKLOADS if not n.endswith("_half")]
     for name in names:
         print(json.dumps(run(name)), flush=True)
         torch.cuda.empty_cache()

@@ -6,6 +6,8 @@
 // rows  > 1024: kernel 1 counts pairs per (1024-pair chunk, expert); kernel 2
 //               gives each chunk its stable base (prefix over experts, then over
 //               earlier chunks) and scatters.
+#include <atomic>
+
 #include "common.cuh"
 #include "quantize_math.cuh"
 
@@ -266,16 +268,18 @@ static __device__ __align__(256) int32_t g_static_scratch[kStaticElems];
 // In host code the array's name is only a handle; the device address comes from
 // cudaGetSymbolAddress, asked once per device with that device current.
 int static_scratch_ptr(int32_t** out) {
-  static int32_t* cached[64] = {nullptr};
+  // two host threads may make the first call on a device at once: both look the address up and
+  // store the same value, through atomics so that neither reads a torn pointer
+  static std::atomic<int32_t*> cached[64];
   int device = 0;
   LM_CUDA(cudaGetDevice(&device));
   if (device < 0 || device >= 64) return set_error(LM_ERR_LIMIT, "dispatch_static: device index out of range");
-  if (cached[device] == nullptr) {
-    int32_t* ptr = nullptr;
+  int32_t* ptr = cached[device].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
     LM_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch));
-    cached[device] = ptr;
+    cached[device].store(ptr, std::memory_order_release);
   }
-  *out = cached[device];
+  *out = ptr;
   return LM_OK;
 }
 

@@ -30,7 +30,6 @@
 // runs out the CTA raises a bit in a status word and leaves the kernel.
 #include <cuda.h>
 
-#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -48,6 +47,7 @@ constexpr int kThreads = 32 * (kFirstEpilogueWarp + kEpilogueWarps);
 constexpr int kMaxExperts = 256;
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitLimitCycles = 2000000000ll;  // about one second
+constexpr int kMaxDevices = 64;  // per-device caches of host-side state
 
 // shared memory: operand slots of 18 KB (a 128 x 128 B tile + its 2 KB of scale factors)
 constexpr int kTileBytes = kTileM * kStageKBytes;        // 16384
@@ -78,24 +78,6 @@ __host__ __device__ constexpr int smem_bytes(int out_kind) {
 
 __device__ uint32_t g_status = 0;
 
-#ifdef LM_GEMM_PROFILE
-// Cycle counters of CTA 0, written when the library is built with -DLM_GEMM_PROFILE:
-// [0] producer waits on empty, [1] MMA waits on full, [2] MMA waits on acc_empty,
-// [3] epilogue (warp 2) waits on acc_full, [4] epilogue (warp 2) busy, [5] kernel cycles,
-// [6] tiles of CTA 0, [7] MMA issue cycles
-__device__ unsigned long long g_prof[16];
-#define LM_PROF_DECL long long prof_t0 = clock64(), prof_acc0 = 0, prof_acc1 = 0, prof_acc2 = 0; (void)prof_t0; (void)prof_acc0; (void)prof_acc1; (void)prof_acc2
-#define LM_PROF_LAP(acc) { const long long now_ = clock64(); acc += now_ - prof_lap; prof_lap = now_; }
-#define LM_PROF_BEGIN() prof_t0 = clock64()
-#define LM_PROF_END(acc) acc += clock64() - prof_t0
-#define LM_PROF_STORE(idx, acc) if (blockIdx.x == 0) g_prof[idx] = static_cast<unsigned long long>(acc)
-#else
-#define LM_PROF_DECL
-#define LM_PROF_LAP(acc)
-#define LM_PROF_BEGIN()
-#define LM_PROF_END(acc)
-#define LM_PROF_STORE(idx, acc)
-#endif
 
 enum : uint32_t {
   kStatusProducerTimeout = 1u,
@@ -130,7 +112,6 @@ struct GemmParams {
   float clamp_limit;
   float sigmoid_alpha;
   float up_bias;
-  int debug_flags;  // profiling builds only: 1 = skip scale-factor copies, 2 = skip MMAs
 };
 
 // ------------------------------------------------------------------ PTX glue
@@ -179,6 +160,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       return false;
     }
   }
+}
+
+// Abort path only: wait for a phase without touching the abort flag, for at most `limit` cycles.
+__device__ __forceinline__ bool mbar_wait_quiet(uint32_t bar, uint32_t parity, long long limit) {
+  const long long start = clock64();
+  while (!mbar_try(bar, parity))
+    if (clock64() - start > limit) return false;
+  return true;
 }
 
 // True in exactly one lane of a converged warp.  Issuing TMA and tcgen05 instructions under
@@ -302,9 +291,14 @@ struct Misc {  // lives after the operand slots and the store staging
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint64_t shared_cols_free;       // 256-column tiles: the columns both accumulators use are read out
+  uint64_t drain;                  // abort path: the MMAs issued so far have completed
   uint32_t tmem_base;
   int abort_flag;
   int total_m_tiles;
+  int fills_issued;                // abort path: ring / resident-A fills the producer started ...
+  int fills_taken;                 // ... and those the MMA warp saw complete
+  int a_fills_issued;
+  int a_fills_taken;
   int pad;
   int cu[kMaxExperts + 1];
   int prefix[kMaxExperts + 2];
@@ -548,9 +542,6 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
         // the whole block belongs to this expert: one TMA store moves it
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-#ifdef LM_GEMM_PROFILE
-        if (!(p.debug_flags & 8))
-#endif
         if (lane == 0 && cols_ok)
           tma_store_2d(c.out_map, warp_store, col64 * 64, t.row0 + quarter * 32);
         return;
@@ -575,9 +566,6 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
           __nv_bfloat16* dst = warp_out + static_cast<int64_t>(row) * p.n;
           if (p.out_row_ptrs != nullptr)
             dst = reinterpret_cast<__nv_bfloat16*>(__shfl_sync(0xFFFFFFFFu, row_base, row));
-#ifdef LM_GEMM_PROFILE
-          if (p.debug_flags & 8) continue;
-#endif
           if (row < rows_here && col < p.n) *reinterpret_cast<uint4*>(dst + col) = d[i];
         }
       }
@@ -670,7 +658,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       mbar_init(smem_u32(&misc->acc_empty[s]), kNB == 1 ? 4 : 8);
     }
     mbar_init(smem_u32(&misc->shared_cols_free), 8);
+    mbar_init(smem_u32(&misc->drain), 1);
     misc->abort_flag = 0;
+    misc->fills_issued = misc->fills_taken = misc->a_fills_issued = misc->a_fills_taken = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -734,7 +724,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     uint32_t phase = 0;
     uint32_t a_phase = 0;
     bool ok = true;
-    LM_PROF_DECL;
+    int fills = 0, a_fills = 0;  // loads started: the abort path waits for those nobody consumed
     for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
       const Unit u = decode_unit(p, unit);
       const RowTile t = walker.at(misc, p, u.mt);
@@ -754,9 +744,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const uint32_t sf_bytes = chunks * 512;
           if (resident && nt == u.n_begin) {
             // the unit's A tile, stage by stage, as soon as the previous unit has let go of it
-            LM_PROF_BEGIN();
             ok = mbar_wait(smem_u32(&misc->a_empty[ks]), a_phase ^ 1u, abort_flag, kStatusProducerTimeout);
-            LM_PROF_END(prof_acc0);
             if (!ok) break;
             if (elect_one()) {
               const uint32_t bar = smem_u32(&misc->a_full[ks]);
@@ -766,10 +754,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               bulk_load(dst + kTileBytes, sfa_src + static_cast<int64_t>(ks) * kSfBytes, sf_bytes, bar);
             }
             __syncwarp();
+            ++a_fills;
           }
-          LM_PROF_BEGIN();
           ok = mbar_wait(smem_u32(&misc->empty[stage]), phase ^ 1u, abort_flag, kStatusProducerTimeout);
-          LM_PROF_END(prof_acc0);
           if (!ok) break;
           if (elect_one()) {
             const uint32_t bar = smem_u32(&misc->full[stage]);
@@ -787,49 +774,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
           }
           __syncwarp();
+          ++fills;
           if (++stage == p.ring_stages) { stage = 0; phase ^= 1u; }
         }
       }
       a_phase ^= 1u;
     }
-    if (lane == 0) { LM_PROF_STORE(0, prof_acc0); }
+    if (lane == 0) {
+      misc->fills_issued = fills;
+      misc->a_fills_issued = a_fills;
+    }
   } else if (warp == 1) {
     // ===================================================== MMA issuer
-#ifdef LM_GEMM_PROFILE
-    const uint32_t idesc = (p.debug_flags >> 8) ? make_idesc(p.debug_flags >> 8) : make_idesc(kNB * kTileN);
-#else
     constexpr uint32_t idesc = make_idesc(kNB * kTileN);
-#endif
     uint32_t sf_slot = 0;  // 256-column tiles: scale-factor slot, alternates per stage
     int stage = 0;
     uint32_t phase = 0;
     uint32_t a_phase = 0;
     int it = 0;
+    int taken = 0, a_taken = 0;
     bool ok = true;
-    LM_PROF_DECL;
-    const long long prof_start = clock64();
-    (void)prof_start;
     for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
       const Unit u = decode_unit(p, unit);
       for (int nt = u.n_begin; nt < u.n_end && ok; ++nt, ++it) {
         const int acc = it & 1;
-        LM_PROF_BEGIN();
         ok = mbar_wait(smem_u32(&misc->acc_empty[acc]), ((it >> 1) & 1u) ^ 1u, abort_flag, kStatusMmaTimeout);
         if (ok && kNB == 2 && it > 0)  // the previous tile's accumulator overlaps this one
           ok = mbar_wait(smem_u32(&misc->shared_cols_free), (it - 1) & 1u, abort_flag, kStatusMmaTimeout);
-        LM_PROF_END(prof_acc1);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * (kNB == 1 ? kTileN : kWideAcc1Col);
         for (int ks = 0; ks < p.k_stages; ++ks) {
-          LM_PROF_BEGIN();
           ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusMmaTimeout);
-          if (ok && resident && nt == u.n_begin)
+          if (ok) ++taken;
+          if (ok && resident && nt == u.n_begin) {
             ok = mbar_wait(smem_u32(&misc->a_full[ks]), a_phase, abort_flag, kStatusMmaTimeout);
-          LM_PROF_END(prof_acc0);
+            if (ok) ++a_taken;
+          }
           if (!ok) break;
           tc_fence_after();
-          LM_PROF_BEGIN();
           const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
           const uint32_t b_smem = ring_base + stage * ring_stride;
           const uint32_t a_smem = resident ? smem_base + ks * kSlotBytes : b_smem + kAOffset;
@@ -854,9 +837,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               tc_mma_nvf4(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 4 * kNB,
                           (ks > 0 || c > 0) ? 1u : 0u);
             };
-#ifdef LM_GEMM_PROFILE
-            if (!(p.debug_flags & 2))
-#endif
             if (chunks == kChunksPerStage) {
 #pragma unroll
               for (int c = 0; c < kChunksPerStage; ++c) chunk(c);
@@ -867,7 +847,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             if (resident && nt == u.n_end - 1) tc_commit(smem_u32(&misc->a_empty[ks]));
           }
           __syncwarp();
-          LM_PROF_END(prof_acc2);
           if (++stage == p.ring_stages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
@@ -877,11 +856,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       a_phase ^= 1u;
     }
     if (lane == 0) {
-      LM_PROF_STORE(1, prof_acc0);
-      LM_PROF_STORE(2, prof_acc1);
-      LM_PROF_STORE(7, prof_acc2);
-      LM_PROF_STORE(5, clock64() - prof_start);
-      LM_PROF_STORE(6, it);
+      misc->fills_taken = taken;
+      misc->a_fills_taken = a_taken;
     }
   } else if (warp >= kFirstEpilogueWarp) {
     // ===================================================== epilogue
@@ -904,7 +880,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     TileWalker walker;
     int it = 0;
     bool ok = true;
-    LM_PROF_DECL;
     for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
       const Unit u = decode_unit(p, unit);
       const RowTile t = walker.at(misc, p, u.mt);
@@ -912,35 +887,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (int nt = u.n_begin; nt < u.n_end; ++nt, ++it) {
         if (kNB == 1 && (it & 1) != group) continue;
         const int acc = it & 1;
-        LM_PROF_END(prof_acc1);  // busy since the previous wait ended
-        LM_PROF_BEGIN();
         ok = mbar_wait(smem_u32(&misc->acc_full[acc]), (it >> 1) & 1u, abort_flag, kStatusEpilogueTimeout);
-        LM_PROF_END(prof_acc0);
-        LM_PROF_BEGIN();
         if (!ok) break;
         tc_fence_after();
         ctx.bar_acc_empty = smem_u32(&misc->acc_empty[acc]);
         drain_tile<kOut, kAct, kNB>(p, t, ctx, acc, nt);
       }
     }
-    LM_PROF_END(prof_acc1);
     if (kOut == LM_OUT_BF16 && lane == 0) tma_store_wait_all();
-    if (warp == kFirstEpilogueWarp && lane == 0) {
-      LM_PROF_STORE(3, prof_acc0);
-      LM_PROF_STORE(4, prof_acc1);
-    }
   }
 
   // ---- teardown
   __syncwarp();
-  if (*abort_flag) {
-    // give copies still in flight time to land before shared memory is released
-    const long long start = clock64();
-    while (clock64() - start < 2000000ll) {
-    }
-  }
   tc_fence_before();
   __syncthreads();
+  if (*abort_flag) {
+    // A bounded wait ran out.  Before shared memory and TMEM are released, wait (bounded again)
+    // for what is still in flight: the loads the producer started and nobody consumed complete
+    // on their `full` barriers, and a commit after the last MMA tells when the tensor core is
+    // done reading shared memory and writing TMEM.
+    constexpr long long kDrainLimit = 200000000ll;  // about 0.1 s per barrier
+    if (warp == 0 && lane == 0) {
+      for (int f = misc->fills_taken; f < misc->fills_issued; ++f)
+        mbar_wait_quiet(smem_u32(&misc->full[f % p.ring_stages]), (f / p.ring_stages) & 1u, kDrainLimit);
+      if (resident)
+        for (int f = misc->a_fills_taken; f < misc->a_fills_issued; ++f)
+          mbar_wait_quiet(smem_u32(&misc->a_full[f % p.k_stages]), (f / p.k_stages) & 1u, kDrainLimit);
+    }
+    if (warp == 1) {
+      if (elect_one()) {
+        tc_commit(smem_u32(&misc->drain));
+        mbar_wait_quiet(smem_u32(&misc->drain), 0, kDrainLimit);
+      }
+      __syncwarp();
+    }
+    tc_fence_before();
+    __syncthreads();
+  }
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
@@ -1094,16 +1077,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       mbar_init(smem_u32(&misc->acc_empty[s]), 16);
     }
     mbar_init(smem_u32(&misc->shared_cols_free), 16);
+    mbar_init(smem_u32(&misc->drain), 1);
     misc->abort_flag = 0;
+    misc->fills_issued = misc->fills_taken = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+    // every tcgen05 instruction of this kernel is a pair (cta_group::2) instruction: warp 1 of
+    // both CTAs allocates together and each CTA reads the common base from its own shared memory
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&misc->tmem_base)),
                  "r"(kTmemCols)
                  : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   if (p.dense) {
     if (threadIdx.x == 0) {
@@ -1159,7 +1146,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    LM_PROF_DECL;
+    int fills = 0;
     for (int unit = first_unit; unit < total_units && ok; unit += unit_stride) {
       const Unit u = decode_unit(p, unit);
       const RowTile t = pair_row_tile(misc, p, cursor, u.mt, rank);
@@ -1171,9 +1158,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int b_row = t.expert * p.n + nt * 2 * kTileN + rank * kTileN;
         const int sfb_row = t.expert * p.sfb_atom_rows + nt * 2;
         for (int ks = 0; ks < p.k_stages; ++ks) {
-          LM_PROF_BEGIN();
           ok = mbar_wait(smem_u32(&misc->empty[stage]), phase ^ 1u, abort_flag, kStatusProducerTimeout);
-          LM_PROF_END(prof_acc0);
           if (!ok) break;
           if (elect_one()) {
             const uint32_t bar = smem_u32(&misc->full[stage]);
@@ -1200,11 +1185,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
           __syncwarp();
+          ++fills;
           if (++stage == p.ring_stages) { stage = 0; phase ^= 1u; }
         }
       }
     }
-    if (lane == 0) { LM_PROF_STORE(0, prof_acc0); }
+    if (lane == 0) {
+      misc->fills_issued = fills;
+    }
   } else if (warp == 1) {
     // ===================================================== MMA issuer (leader only)
     if (leader) {
@@ -1213,29 +1201,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
+      int taken = 0;
       bool ok = true;
-      LM_PROF_DECL;
-      const long long prof_start = clock64();
-      (void)prof_start;
       for (int unit = first_unit; unit < total_units && ok; unit += unit_stride) {
         const Unit u = decode_unit(p, unit);
         for (int nt = u.n_begin; nt < u.n_end && ok; ++nt, ++it) {
           const int acc = it & 1;
-          LM_PROF_BEGIN();
           ok = mbar_wait(smem_u32(&misc->acc_empty[acc]), ((it >> 1) & 1u) ^ 1u, abort_flag, kStatusMmaTimeout);
           if (ok && it > 0)
             ok = mbar_wait(smem_u32(&misc->shared_cols_free), (it - 1) & 1u, abort_flag, kStatusMmaTimeout);
-          LM_PROF_END(prof_acc1);
           if (!ok) break;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * kWideAcc1Col;
           for (int ks = 0; ks < p.k_stages; ++ks) {
-            LM_PROF_BEGIN();
             ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusMmaTimeout);
-            LM_PROF_END(prof_acc0);
             if (!ok) break;
+            ++taken;
             tc_fence_after();
-            LM_PROF_BEGIN();
             const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
             const uint32_t stage_smem = smem_base + stage * kPairStageBytes;
             const uint32_t sfa_t = tmem_base + kWideSfCol + sf_slot * kWideSfSlotCols;
@@ -1264,7 +1246,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               tc_commit_pair(smem_u32(&misc->empty[stage]));
             }
             __syncwarp();
-            LM_PROF_END(prof_acc2);
             if (++stage == p.ring_stages) { stage = 0; phase ^= 1u; }
           }
           if (!ok) break;
@@ -1273,11 +1254,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
       if (lane == 0) {
-        LM_PROF_STORE(1, prof_acc0);
-        LM_PROF_STORE(2, prof_acc1);
-        LM_PROF_STORE(7, prof_acc2);
-        LM_PROF_STORE(5, clock64() - prof_start);
-        LM_PROF_STORE(6, it);
+        misc->fills_taken = taken;
       }
     }
   } else if (warp >= kFirstEpilogueWarp) {
@@ -1316,17 +1293,34 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   // ---- teardown: neither CTA leaves while the other may still signal its barriers
   __syncwarp();
+  tc_fence_before();
+  __syncthreads();
   if (*abort_flag) {
+    // As in gemm_kernel: the leader waits (bounded) for the stage fills that were started and
+    // never consumed -- the loads of both CTAs complete on its barriers -- and for its MMAs.
+    // A load the peer started for a stage the leader never announced cannot be waited for by
+    // anyone; for that case alone both CTAs also let a fixed two million cycles pass.
+    constexpr long long kDrainLimit = 200000000ll;
+    if (leader && warp == 0 && lane == 0)
+      for (int f = misc->fills_taken; f < misc->fills_issued; ++f)
+        mbar_wait_quiet(smem_u32(&misc->full[f % p.ring_stages]), (f / p.ring_stages) & 1u, kDrainLimit);
+    if (leader && warp == 1) {
+      if (elect_one()) {
+        tc_commit_pair(smem_u32(&misc->drain));
+        mbar_wait_quiet(smem_u32(&misc->drain), 0, kDrainLimit);
+      }
+      __syncwarp();
+    }
     const long long start = clock64();
     while (clock64() - start < 2000000ll) {
     }
+    tc_fence_before();
+    __syncthreads();
   }
-  tc_fence_before();
-  __syncthreads();
   cluster_sync();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
                  : "memory");
   }
 }
@@ -1418,10 +1412,13 @@ int encode_sf(CUtensorMap* map, const void* base, uint64_t atom_cols, uint64_t a
 template <int kOut, int kAct, int kNB>
 int launch_kernel(const PlanData& pd, cudaStream_t stream) {
   auto kernel = gemm_kernel<kOut, kAct, kNB>;
-  static bool configured = false;
-  if (!configured) {
+  // the shared-memory opt-in is a per-device attribute of the function
+  static bool configured[kMaxDevices] = {};
+  int device = 0;
+  LM_CUDA(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices || !configured[device]) {
     LM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(kOut)));
-    configured = true;
+    if (device >= 0 && device < kMaxDevices) configured[device] = true;
   }
   kernel<<<pd.grid, kThreads, smem_bytes(kOut), stream>>>(pd.map_a, pd.map_a64, pd.map_a32, pd.map_b,
                                                           pd.map_out, pd.params);
@@ -1432,10 +1429,12 @@ int launch_kernel(const PlanData& pd, cudaStream_t stream) {
 template <int kOut, int kAct>
 int launch_pair(const PlanData& pd, cudaStream_t stream) {
   auto kernel = gemm_pair_kernel<kOut, kAct>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[kMaxDevices] = {};
+  int device = 0;
+  LM_CUDA(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices || !configured[device]) {
     LM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes(kOut)));
-    configured = true;
+    if (device >= 0 && device < kMaxDevices) configured[device] = true;
   }
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(pd.grid);
@@ -1536,9 +1535,6 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   p.clamp_limit = a->clamp_limit;
   p.sigmoid_alpha = a->sigmoid_alpha;
   p.up_bias = a->up_bias;
-#ifdef LM_GEMM_PROFILE
-  if (const char* flags = getenv("LM_GEMM_DEBUG")) p.debug_flags = atoi(flags);
-#endif
   const int sms = sm_count();
   LM_REQUIRE(sms > 0, "gemm: no CUDA device");
   pd.grid = a->max_ctas > 0 ? a->max_ctas : sms;
@@ -1552,9 +1548,6 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   p.a_resident =
       (pd.n_blocks == 1 && p.k_stages <= kMaxResident && slots - p.k_stages >= 6 && p.n_tiles >= 2) ? 1 : 0;
   const int row_tile = pd.pair ? 2 * kTileM : kTileM;
-#ifdef LM_GEMM_PROFILE
-  if (p.debug_flags & 4) p.a_resident = 0;
-#endif
   if (p.a_resident) {
     p.ring_stages = slots - p.k_stages < kMaxRing ? slots - p.k_stages : kMaxRing;
     // the longest run of column tiles that still leaves about eight units per CTA
@@ -1567,9 +1560,6 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
     if (pd.pair) p.ring_stages = pair_ring_stages(a->out_kind);
     p.n_per_unit = 1;
   }
-#ifdef LM_GEMM_PROFILE
-  if (const char* ring = getenv("LM_GEMM_RING")) p.ring_stages = atoi(ring) < p.ring_stages ? atoi(ring) : p.ring_stages;
-#endif
   p.units_per_mtile = (p.n_tiles + p.n_per_unit - 1) / p.n_per_unit;
   // more CTAs than units would only idle: rows/128 + experts bounds the row tiles
   const int64_t max_units = ((a->rows + row_tile - 1) / row_tile + a->experts) * p.units_per_mtile;
@@ -1641,11 +1631,3 @@ extern "C" int lm_device_status_clear(lm_stream_t stream) {
   return ep_status_clear();
 }
 
-#ifdef LM_GEMM_PROFILE
-extern "C" int lm_gemm_profile_read(unsigned long long* out, lm_stream_t stream) {
-  using namespace lm;
-  LM_CUDA(cudaStreamSynchronize(as_stream(stream)));
-  LM_CUDA(cudaMemcpyFromSymbol(out, g_prof, sizeof(g_prof)));
-  return LM_OK;
-}
-#endif

@@ -68,6 +68,28 @@ class ExpertParallelExchange:
         dist.all_to_all_single(received, counts, group=self.group)
         return received
 
+    def verify_splits(self, send_splits: list[int], recv_splits: list[int]) -> None:
+        """Host-side check before an all-to-all-v: what this rank is about to send to rank o
+        must be what o expects from it.  A mismatch (ranks built with different expert counts,
+        a count table that was overwritten) would otherwise surface as a hang or as rows in the
+        wrong place.  Every rank learns of a mismatch anywhere and raises ``RuntimeError``, so
+        no rank enters the exchange alone.  Costs two small collectives: a debugging aid, off
+        by default."""
+        if self.world == 1:
+            return
+        backend = dist.get_backend(self.group)
+        device = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
+        mine = torch.tensor(send_splits, dtype=torch.int64, device=device)
+        theirs = torch.empty_like(mine)
+        dist.all_to_all_single(theirs, mine, group=self.group)  # theirs[o] = rows o will send here
+        expected = torch.tensor(recv_splits, dtype=torch.int64, device=device)
+        flag = (theirs != expected).any().to(torch.int32).reshape(1)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group)
+        if int(flag.item()):
+            raise RuntimeError(
+                f"rank {self.rank}: all-to-all split sizes disagree between ranks "
+                f"(peers send {theirs.tolist()}, this rank expects {list(recv_splits)})")
+
     def forward_rows(self, rows: torch.Tensor, send_splits: list[int], recv_splits: list[int]):
         if self.world == 1:
             return rows
@@ -162,6 +184,7 @@ class ExpertParallelMoE:
         self._out = torch.empty(max_tokens, hidden_size, dtype=torch.bfloat16, device=self.device)
         self._ones = torch.ones(max_recv_rows, 1, dtype=torch.float32, device=self.device)
         self.last_recv_rows = 0
+        self.verify_splits = False  # collective transport: check the split lists across ranks first
         self._peer = None
         if transport == "peer":
             self._build_peer_buffers()
@@ -395,6 +418,8 @@ class ExpertParallelMoE:
         send_list, recv_list = host[: ex.world], host[ex.world :]
         received = sum(recv_list)
         self.last_recv_rows = received
+        if self.verify_splits:
+            ex.verify_splits(send_list, recv_list)
         if received > self.max_recv_rows:
             raise RuntimeError(f"received {received} rows, workspace holds {self.max_recv_rows}")
 
@@ -460,10 +485,13 @@ def run_virtual_ranks(layers, batches, outs=None):
     return [layer._phase_combine(None if outs is None else outs[layer.rank]) for layer in ordered]
 
 
-def reference_step(x, topk_ids, topk_weights, compute_rows: Callable, exchange: ExpertParallelExchange):
+def reference_step(x, topk_ids, topk_weights, compute_rows: Callable, exchange: ExpertParallelExchange,
+                   *, verify: bool = False, tamper: Callable | None = None):
     """The same exchange pattern on plain torch ops, for host-side (gloo) tests.
 
-    ``compute_rows(rows, local_expert_ids)`` stands in for the expert GEMMs.
+    ``compute_rows(rows, local_expert_ids)`` stands in for the expert GEMMs.  ``verify`` runs
+    :meth:`ExpertParallelExchange.verify_splits` before rows move; ``tamper(send, recv)`` lets a
+    test corrupt the split lists of one rank first.
     """
     tokens, k = topk_ids.shape
     flat = topk_ids.reshape(-1).long()
@@ -474,6 +502,10 @@ def reference_step(x, topk_ids, topk_weights, compute_rows: Callable, exchange: 
     recv_counts = exchange.exchange_counts(m_indptr)
     send_list = owner_splits(m_indptr, exchange.world).tolist()
     recv_list = recv_counts.sum(1).tolist()
+    if tamper is not None:
+        send_list, recv_list = tamper(send_list, recv_list)
+    if verify:
+        exchange.verify_splits(send_list, recv_list)
     recv_rows = exchange.forward_rows(x[(order // k)].contiguous(), send_list, recv_list)
     ids = received_expert_ids(recv_counts)
     back = compute_rows(recv_rows, ids)

@@ -14,7 +14,6 @@ dispatch -> quantize gathered rows -> fc1 (activation + requantization fused)
 from __future__ import annotations
 
 import math
-import os
 from dataclasses import dataclass
 
 import torch
@@ -52,11 +51,8 @@ def _tile_n(n: int, k: int, decode: bool) -> int:
     128 x 256 tiles pull a quarter less data into the SM per FLOP than 128 x 128 tiles and
     were 1.25x to 1.7x faster on every prefill shape measured (K from 512 to 4096); decode
     steps have few row tiles and keep the narrow tile so that more CTAs share the weight
-    traffic.  ``NVFP4MOE_TILE_N`` (128 or 256) overrides the choice for tuning.
+    traffic.
     """
-    forced = os.environ.get("NVFP4MOE_TILE_N")
-    if forced:
-        return int(forced)
     return 128 if decode or n % 256 else 256
 
 
@@ -87,11 +83,8 @@ def _row_tile(policy_tile_m: int, rows: int, experts: int, n: int, k: int, decod
     expected padded rows of both tile heights are compared for the plan's mean rows per
     expert (with about 256 rows per expert the taller tile pads 20 % more and loses; with
     192, or with 512 and more, it wins).  The reference's own table (``_tile_m``) is not
-    consulted.  ``NVFP4MOE_TILE_M`` (128 or 256) overrides the choice for tuning.
+    consulted.
     """
-    forced = os.environ.get("NVFP4MOE_TILE_M")
-    if forced:
-        return int(forced)
     if decode or n % 256 or rows < 128 * experts:
         return 128
     mean_rows = rows / experts
@@ -308,6 +301,9 @@ class InferenceMoE:
             self._alpha1 = torch.empty(1, dtype=torch.float32, device=self.device)
             self._alpha2 = torch.empty(1, dtype=torch.float32, device=self.device)
 
+        # (tile_m, tile_n) forced on every GEMM this plan builds from now on, or None for the
+        # policy above; tests use it to compare tilings bit for bit
+        self.tile_override: tuple[int, int] | None = None
         self._weights_ready = False
         self._scales_ready = False
         self._full_executions: dict[tuple[int, bool], _FullExecution] = {}
@@ -461,14 +457,17 @@ class InferenceMoE:
         fc1_m, fc2_m = _tile_m(rows, self.experts, self.hidden_size, self.intermediate_size)
         if projection == "fc1":
             unary = self.activation == "relu2"
+            n1 = self.intermediate_size if unary else 2 * self.intermediate_size
+            tile_m, tile_n = self.tile_override or (
+                _row_tile(fc1_m, rows, self.experts, n1, self.hidden_size, decode,
+                          output_dtype == torch.float4_e2m1fn_x2),
+                _tile_n(n1, self.hidden_size, decode))
             return GroupedNvfp4Gemm(
                 self.experts,
-                self.intermediate_size if unary else 2 * self.intermediate_size,
+                n1,
                 self.hidden_size,
-                _row_tile(fc1_m, rows, self.experts, self.intermediate_size if unary else 2 * self.intermediate_size,
-                          self.hidden_size, decode, output_dtype == torch.float4_e2m1fn_x2),
-                _tile_n(self.intermediate_size if unary else 2 * self.intermediate_size,
-                        self.hidden_size, decode),
+                tile_m,
+                tile_n,
                 output_dtype=output_dtype,
                 epilogue=self._epilogue() if output_dtype == torch.float4_e2m1fn_x2 else None,
                 use_dynamic_sched=schedule,
@@ -476,12 +475,15 @@ class InferenceMoE:
                 swap_ab=False,
                 fast_decode_sched=(decode and not schedule and self.hidden_size >= 2048),
             )
+        tile_m, tile_n = self.tile_override or (
+            _row_tile(fc2_m, rows, self.experts, self.hidden_size, self.intermediate_size, decode, False),
+            _tile_n(self.hidden_size, self.intermediate_size, decode))
         return GroupedNvfp4Gemm(
             self.experts,
             self.hidden_size,
             self.intermediate_size,
-            _row_tile(fc2_m, rows, self.experts, self.hidden_size, self.intermediate_size, decode, False),
-            _tile_n(self.hidden_size, self.intermediate_size, decode),
+            tile_m,
+            tile_n,
             use_dynamic_sched=schedule,
             use_pdl=True,
         )

@@ -505,6 +505,38 @@ def moe_layer(x, topk_ids, topk_weights, w1_q, w1_sf, w1_pts, w2_q, w2_sf, w2_pt
     return out
 
 
+def moe_layer_sampled(x, topk_ids, topk_weights, expert_weights, w1_pts, w2_pts, x_scale, h_scale,
+                      activation="swiglu", clamp=None, sigmoid_alpha=1.0, up_bias=0.0):
+    """:func:`moe_layer` for a handful of tokens of a large batch.
+
+    Every output row of the layer depends on its own token only, so a sample of the tokens can
+    be checked end to end without the whole batch: ``x`` (T, H), ``topk_ids`` / ``topk_weights``
+    (T, k) are the sampled rows and ``expert_weights[e]`` = ``(w1_q, w1_sf, w2_q, w2_sf)`` holds
+    the packed weights (row-major scale factors) of every expert the sample touches.  Same
+    stage order and arithmetic as :func:`moe_layer` (``inference.py:883-930``).
+    """
+    tokens, k = topk_ids.shape
+    w1_pts = torch.as_tensor(w1_pts, dtype=torch.float32).reshape(-1)
+    w2_pts = torch.as_tensor(w2_pts, dtype=torch.float32).reshape(-1)
+    qx, sfx = quantize_rows(x, x_scale, te_math=True)
+    xd = dequantize_rows(qx, sfx, 1.0)
+    routed = torch.zeros(tokens, k, x.shape[1], dtype=torch.bfloat16)
+    for e in topk_ids.unique().tolist():
+        tok, route = (topk_ids == e).nonzero(as_tuple=True)
+        w1_q, w1_sf, w2_q, w2_sf = expert_weights[e]
+        alpha1 = _f32(x_scale) * (w1_pts[e] if w1_pts.numel() > 1 else w1_pts[0])
+        alpha2 = _f32(h_scale) * (w2_pts[e] if w2_pts.numel() > 1 else w2_pts[0])
+        pre = (xd[tok] @ dequantize_rows(w1_q, w1_sf, 1.0).T) * alpha1
+        hidden = apply_activation(pre, activation, clamp, sigmoid_alpha, up_bias)
+        qh, sfh = quantize_epilogue(hidden, h_scale)
+        out = (dequantize_rows(qh, sfh, 1.0) @ dequantize_rows(w2_q, w2_sf, 1.0).T) * alpha2
+        routed[tok, route] = out.to(torch.bfloat16)
+    acc = torch.zeros(tokens, x.shape[1], dtype=torch.float32)
+    for j in range(k):
+        acc += routed[:, j].to(torch.float32) * topk_weights[:, j].to(torch.float32).unsqueeze(1)
+    return acc.to(torch.bfloat16)
+
+
 def calibrate(x, topk_ids, topk_weights, w1_q, w1_sf, w1_pts, activation="swiglu",
               clamp=None, sigmoid_alpha=1.0, up_bias=0.0):
     """Static activation scales as ``inference.py:723-805`` derives them.

@@ -224,3 +224,31 @@ def test_host_pipeline_needs_cuda():
         HostPipeline(object(), 8, 128, 2)
     with pytest.raises(ValueError, match="depth"):
         HostPipeline(object(), 8, 128, 2, depth=0)
+
+
+def test_tensor_scale_tracks_amax_without_host_reads():
+    """``TensorScale`` (``lightmoe/_quantization.py:14-67``): amax / 2688 with its reciprocal,
+    floored at the smallest normal FP32, readable only after a first update."""
+    from nvfp4moe_b200._quantization import TensorScale
+
+    scale = TensorScale(device="cpu")
+    with pytest.raises(AssertionError, match="before calibration"):
+        scale.pair
+    t = torch.tensor([[0.5, -5376.0], [3.0, 1.0]], dtype=torch.bfloat16)
+    scale.update(t)
+    assert scale.pair.dtype == torch.float32 and tuple(scale.pair.shape) == (2,)
+    assert float(scale.pts) == 2.0 and float(scale.inv_pts) == 0.5  # |-5376| / 2688
+    scale.update(torch.tensor([1344.0, -2.0]))
+    assert float(scale.pts) == 0.5 and float(scale.inv_pts) == 2.0
+    scale.set_amax(torch.tensor(2688.0))
+    assert float(scale.pts) == 1.0 and float(scale.inv_pts) == 1.0
+    # an all-zero tensor does not produce an infinite reciprocal
+    scale.update(torch.zeros(4))
+    assert float(scale.pts) == torch.finfo(torch.float32).tiny
+    assert torch.isfinite(scale.inv_pts).all()
+    # the views alias the pair: a later update is visible through views taken earlier
+    pts_view = scale.pts
+    scale.set_amax(torch.tensor(5376.0))
+    assert float(pts_view) == 2.0
+    with pytest.raises(NotImplementedError):
+        TensorScale(device="cpu", te_rht=True)

@@ -36,40 +36,98 @@ def _expert_fn(rows: torch.Tensor, global_expert: torch.Tensor) -> torch.Tensor:
 
 
 def _expected(x, ids, w):
-    out = torch.zeros(TOKENS, HIDDEN)
-    for t in range(TOKENS):
+    out = torch.zeros(x.shape[0], HIDDEN)
+    for t in range(x.shape[0]):
         for j in range(TOPK):
             e = ids[t, j].reshape(1)
             out[t] += _expert_fn(x[t : t + 1], e)[0].float() * w[t, j]
     return out
 
 
-def _worker(rank: int, world: int, port: int, fail_rank: int, results):
+def _worker(rank: int, world: int, port: int, scenario: str, results):
+    """One gloo rank.  Scenarios (every failure is made on the host, none touches a GPU):
+    ``ok``           both ranks run a step;
+    ``empty``        rank 1 brings a batch of zero tokens;
+    ``tamper``       rank 1 corrupts its split lists, the verified exchange must refuse on both;
+    ``raise_before`` rank 1 raises before the exchange, rank 0's collective must end with an
+                     error (closed connection or the group's short timeout) instead of hanging.
+    """
+    import datetime
+
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
     try:
         exchange = ExpertParallelExchange(EXPERTS)
         assert exchange.local_experts == EXPERTS // world
         x, ids, w = _inputs(rank)
+        if scenario == "empty" and rank == 1:
+            x, ids, w = x[:0], ids[:0], w[:0]
         first_local = rank * exchange.local_experts
 
         def compute(rows, local_ids):
             return _expert_fn(rows, local_ids + first_local)
 
-        out = reference_step(x, ids, w, compute, exchange)
+        if scenario == "raise_before" and rank == 1:
+            results[rank] = "raised before the exchange"
+            raise RuntimeError("injected host failure")
+        tamper = None
+        if scenario == "tamper" and rank == 1:
+            def tamper(send, recv):
+                return [send[0] + 1, send[1] - 1], recv
+        try:
+            out = reference_step(x, ids, w, compute, exchange, verify=scenario == "tamper", tamper=tamper)
+        except RuntimeError as error:
+            results[rank] = f"error: {error}"
+            return
         expected = _expected(x, ids, w)
         results[rank] = bool(torch.allclose(out, expected, rtol=1e-5, atol=1e-5))
     finally:
-        dist.destroy_process_group()
+        try:
+            dist.destroy_process_group()
+        except Exception:  # the peer may be gone already
+            pass
+
+
+def _run_ranks(scenario: str, world: int = 2, limit_s: float = 120.0):
+    manager = mp.Manager()
+    results = manager.dict()
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_worker, args=(rank, world, port, scenario, results)) for rank in range(world)]
+    for proc in procs:
+        proc.start()
+    for proc in procs:
+        proc.join(limit_s)
+    hung = [proc.pid for proc in procs if proc.is_alive()]
+    for proc in procs:
+        if proc.is_alive():
+            proc.kill()
+    assert not hung, f"ranks still running after {limit_s} s: a failure turned into a hang"
+    return dict(results)
 
 
 def test_two_rank_exchange_matches_single_process():
-    world = 2
-    manager = mp.Manager()
-    results = manager.dict()
-    mp.spawn(_worker, args=(world, _free_port(), -1, results), nprocs=world, join=True)
-    assert dict(results) == {0: True, 1: True}
+    assert _run_ranks("ok") == {0: True, 1: True}
+
+
+def test_rank_with_zero_tokens():
+    """A rank with an empty batch still takes part in every exchange and computes the rows the
+    other rank routes to its experts."""
+    assert _run_ranks("empty") == {0: True, 1: True}
+
+
+def test_mismatched_split_sizes_are_refused_on_every_rank():
+    results = _run_ranks("tamper")
+    assert set(results) == {0, 1}
+    for rank in (0, 1):
+        assert isinstance(results[rank], str) and "split sizes disagree" in results[rank], results
+
+
+def test_rank_that_raises_before_the_exchange_does_not_hang_the_others():
+    results = _run_ranks("raise_before")
+    assert results[1] == "raised before the exchange"
+    assert isinstance(results[0], str) and results[0].startswith("error:"), results
 
 
 def test_split_helpers():

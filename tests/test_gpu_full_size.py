@@ -8,8 +8,6 @@ permutation consistent with the routing.  Small cases of the same code are compa
 oracle in the other test files.
 """
 
-import os
-
 import pytest
 import torch
 
@@ -38,18 +36,16 @@ def _layer(hidden, inter, experts, k, tokens, activation="swiglu", clamp=None, s
 
 
 def _with_tiles(plan, tile_m, tile_n, fn):
-    saved = {k: os.environ.get(k) for k in ("NVFP4MOE_TILE_M", "NVFP4MOE_TILE_N")}
-    os.environ["NVFP4MOE_TILE_M"], os.environ["NVFP4MOE_TILE_N"] = str(tile_m), str(tile_n)
+    """Run ``fn`` with every GEMM of the plan forced to one tiling."""
+    plan.tile_override = (tile_m, tile_n)
+    plan._full_executions.clear()
+    plan._routed_gemms.clear()
     try:
-        plan._full_executions.clear()
         return fn()
     finally:
-        for key, value in saved.items():
-            if value is None:
-                os.environ.pop(key, None)
-            else:
-                os.environ[key] = value
+        plan.tile_override = None
         plan._full_executions.clear()
+        plan._routed_gemms.clear()
 
 
 def test_c2_full_size_properties():

@@ -500,6 +500,47 @@ def test_fused_decode_prepare_matches_oracle(tokens, experts, k, features):
     assert torch.equal(O.sf_from_varlen(sf.cpu(), ref[1], features // 16), sf_ref)
 
 
+@pytest.mark.parametrize(("tokens", "experts", "k", "features"),
+                         ((333, 64, 4, 2048), (1500, 256, 8, 2048), (96, 32, 6, 6144), (2048, 128, 4, 6144)))
+def test_quantize_once_scatter_matches_oracle_bytes(tokens, experts, k, features):
+    """The quantizer of the prefill step (and of decode steps beyond 1024 routes): each token
+    is quantized once and its bytes are stored to every expert-major row it was routed to.
+    Byte for byte the result must be the row quantizer applied to the gathered rows, as the
+    reference pins it (tests/test_training_gpu.py:231-263); routes whose slot is -1 are
+    dropped and leave their destination bytes untouched."""
+    from nvfp4moe_b200.kernels.quantize import nvfp4_quantize_decode
+
+    ids, w = _route(tokens, experts, k, "hot", features + tokens)
+    g = torch.Generator().manual_seed(tokens + experts)
+    x = torch.randn(tokens, features, generator=g).to(torch.bfloat16)
+    x[1, :32] = 0
+    x[2, 16:48] *= 1e-6
+    rows = tokens * k
+    gather, cu, _, slots, off, _ = O.dispatch(ids, w, experts)
+    pts = O.tensor_scale(x)
+    q_ref, sf_ref = O.quantize_rows(x[gather.long()], pts, te_math=True)
+    tiles = -(-rows // 128) + experts
+    # drop every 7th route: its row keeps the fill pattern
+    dropped = slots.clone()
+    dropped[::7] = -1
+    lost_rows = slots[::7].long()
+    dev = "cuda"
+    pair = torch.cat((pts, 1.0 / pts)).to(dev)
+    for slot_table, lost in ((slots, None), (dropped, lost_rows)):
+        q = torch.full((rows, features // 2), 0xA5, dtype=torch.uint8, device=dev)
+        sf = torch.full((1, tiles, features // 64, 32, 4, 4), 0x7F, dtype=torch.uint8, device=dev)
+        nvfp4_quantize_decode(x.to(dev), ids.to(dev), slot_table.to(dev), cu.to(dev), off.to(dev), pair,
+                              q, sf.view(torch.float8_e4m3fn))
+        torch.cuda.synchronize()
+        q_want = q_ref.clone()
+        sf_want = sf_ref.clone()
+        if lost is not None:
+            q_want[lost] = 0xA5
+            sf_want[lost] = 0x7F
+        assert torch.equal(q.cpu(), q_want)
+        assert torch.equal(O.sf_from_varlen(sf.cpu(), cu, features // 16), sf_want)
+
+
 # --------------------------------------------------------------------------
 # router step: softmax -> top-k -> renormalise
 # --------------------------------------------------------------------------

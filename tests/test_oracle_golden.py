@@ -155,3 +155,25 @@ def test_layer_tracks_bf16_reference():
     ref = O.bf16_layer(x, ids, w, gate, up, down)
     assert O.cosine(out, ref) > 0.95  # tests/test_inference.py:166-170
     assert np.isfinite(out.float().numpy()).all()
+
+
+def test_sampled_layer_oracle_equals_whole_batch_oracle():
+    """``moe_layer_sampled`` (used by the full-size GPU tests) computes the same rows as
+    ``moe_layer`` run on the whole batch."""
+    tokens, hidden, inter, experts, k = 40, 128, 64, 6, 3
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16)
+    gate = (torch.randn(experts, inter, hidden, generator=g) * 0.09).to(torch.bfloat16)
+    up = (torch.randn(experts, inter, hidden, generator=g) * 0.09).to(torch.bfloat16)
+    down = (torch.randn(experts, hidden, inter, generator=g) * 0.12).to(torch.bfloat16)
+    ids, w = O.route_topk(torch.randn(tokens, experts, generator=g), k)
+    w1 = O.pack_weights(O.interleave_gate_up(gate, up))
+    w2 = O.pack_weights(down)
+    xs, hs = O.calibrate(x, ids, w, *w1, "swiglu_oai", 7.0, 1.702, 1.0)
+    full = O.moe_layer(x, ids, w, *w1, *w2, xs, hs, "swiglu_oai", 7.0, 1.702, 1.0)
+    sample = torch.tensor([0, 7, 8, 23, 39])
+    table = {e: (w1[0][e], w1[1][e], w2[0][e], w2[1][e]) for e in ids[sample].unique().tolist()}
+    part = O.moe_layer_sampled(x[sample], ids[sample], w[sample], table, w1[2], w2[2], xs, hs,
+                               "swiglu_oai", 7.0, 1.702, 1.0)
+    # same arithmetic on the same values; only the row count of the FP32 matmuls differs
+    assert O.rel_frobenius(part.float(), full[sample].float()) < 1e-3

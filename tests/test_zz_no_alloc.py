@@ -59,6 +59,12 @@ def _both(tokens, experts, k, seed, plan_tile_rows=128):
     for name in ("gather", "m_indptr", "probs", "slots", "padded"):
         assert torch.equal(a[name], b[name]), (name, tokens, experts, k)
     assert int(a["m_indptr"][-1]) == rows
+    # and directly against the CPU oracle's stable sort
+    from oracle import nvfp4_oracle as O
+
+    want = O.dispatch(ids.cpu(), w.cpu(), experts, plan_tile_rows if rows <= 1024 else 128)
+    for name, ref in zip(("gather", "m_indptr", "probs", "slots", "padded"), want):
+        assert torch.equal(b[name].cpu(), ref), (name, tokens, experts, k)
     if rows <= 1024:
         assert torch.equal(a["scratch"], b["scratch"])  # the decode plan
 
@@ -68,6 +74,44 @@ def test_static_dispatch_matches_regular_dispatch_twice_in_a_row():
     _both(700, 64, 4, seed=2)              # fewer chunks, other expert count: stale counts around
     _both(64, 128, 8, seed=3, plan_tile_rows=8)   # single-block path with a decode plan
     _both(16384, 8, 8, seed=4)             # the stated maximum: 131072 assignments
+
+
+def test_static_dispatch_replays_inside_a_cuda_graph():
+    """The documented order of use: one plain call first (it looks up the array's device
+    address), then a capture of a second call, then replays of the graph on new routing."""
+    from nvfp4moe_b200 import _lib
+
+    lib = _lib.lib()
+    tokens, experts, k = 2048, 64, 4
+    rows = tokens * k
+    n = int(lib.lm_dispatch_scratch_elems(rows, experts))
+    _both(tokens, experts, k, seed=5)  # the first call on this device, outside any capture
+    ids, w = _route(tokens, experts, k, 6)
+    got = _buffers(rows, experts, 1)
+
+    def call():
+        _lib.check(lib.lm_dispatch_static(ids.data_ptr(), w.data_ptr(), tokens, k, experts,
+                                          got["gather"].data_ptr(), got["m_indptr"].data_ptr(),
+                                          got["probs"].data_ptr(), got["slots"].data_ptr(),
+                                          got["padded"].data_ptr(), None, 0, 128, _lib.stream_handle()))
+
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        call()
+    for seed in (7, 8):
+        new_ids, new_w = _route(tokens, experts, k, seed)
+        ids.copy_(new_ids)
+        w.copy_(new_w)
+        graph.replay()
+        ref = _buffers(rows, experts, n)
+        _lib.check(lib.lm_dispatch(ids.data_ptr(), w.data_ptr(), tokens, k, experts,
+                                   ref["gather"].data_ptr(), ref["m_indptr"].data_ptr(),
+                                   ref["probs"].data_ptr(), ref["slots"].data_ptr(),
+                                   ref["padded"].data_ptr(), ref["scratch"].data_ptr(), n, 128,
+                                   _lib.stream_handle()))
+        torch.cuda.synchronize()
+        for name in ("gather", "m_indptr", "probs", "slots", "padded"):
+            assert torch.equal(got[name], ref[name]), (name, seed)
 
 
 def test_static_dispatch_rejects_sizes_beyond_its_scratch():
