@@ -63,6 +63,10 @@ const char* lm_last_error_string(void);
 /* Number of SMs of the current device (used to size persistent grids). */
 int lm_sm_count(int* out);
 
+/* Kernel launches this process has made through the library so far (launches recorded into a
+   CUDA graph count once, at capture).  For benchmarks that report how many kernels a step is. */
+unsigned long long lm_launch_count(void);
+
 /*
  * Device-side status word.  A kernel whose bounded wait ran out sets a bit here and returns
  * instead of hanging: bits 0-2 the GEMM's producer / MMA / epilogue roles (bit 3 unused),
@@ -228,6 +232,26 @@ typedef struct lm_gemm_args {
   const uint64_t* out_row_ptrs; /* BF16 output, optional: device table (rows) of 16-byte aligned
                                    addresses, row i is written there instead of out + i*n; the
                                    addresses may point into a peer GPU's memory */
+  /* Decode-shaped kernel (swap_ab of lightmoe/kernels/grouped/runtime.py:181-203, kernel
+     lightmoe/kernels/grouped/kernel.py:155-221): the expert's weights take the 128-row side of
+     the MMA and its few token rows the 8..64-column side; tile_m / tile_n are ignored, the
+     result is bit-identical to the other tilings.  For steps with a handful of rows per expert. */
+  int32_t swap_ab;
+  /* swap_ab only (direct_routes / broadcast_a of the same constructor,
+     lightmoe/inference.py:656-721): > 0 = the routes of ONE token without a dispatch.
+     m_indptr then holds `direct_routes` expert ids; route r multiplies row r of a (row 0 with
+     broadcast_a) -- its scale factors in atom row r (0), row 0 -- with expert m_indptr[r] and
+     writes row r of out (NVFP4 output: scale factors in atom row r, row 0).  rows must equal
+     direct_routes (<= 32).  An id outside [0, experts) computes nothing. */
+  int32_t direct_routes;
+  int32_t broadcast_a;
+  /* Launch as a programmatic dependent of the previous kernel in the stream (use_pdl of the
+     reference's constructor).  swap_ab only; other kernels ignore it. */
+  int32_t use_pdl;
+  /* use_pdl only: start the weight stream before waiting for the previous kernel.  Allowed
+     when m_indptr, b, sfb and alpha were complete before the previous kernel began and that
+     kernel is itself a swap_ab launch of this library (the second projection of a layer). */
+  int32_t weights_ahead;
 } lm_gemm_args;
 
 /* Caller-provided storage for a prepared GEMM (tensor maps + arguments). */

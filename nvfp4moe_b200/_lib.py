@@ -51,6 +51,11 @@ class GemmArgs(ctypes.Structure):
         ("out_sf", c_ptr),
         ("out_scale", c_ptr),
         ("out_row_ptrs", c_ptr),
+        ("swap_ab", c_i32),
+        ("direct_routes", c_i32),
+        ("broadcast_a", c_i32),
+        ("use_pdl", c_i32),
+        ("weights_ahead", c_i32),
     ]
 
 
@@ -62,6 +67,7 @@ _SIGNATURES = {
     "lm_version": (c_i32, []),
     "lm_last_error_string": (ctypes.c_char_p, []),
     "lm_sm_count": (c_i32, [ctypes.POINTER(c_i32)]),
+    "lm_launch_count": (ctypes.c_uint64, []),
     "lm_device_status": (c_i32, [ctypes.POINTER(ctypes.c_uint32), c_ptr]),
     "lm_device_status_clear": (c_i32, [c_ptr]),
     "lm_quantize_rowwise": (
@@ -166,3 +172,8 @@ def device_status() -> int:
 
 def device_status_clear() -> None:
     check(lib().lm_device_status_clear(stream_handle()))
+
+
+def launch_count() -> int:
+    """Kernel launches made through the library so far in this process."""
+    return int(lib().lm_launch_count())

@@ -194,7 +194,12 @@ def run(name: str) -> dict:
     ex = plan._full_execution(tokens, decode=decode)
     n1 = inter if unary else 2 * inter
     for label, gemm, n, kk in (("fc1", ex.fc1, n1, hidden), ("fc2", ex.fc2, hidden, inter)):
-        stats = _timed(gemm.launch)
+        # one launch per graph: a replay costs the host a few microseconds, a launch through the
+        # Python binding 10-20, which would bound the samples of kernels shorter than that
+        single = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(single):
+            gemm.launch()
+        stats = _timed(single.replay)
         stats["tflops"] = round(2.0 * rows * n * kk / (stats["median_us"] * 1e-6) / 1e12, 1)
         stats["pct_of_9000"] = round(stats["tflops"] / 90.0, 1)
         result[label] = stats

@@ -1,11 +1,16 @@
 // Error reporting and device queries shared by every entry point.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace lm {
 
 namespace {
 thread_local char g_error[512] = "";
+std::atomic<unsigned long long> g_launches{0};
 }
+
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int set_error(int code, const char* fmt, ...) {
   va_list args;
@@ -39,3 +44,5 @@ extern "C" int lm_sm_count(int* out) {
   if (*out <= 0) return lm::set_error(LM_ERR_CUDA, "no CUDA device");
   return LM_OK;
 }
+
+extern "C" unsigned long long lm_launch_count(void) { return lm::g_launches.load(std::memory_order_relaxed); }

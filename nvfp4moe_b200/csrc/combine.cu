@@ -104,8 +104,10 @@ extern "C" int lm_finalize(const void* routed_out, const int32_t* slots, const f
   dim3 grid(static_cast<unsigned>(tokens), (p.vec_per_row + kThreads - 1) / kThreads);
   if (weights != nullptr) {
     combine_kernel<true><<<grid, kThreads, 0, as_stream(stream)>>>(p);
+    note_launch();
   } else {
     combine_kernel<false><<<grid, kThreads, 0, as_stream(stream)>>>(p);
+    note_launch();
   }
   LM_CUDA(cudaGetLastError());
   return LM_OK;

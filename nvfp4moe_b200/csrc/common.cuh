@@ -32,6 +32,8 @@ int set_error(int code, const char* fmt, ...);
 inline cudaStream_t as_stream(lm_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
 int sm_count();
+// Counts one kernel launch of this library (lm_launch_count reports the total).
+void note_launch();
 // status word of the expert-parallel kernels (expert_parallel.cu)
 int ep_status_read(uint32_t* out);
 int ep_status_clear();

@@ -313,11 +313,14 @@ extern "C" int lm_dispatch(const int32_t* topk_ids, const float* topk_weights, i
     int64_t plan_need = 1 + (rows + plan_tile_rows - 1) / plan_tile_rows + experts + experts;
     LM_REQUIRE(scratch_elems >= plan_need, "dispatch: scratch too small for the decode plan");
     dispatch_scatter_kernel<true><<<1, kThreads, smem, s>>>(p);
+    note_launch();
   } else {
     LM_REQUIRE(scratch_elems >= static_cast<int64_t>(chunks) * experts, "dispatch: scratch too small");
     dispatch_count_kernel<<<chunks, kThreads, 0, s>>>(p);
+    note_launch();
     LM_CUDA(cudaGetLastError());
     dispatch_scatter_kernel<false><<<chunks, kThreads, smem, s>>>(p);
+    note_launch();
   }
   LM_CUDA(cudaGetLastError());
   return LM_OK;
@@ -360,10 +363,13 @@ extern "C" int lm_dispatch_static(const int32_t* topk_ids, const float* topk_wei
       p.scratch_elems = plan_elems;
     }
     dispatch_scatter_kernel<true><<<1, kThreads, smem, s>>>(p);
+    note_launch();
   } else {
     dispatch_count_kernel<<<chunks, kThreads, 0, s>>>(p);
+    note_launch();
     LM_CUDA(cudaGetLastError());
     dispatch_scatter_kernel<false><<<chunks, kThreads, smem, s>>>(p);
+    note_launch();
   }
   LM_CUDA(cudaGetLastError());
   return LM_OK;
@@ -401,6 +407,7 @@ extern "C" int lm_dispatch_quantize_decode(const void* x, const int32_t* topk_id
   const size_t smem = sizeof(int) * (static_cast<size_t>(kSegments) * experts + 2 * kChunk);
   dim3 grid(static_cast<unsigned>((tokens + kThreads / 32 - 1) / (kThreads / 32)), (features + 511) / 512);
   dispatch_quantize_decode_kernel<<<grid, kThreads, smem, as_stream(stream)>>>(p);
+  note_launch();
   LM_CUDA(cudaGetLastError());
   return LM_OK;
 }

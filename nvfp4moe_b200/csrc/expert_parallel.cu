@@ -372,6 +372,7 @@ extern "C" int lm_ep_plan(const int32_t* counts_all, int world, int rank, int ex
   p.valid = valid;
   const int segments = p.local_experts * world;
   ep_plan_kernel<<<segments < 296 ? segments : 296, kPlanThreads, 0, as_stream(stream)>>>(p);
+  note_launch();
   LM_CUDA(cudaGetLastError());
   return LM_OK;
 }
@@ -412,6 +413,7 @@ extern "C" int lm_ep_quantize_send(const void* x, int64_t tokens, int features, 
   }
   dim3 grid(static_cast<unsigned>((tokens + kWarps - 1) / kWarps));
   ep_quantize_send_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(p);
+  note_launch();
   LM_CUDA(cudaGetLastError());
   return LM_OK;
 }
@@ -430,6 +432,7 @@ extern "C" int lm_ep_sf_swizzle(const uint8_t* linear, int64_t max_rows, int fea
   const int64_t atom_rows = (max_rows + kTileRows - 1) / kTileRows + experts;
   dim3 grid(static_cast<unsigned>(atom_rows), (features / 16 + kSwizzleCols - 1) / kSwizzleCols);
   ep_sf_swizzle_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(p);
+  note_launch();
   LM_CUDA(cudaGetLastError());
   return LM_OK;
 }
@@ -458,6 +461,7 @@ extern "C" int lm_ep_signal(const int32_t* m_indptr, int experts, int world, int
     }
   }
   ep_signal_kernel<<<1, 256, 0, as_stream(stream)>>>(p);
+  note_launch();
   LM_CUDA(cudaGetLastError());
   return LM_OK;
 }

@@ -346,15 +346,16 @@ __device__ __forceinline__ Unit decode_unit(const GemmParams& p, int unit) {
 
 // ------------------------------------------------------------- activations
 template <int kAct>
-__device__ __forceinline__ float gated_value(float g, float u, const GemmParams& p) {
-  if (p.clamp_limit > 0.0f) {
-    g = fminf(g, p.clamp_limit);
-    u = fmaxf(fminf(u, p.clamp_limit), -p.clamp_limit);
+__device__ __forceinline__ float gated_value(float g, float u, float clamp_limit, float sigmoid_alpha,
+                                             float up_bias) {
+  if (clamp_limit > 0.0f) {
+    g = fminf(g, clamp_limit);
+    u = fmaxf(fminf(u, clamp_limit), -clamp_limit);
   }
   if (kAct == LM_ACT_SWIGLU || kAct == LM_ACT_SWIGLU_OAI) {
     float sig;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(sig) : "f"(1.0f + __expf(-p.sigmoid_alpha * g)));
-    return g * sig * (u + p.up_bias);
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(sig) : "f"(1.0f + __expf(-sigmoid_alpha * g)));
+    return g * sig * (u + up_bias);
   }
   if (kAct == LM_ACT_GEGLU) {
     const float root = 0.7978845608028654f;  // sqrt(2/pi)
@@ -464,8 +465,8 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
         float h[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i)
-          h[i] = gated_value<kAct>(__uint_as_float(v[2 * i]) * alpha,
-                                   __uint_as_float(v[2 * i + 1]) * alpha, p);
+          h[i] = gated_value<kAct>(__uint_as_float(v[2 * i]) * alpha, __uint_as_float(v[2 * i + 1]) * alpha,
+                                   p.clamp_limit, p.sigmoid_alpha, p.up_bias);
         const uint32_t sf = requant16(h, inv_h, &q[2 * half]);
         sfw = half == 0 ? sf : (sfw | (sf << 8));
       } else {
@@ -829,19 +830,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             // before its MMA; copies and MMAs of one thread run in issue order, so a TMEM slot
             // is never overwritten while an earlier MMA still reads it.
             // 64 FP4 values = 32 bytes along K: +2 in 16-byte descriptor units
-            auto chunk = [&](int c) {
+            auto copies = [&](int c) {
               tc_copy_sf(sfa_t + c * 4, sfa_desc + c * (512 >> 4));
 #pragma unroll
               for (int j = 0; j < kNB; ++j)
                 tc_copy_sf(sfb_t + (c * kNB + j) * 4, sfb_desc + j * (kSfBytes >> 4) + c * (512 >> 4));
+            };
+            auto mma = [&](int c) {
               tc_mma_nvf4(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 4 * kNB,
                           (ks > 0 || c > 0) ? 1u : 0u);
             };
             if (chunks == kChunksPerStage) {
 #pragma unroll
-              for (int c = 0; c < kChunksPerStage; ++c) chunk(c);
+              for (int c = 0; c < kChunksPerStage; ++c) { copies(c); mma(c); }
             } else {
-              for (int c = 0; c < chunks; ++c) chunk(c);
+              for (int c = 0; c < chunks; ++c) { copies(c); mma(c); }
             }
             tc_commit(smem_u32(&misc->empty[stage]));
             if (resident && nt == u.n_end - 1) tc_commit(smem_u32(&misc->a_empty[ks]));
@@ -1230,18 +1233,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (elect_one()) {
               // the atoms of a 64-element chunk go to TMEM right before its MMA; copies and MMAs
               // of one thread run in issue order, so a slot is never overwritten while in use
-              auto chunk = [&](int c) {
+              auto copies = [&](int c) {
                 tc_copy_sf_pair(sfa_t + c * 4, sfa_desc + c * (512 >> 4));
                 tc_copy_sf_pair(sfb_t + c * 8, sfb_desc + c * (512 >> 4));
                 tc_copy_sf_pair(sfb_t + c * 8 + 4, sfb_desc + (kSfBytes >> 4) + c * (512 >> 4));
+              };
+              auto mma = [&](int c) {
                 tc_mma_nvf4_pair(d_tmem, a_desc + 2 * c, b_desc + 2 * c, idesc, sfa_t + c * 4, sfb_t + c * 8,
                                  (ks > 0 || c > 0) ? 1u : 0u);
               };
               if (chunks == kChunksPerStage) {
 #pragma unroll
-                for (int c = 0; c < kChunksPerStage; ++c) chunk(c);
+                for (int c = 0; c < kChunksPerStage; ++c) { copies(c); mma(c); }
               } else {
-                for (int c = 0; c < chunks; ++c) chunk(c);
+                for (int c = 0; c < chunks; ++c) { copies(c); mma(c); }
               }
               tc_commit_pair(smem_u32(&misc->empty[stage]));
             }
@@ -1324,6 +1329,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                  : "memory");
   }
 }
+
+#include "gemm_decode.cuh"
 
 // --------------------------------------------------------------- host side
 struct PlanData {
@@ -1409,6 +1416,130 @@ int encode_sf(CUtensorMap* map, const void* base, uint64_t atom_cols, uint64_t a
   return LM_OK;
 }
 
+// ---- decode-shaped plans
+struct DecodePlanData {
+  uint32_t magic;
+  int32_t out_kind;
+  int32_t activation;
+  int32_t grid;
+  int32_t use_pdl;
+  DecodeParams params;
+  alignas(64) CUtensorMap map_w;    // weights, 128-row boxes
+  alignas(64) CUtensorMap map_w64;  // weights, 64-row boxes (half blocks)
+  alignas(64) CUtensorMap map_w32;  // weights, 32-row boxes (quarter blocks)
+  alignas(64) CUtensorMap map_t8;   // token rows, boxes of 8 / 16 / 32 / 64
+  alignas(64) CUtensorMap map_t16;
+  alignas(64) CUtensorMap map_t32;
+  alignas(64) CUtensorMap map_t64;
+};
+static_assert(sizeof(DecodePlanData) <= sizeof(lm_gemm_plan), "plan storage too small");
+constexpr uint32_t kDecodePlanMagic = 0x4C4D4444u;
+
+constexpr int dec_smem_bytes(int ring_stages, int stage_bytes) { return 1024 + ring_stages * stage_bytes + kMiscBytes; }
+
+template <int kOut, int kAct>
+int launch_decode(const DecodePlanData& pd, cudaStream_t stream) {
+  auto kernel = gemm_decode_kernel<kOut, kAct>;
+  static bool configured[kMaxDevices] = {};
+  int device = 0;
+  LM_CUDA(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices || !configured[device]) {
+    LM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    if (device >= 0 && device < kMaxDevices) configured[device] = true;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(pd.grid);
+  config.blockDim = dim3(kDecThreads);
+  config.dynamicSmemBytes = dec_smem_bytes(pd.params.ring_stages, pd.params.stage_bytes);
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = pd.use_pdl ? 1 : 0;
+  LM_CUDA(cudaLaunchKernelEx(&config, kernel, pd.map_w, pd.map_w64, pd.map_w32, pd.map_t8, pd.map_t16, pd.map_t32, pd.map_t64,
+                             pd.params));
+  note_launch();
+  return LM_OK;
+}
+
+int launch_decode_plan(const DecodePlanData& pd, cudaStream_t stream) {
+  if (pd.out_kind == LM_OUT_BF16) return launch_decode<LM_OUT_BF16, LM_ACT_NONE>(pd, stream);
+  if (pd.out_kind == LM_OUT_F32) return launch_decode<LM_OUT_F32, LM_ACT_NONE>(pd, stream);
+  switch (pd.activation) {
+    case LM_ACT_SWIGLU: return launch_decode<LM_OUT_NVFP4, LM_ACT_SWIGLU>(pd, stream);
+    case LM_ACT_SWIGLU_OAI: return launch_decode<LM_OUT_NVFP4, LM_ACT_SWIGLU_OAI>(pd, stream);
+    case LM_ACT_GEGLU: return launch_decode<LM_OUT_NVFP4, LM_ACT_GEGLU>(pd, stream);
+    case LM_ACT_REGLU: return launch_decode<LM_OUT_NVFP4, LM_ACT_REGLU>(pd, stream);
+    case LM_ACT_RELU2: return launch_decode<LM_OUT_NVFP4, LM_ACT_RELU2>(pd, stream);
+  }
+  return set_error(LM_ERR_INVALID, "gemm: unknown activation");
+}
+
+// Plan of the decode-shaped kernel.  Common argument checks were made by the caller.
+int prepare_decode(const lm_gemm_args* a, int out_atom_cols, lm_gemm_plan* plan) {
+  LM_REQUIRE(!a->dense, "gemm: swap_ab serves grouped GEMMs");
+  LM_REQUIRE(a->direct_routes >= 0 && a->direct_routes <= 32, "gemm: direct route count must be between 0 and 32");
+  LM_REQUIRE(a->direct_routes == 0 || a->rows == a->direct_routes, "gemm: direct routes have one row each");
+  LM_REQUIRE(!a->broadcast_a || a->direct_routes > 0, "gemm: broadcast A requires direct routing");
+  LM_REQUIRE(!a->weights_ahead || a->use_pdl, "gemm: weights_ahead requires use_pdl");
+  DecodePlanData pd{};
+  pd.magic = kDecodePlanMagic;
+  pd.out_kind = a->out_kind;
+  pd.activation = a->activation;
+  pd.use_pdl = a->use_pdl ? 1 : 0;
+  DecodeParams& p = pd.params;
+  p.experts = a->experts;
+  p.direct = a->direct_routes > 0 ? 1 : 0;
+  p.groups = p.direct ? a->direct_routes : a->experts;
+  p.broadcast = a->broadcast_a ? 1 : 0;
+  p.prefetch = a->weights_ahead ? 1 : 0;
+  p.n = a->n;
+  p.n_blocks = (a->n + kTileM - 1) / kTileM;
+  p.atom_cols = a->k / 64;
+  p.k_stages = (p.atom_cols + kChunksPerStage - 1) / kChunksPerStage;
+  p.alpha_per_expert = a->alpha_per_expert;
+  // no expert can hold more than `rows` rows: steps of up to 32 rows keep the deeper ring
+  p.cap = a->rows <= 32 ? 32 : 64;
+  p.stage_bytes = kTileBytes + p.cap * kStageKBytes + 2 * kSfBytes;
+  p.ring_stages = (kSmemLimit - 1024 - kMiscBytes) / p.stage_bytes;
+  if (p.ring_stages > 16) p.ring_stages = 16;
+  p.rows = a->rows;
+  p.m_indptr = a->m_indptr;
+  p.sft = static_cast<const uint8_t*>(a->sfa);
+  p.sfw = static_cast<const uint8_t*>(a->sfb);
+  p.alpha = a->alpha;
+  p.out = a->out;
+  p.out_sf = static_cast<uint8_t*>(a->out_sf);
+  p.out_scale = a->out_scale;
+  p.out_row_ptrs = a->out_row_ptrs;
+  p.out_atom_cols = out_atom_cols;
+  p.clamp_limit = a->clamp_limit;
+  p.sigmoid_alpha = a->sigmoid_alpha;
+  p.up_bias = a->up_bias;
+  const int sms = sm_count();
+  LM_REQUIRE(sms > 0, "gemm: no CUDA device");
+  pd.grid = a->max_ctas > 0 ? a->max_ctas : sms;
+  // quarter blocks bound the CTAs that can have work: (rows / cap + groups) row tiles at most
+  const int64_t max_quarters = (a->rows / p.cap + p.groups) * static_cast<int64_t>(p.n_blocks) * 4;
+  if (pd.grid > max_quarters) pd.grid = static_cast<int>(max_quarters);
+  const uint64_t k_bytes = static_cast<uint64_t>(a->k / 2);
+  const uint64_t w_rows = static_cast<uint64_t>(a->experts) * a->n;
+  int rc = encode_bytes_2d(&pd.map_w, a->b, k_bytes, w_rows, kTileM);
+  if (rc != LM_OK) return rc;
+  rc = encode_bytes_2d(&pd.map_w64, a->b, k_bytes, w_rows, 64);
+  if (rc != LM_OK) return rc;
+  rc = encode_bytes_2d(&pd.map_w32, a->b, k_bytes, w_rows, 32);
+  if (rc != LM_OK) return rc;
+  CUtensorMap* token_maps[4] = {&pd.map_t8, &pd.map_t16, &pd.map_t32, &pd.map_t64};
+  for (int i = 0; i < 4; ++i) {
+    rc = encode_bytes_2d(token_maps[i], a->a, k_bytes, static_cast<uint64_t>(a->rows), 8u << i);
+    if (rc != LM_OK) return rc;
+  }
+  memcpy(plan, &pd, sizeof(pd));
+  return LM_OK;
+}
+
 template <int kOut, int kAct, int kNB>
 int launch_kernel(const PlanData& pd, cudaStream_t stream) {
   auto kernel = gemm_kernel<kOut, kAct, kNB>;
@@ -1422,6 +1553,7 @@ int launch_kernel(const PlanData& pd, cudaStream_t stream) {
   }
   kernel<<<pd.grid, kThreads, smem_bytes(kOut), stream>>>(pd.map_a, pd.map_a64, pd.map_a32, pd.map_b,
                                                           pd.map_out, pd.params);
+  note_launch();
   LM_CUDA(cudaGetLastError());
   return LM_OK;
 }
@@ -1450,6 +1582,7 @@ int launch_pair(const PlanData& pd, cudaStream_t stream) {
   config.numAttrs = 1;
   LM_CUDA(cudaLaunchKernelEx(&config, kernel, pd.map_a, pd.map_a64, pd.map_a32, pd.map_b, pd.map_out,
                              pd.map_sfa, pd.map_sfb, pd.params));
+  note_launch();
   return LM_OK;
 }
 
@@ -1507,6 +1640,8 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
     LM_REQUIRE(a->activation == LM_ACT_NONE, "gemm: activations require NVFP4 output");
     LM_REQUIRE(a->n % 8 == 0, "gemm: N must be a multiple of 8");
   }
+  if (a->swap_ab) return prepare_decode(a, p.out_atom_cols, plan);
+  LM_REQUIRE(a->direct_routes == 0 && !a->broadcast_a, "gemm: direct routes require swap_ab");
   p.experts = a->experts;
   p.n = a->n;
   // 256-column tiles on request, when N splits into them evenly
@@ -1605,7 +1740,14 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
 extern "C" int lm_gemm_launch(const lm_gemm_plan* plan, lm_stream_t stream) {
   using namespace lm;
   LM_REQUIRE(plan, "gemm: null plan");
-  PlanData pd;  // the caller's storage need not be 64-byte aligned: work on a copy
+  uint32_t magic;
+  memcpy(&magic, plan, sizeof(magic));
+  if (magic == kDecodePlanMagic) {
+    DecodePlanData dp;  // the caller's storage need not be 64-byte aligned: work on a copy
+    memcpy(&dp, plan, sizeof(dp));
+    return launch_decode_plan(dp, as_stream(stream));
+  }
+  PlanData pd;
   memcpy(&pd, plan, sizeof(pd));
   LM_REQUIRE(pd.magic == kPlanMagic, "gemm: plan was not prepared");
   return launch_plan(pd, as_stream(stream));

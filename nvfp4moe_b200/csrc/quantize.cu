@@ -269,8 +269,10 @@ extern "C" int lm_quantize_rowwise(const void* x, int x_dtype, int64_t rows, int
   dim3 grid(static_cast<unsigned>(atom_rows), (features + kTileCols - 1) / kTileCols);
   if (x_dtype == LM_DTYPE_BF16) {
     quantize_rowwise_kernel<__nv_bfloat16><<<grid, kThreads, 0, as_stream(stream)>>>(p);
+    note_launch();
   } else {
     quantize_rowwise_kernel<float><<<grid, kThreads, 0, as_stream(stream)>>>(p);
+    note_launch();
   }
   LM_CUDA(cudaGetLastError());
   return LM_OK;
@@ -291,6 +293,7 @@ extern "C" int lm_quantize_decode(const void* x, int64_t tokens, int features, i
                        topk_ids, m_indptr, scale_pair, q, sf};
   dim3 grid(static_cast<unsigned>((tokens + kWarps - 1) / kWarps));
   quantize_scatter_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(p);
+  note_launch();
   LM_CUDA(cudaGetLastError());
   return LM_OK;
 }

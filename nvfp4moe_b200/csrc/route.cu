@@ -112,8 +112,10 @@ extern "C" int lm_route_topk(const void* logits, int logits_dtype, int64_t token
   const unsigned grid = static_cast<unsigned>((tokens + kWarps - 1) / kWarps);
   if (logits_dtype == LM_DTYPE_F32) {
     route_topk_kernel<float><<<grid, kThreads, 0, as_stream(stream)>>>(p);
+    note_launch();
   } else {
     route_topk_kernel<__nv_bfloat16><<<grid, kThreads, 0, as_stream(stream)>>>(p);
+    note_launch();
   }
   LM_CUDA(cudaGetLastError());
   return LM_OK;

@@ -314,7 +314,7 @@ class ExpertParallelMoE:
                                                peer["valid"].data_ptr(), plan._x_scale.data_ptr(),
                                                peer["q_base"], peer["sf_base"], stream))
 
-    def _phase_compute(self):
+    def _phase_compute(self, mark=None):
         from . import _lib
 
         fc1, fc2 = self._peer_gemms()
@@ -324,8 +324,14 @@ class ExpertParallelMoE:
                                                    self.hidden_size, plan._m_indptr.data_ptr(),
                                                    self.local_experts, peer["sfx"].data_ptr(),
                                                    _lib.stream_handle()))
+        if mark is not None:
+            mark("swizzle")
         fc1.launch()
+        if mark is not None:
+            mark("fc1")
         fc2.launch()
+        if mark is not None:
+            mark("fc2_and_return")
 
     def _phase_combine(self, out):
         from .kernels.routing.combine import moe_finalize
@@ -381,6 +387,44 @@ class ExpertParallelMoE:
         self._phase_compute()
         self._signal()  # all result rows have landed on their sources
         return self._phase_combine(out)
+
+    @torch.no_grad()
+    def run_phases(self, x, topk_ids, topk_weights, *, out=None):
+        """One peer-transport step with a CUDA event after every phase.  Returns
+        ``({phase: milliseconds}, output)``; the time a rank spends waiting for the others inside
+        a signal kernel counts towards the phase that the signal closes.  Synchronises the
+        stream (a measuring aid, not part of the serving path)."""
+        if self.transport != "peer" or self.virtual:
+            raise RuntimeError("run_phases times the peer transport of a real rank")
+        marks = [("start", torch.cuda.Event(enable_timing=True))]
+        marks[0][1].record()
+
+        def mark(name):
+            event = torch.cuda.Event(enable_timing=True)
+            event.record()
+            marks.append((name, event))
+
+        self._check_inputs(x, topk_ids, topk_weights)
+        if self.world == 1:
+            self._peer["counts_all"].copy_(self._phase_dispatch(topk_ids, topk_weights).view(1, -1))
+            mark("dispatch")
+        else:
+            _, m_indptr, _, _ = self.source(topk_ids, topk_weights)
+            mark("dispatch")
+            self._signal(m_indptr)
+            mark("exchange_counts")
+        self._phase_send(x)
+        mark("plan_quantize_send")
+        self._signal()
+        mark("fence_rows_landed")
+        self._phase_compute(mark)
+        self._signal()
+        mark("fence_results_landed")
+        output = self._phase_combine(out)
+        mark("combine")
+        torch.cuda.synchronize(self.device)
+        times = {name: marks[i][1].elapsed_time(event) for i, (name, event) in enumerate(marks[1:])}
+        return times, output
 
     def step_is_valid(self) -> bool:
         """False when the last step was skipped because a rank would have received more than

@@ -462,6 +462,10 @@ class InferenceMoE:
                 _row_tile(fc1_m, rows, self.experts, n1, self.hidden_size, decode,
                           output_dtype == torch.float4_e2m1fn_x2),
                 _tile_n(n1, self.hidden_size, decode))
+            if decode and self.tile_override is None:
+                # the decode-shaped kernel: weights on the 128-row side of the MMA
+                tile_m, tile_n = 128, _decode_tile_rows(rows // self.topk, self.hidden_size,
+                                                        self.intermediate_size, self.experts)
             return GroupedNvfp4Gemm(
                 self.experts,
                 n1,
@@ -472,12 +476,15 @@ class InferenceMoE:
                 epilogue=self._epilogue() if output_dtype == torch.float4_e2m1fn_x2 else None,
                 use_dynamic_sched=schedule,
                 use_pdl=True,
-                swap_ab=False,
+                swap_ab=decode and self.tile_override is None,
                 fast_decode_sched=(decode and not schedule and self.hidden_size >= 2048),
             )
         tile_m, tile_n = self.tile_override or (
             _row_tile(fc2_m, rows, self.experts, self.hidden_size, self.intermediate_size, decode, False),
             _tile_n(self.hidden_size, self.intermediate_size, decode))
+        if decode and self.tile_override is None:
+            tile_m, tile_n = 128, _decode_tile_rows(rows // self.topk, self.hidden_size,
+                                                    self.intermediate_size, self.experts)
         return GroupedNvfp4Gemm(
             self.experts,
             self.hidden_size,
@@ -486,6 +493,7 @@ class InferenceMoE:
             tile_n,
             use_dynamic_sched=schedule,
             use_pdl=True,
+            swap_ab=decode and self.tile_override is None,
         )
 
     def _full_execution(self, tokens: int, *, decode: bool) -> _FullExecution:
@@ -501,6 +509,9 @@ class InferenceMoE:
             if decode:
                 fc1.fast_decode_sched = not fc1.use_dynamic_sched
             fc2 = self._new_gemm("fc2", rows, decode=decode)
+            # fc2 follows fc1 directly and its routing table is older than fc1: its weight
+            # stream may start while fc1 drains
+            fc2.weights_ahead = decode and fc2.swap_ab
         fc1.prepare(qx, self.qb1, qh, self._m_indptr, sfx, self.sfb1, self._alpha1,
                     output_sf=sfh, output_scale=self._h_scale)
         fc2.prepare(qh, self.qb2, routed_out, self._m_indptr, sfh, self.sfb2, self._alpha2)

@@ -23,11 +23,11 @@ DECODE_GRID_DOUBLE = 1
 
 
 def _resolve_dynamic_schedule(use_dynamic_sched: bool | None, k: int) -> bool:
-    """Scheduling policy flag of the reference (``runtime.py:22-25``).
+    """Scheduling policy flag of the reference (``runtime.py:22-25``): a performance hint.
 
-    This kernel's static round-robin tile walk gives every CTA the same number
-    of equally sized tiles, so the flag selects nothing here; it is kept
-    because callers read it back.
+    The kernels here deal their units statically (round-robin, or equal contiguous shares in
+    the decode-shaped kernel); the flag is resolved and kept because callers read it back and
+    because ``fast_decode_sched`` is validated against it.
     """
     if use_dynamic_sched is None:
         return k > 2048
@@ -54,7 +54,28 @@ def _out_kind(dtype: torch.dtype) -> int:
 
 
 class GroupedNvfp4Gemm:
-    """Grouped NVFP4 GEMM for contiguous expert-major assignments."""
+    """Grouped NVFP4 GEMM for contiguous expert-major assignments.
+
+    What the decode options of the reference's constructor select here:
+
+    ``swap_ab``            the decode-shaped kernel: the expert's weights take the 128-row side
+                           of the MMA and its few rows the 8..64-column side; ``tile_m`` /
+                           ``tile_n`` then only pass validation.  Results are bit-identical to
+                           the other tilings.
+    ``direct_routes``      (with or without ``swap_ab``) the routes of one token without a
+                           dispatch, on the same kernel: ``cu`` holds the expert id of each
+                           route, route r reads row r of A (row 0 with ``broadcast_a``) and
+                           writes row r of the output.
+    ``use_pdl``            the decode-shaped kernel launches as a programmatic dependent of the
+                           previous kernel; the prefill kernels launch normally (measured: no
+                           gain there).  ``weights_ahead`` (attribute, set before ``prepare``)
+                           lets it start its weight stream before the previous kernel ends.
+    ``fast_decode_sched``  a scheduling hint of the reference (tiles read from the dispatch
+                           plan); every kernel here derives its tiles from ``cu`` on the device,
+                           so the flag changes nothing and is only validated.
+    ``gather_b``           refused: the quantizers of this build write rows expert-major, there
+                           is no token-major buffer to gather from.
+    """
 
     def __init__(
         self,
@@ -143,20 +164,23 @@ class GroupedNvfp4Gemm:
             raise ValueError("fast decode scheduling requires a static GEMM")
         if self.direct_routes < 0 or self.direct_routes > 32:
             raise ValueError("direct route count must be between 0 and 32")
-        if self.direct_routes:
-            raise NotImplementedError("direct routing is not part of the inference plan")
-        if self.broadcast_a:
+        if self.broadcast_a and not self.direct_routes:
             raise ValueError("broadcast A requires direct routing")
         if self.gather_b and not (self.swap_ab and self.fast_decode_sched):
             raise ValueError("gather B requires swapped fast decode")
         if self.gather_b:
-            raise NotImplementedError("token-major gather is not part of this build's decode path")
+            raise NotImplementedError(
+                "gather_b: the quantizers of this build write rows expert-major, there is no "
+                "token-major buffer to gather from")
         self.output_n = n
         if gated:
             self.output_n = n // 2
         self.device = torch.cuda.current_device()
-        self.stages = 6
         self.max_ctas = 0  # 0 = one CTA per SM; tests lower it to run many tiles per CTA
+        # decode-shaped kernel with use_pdl: start the weight stream before the previous kernel
+        # in the stream has finished.  Only for a second projection that directly follows its
+        # first projection (cu, B, SFB and alpha are older than that kernel).
+        self.weights_ahead = False
         # Set before ``prepare``: int64 CUDA tensor with one 16-byte aligned address per row.
         # Every BF16 output row is then written to its own address (which may lie in a peer
         # GPU's memory) instead of ``out``; the expert-parallel layer returns rows to their
@@ -197,10 +221,11 @@ class GroupedNvfp4Gemm:
             raise ValueError(
                 f"output must use {self.output_dtype} with shape ({rows}, {output_cols})"
             )
-        if cu.dtype != torch.int32 or tuple(cu.shape) != (self.experts + 1,):
-            raise ValueError(
-                f"routing metadata must be contiguous int32 with shape {(self.experts + 1,)}"
-            )
+        cu_shape = (self.direct_routes,) if self.direct_routes else (self.experts + 1,)
+        if cu.dtype != torch.int32 or tuple(cu.shape) != cu_shape:
+            raise ValueError(f"routing metadata must be contiguous int32 with shape {cu_shape}")
+        if self.direct_routes and rows != self.direct_routes:
+            raise ValueError("direct routing takes one row per route")
         expected_sfa = (1, -(-rows // 128) + self.experts, self.k // 64, 32, 4, 4)
         expected_sfb = (self.experts, -(-self.n // 128), self.k // 64, 32, 4, 4)
         if sfa.dtype != torch.float8_e4m3fn or tuple(sfa.shape) != expected_sfa:
@@ -265,6 +290,12 @@ class GroupedNvfp4Gemm:
                     or not output_row_ptrs.is_contiguous()):
                 raise ValueError(f"output_row_ptrs must be a contiguous int64 CUDA tensor of {rows} addresses")
             args.out_row_ptrs = output_row_ptrs.data_ptr()
+        decode_shaped = self.swap_ab or self.direct_routes > 0
+        args.swap_ab = int(decode_shaped)
+        args.direct_routes = self.direct_routes
+        args.broadcast_a = int(self.broadcast_a)
+        args.use_pdl = int(self.use_pdl and decode_shaped)
+        args.weights_ahead = int(self.weights_ahead and self.use_pdl and decode_shaped)
         plan = _lib.GemmPlan()
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().lm_gemm_prepare(ctypes.byref(args), ctypes.byref(plan)))

@@ -458,6 +458,156 @@ def test_fused_epilogue_matches_oracle(activation, clamp, tile_m, tile_n):
 
 
 # --------------------------------------------------------------------------
+# decode-shaped GEMM: weights on the 128-row side of the MMA (swap_ab), direct routes
+# --------------------------------------------------------------------------
+
+
+def _run_swapped(cu, packed, n, k, out_dtype=torch.bfloat16, max_ctas=0, use_pdl=False):
+    from nvfp4moe_b200 import gemm
+
+    qa, qb, sfa, sfb, alpha = packed
+    out = torch.full((qa.shape[0], n), float("nan"), dtype=out_dtype, device="cuda")
+    plan = gemm.GroupedGemm(qb.shape[0], n, k, 128, 32, output_dtype=out_dtype, swap_ab=True,
+                            use_pdl=use_pdl)
+    plan.max_ctas = max_ctas
+    plan(qa, qb, out, cu.cuda(), sfa, sfb, alpha)
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("out_dtype", (torch.bfloat16, torch.float32))
+@pytest.mark.parametrize(
+    ("lens", "n", "k", "max_ctas"),
+    (
+        ([1, 0, 2, 1], 256, 512, 0),                       # fewer blocks than SMs: quarter-block shares
+        ([1, 0, 0, 0, 1, 0, 1, 1], 1024, 2048, 0),          # one token, four experts
+        ([3, 8, 9, 16, 17, 0, 31, 32], 384, 768, 0),        # every token-box size up to 32 rows
+        ([5, 33, 64, 65, 0, 130, 1, 200], 512, 1280, 0),    # 64-row chunks, several per expert
+        ([5, 33, 64, 65, 0, 130, 1, 200], 512, 1280, 5),    # few CTAs: whole blocks, many tiles each
+        ([7, 2, 0, 12], 136, 320, 3),                       # N tail inside a block, K tail inside a stage
+        ([2] * 64, 256, 256, 0),                            # many experts
+    ),
+)
+def test_swapped_decode_gemm_bit_identical(lens, n, k, max_ctas, out_dtype):
+    """The decode-shaped kernel accumulates every output over the whole K in the same order as
+    the 128 x 128 tiles: identical bits, and within tolerance of the oracle."""
+    from nvfp4moe_b200 import _lib
+
+    cu, a, b = _grouped_case(lens, n, k, seed=n + k + len(lens), b_std=0.05)
+    base, packed = _run_grouped(cu, a, b, out_dtype=out_dtype)
+    for pdl in (False, True):
+        got = _run_swapped(cu, packed, n, k, out_dtype, max_ctas, use_pdl=pdl)
+        assert torch.isfinite(got).all()
+        assert torch.equal(got, base), (lens, n, k, pdl)
+    ref, _ = _oracle_grouped(cu, a, b)
+    tol = GEMM_REL_TOL if out_dtype == torch.bfloat16 else 1e-5
+    assert O.rel_frobenius(base.cpu().float(), ref.to(out_dtype).float()) <= tol
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize(
+    ("activation", "clamp"),
+    (("swiglu", None), ("swiglu_oai", None), ("swiglu", 10.0), ("geglu", None), ("reglu", None),
+     ("relu2", None)),
+)
+def test_swapped_decode_fused_epilogue_bit_identical(activation, clamp):
+    """Activation + NVFP4 requantization of the decode-shaped kernel: byte for byte the codes
+    and scale factors of the 128 x 128 kernel (whose bytes are checked against the oracle in
+    test_fused_epilogue_matches_oracle)."""
+    from nvfp4moe_b200 import gemm
+    from nvfp4moe_b200.kernels.gated import GatedEpilogue
+    from nvfp4moe_b200.kernels.unary import UnaryEpilogue
+
+    lens = [1, 0, 9, 40, 2, 70, 129]
+    inter, hidden = 256, 512
+    n = inter if activation == "relu2" else 2 * inter
+    cu, a, b = _grouped_case(lens, n, hidden, seed=13, b_std=hidden**-0.5)
+    rows = a.shape[0]
+    qa, qb, sfa, sfb, alpha = gemm.quantize_grouped(a.cuda(), b.cuda(), cu.cuda())
+    policy = UnaryEpilogue(activation) if activation == "relu2" else GatedEpilogue(activation, clamp_limit=clamp)
+    tiles = -(-rows // 128) + len(lens)
+    pair = torch.tensor([0.004, 250.0], device="cuda")
+    results = []
+    for swap in (False, True):
+        qh = torch.full((rows, inter // 2), 0xEE, dtype=torch.uint8, device="cuda")
+        sfh = torch.zeros(1, tiles, inter // 64, 32, 4, 4, dtype=torch.float8_e4m3fn, device="cuda")
+        plan = gemm.GroupedGemm(len(lens), n, hidden, 128, 32 if swap else 128,
+                                output_dtype=torch.float4_e2m1fn_x2, epilogue=policy, swap_ab=swap)
+        plan(qa, qb, qh.view(torch.float4_e2m1fn_x2), cu.cuda(), sfa, sfb, alpha, output_sf=sfh,
+             output_scale=pair)
+        torch.cuda.synchronize()
+        results.append((qh.cpu(), O.sf_from_varlen(sfh.view(torch.uint8).cpu(), cu, inter // 16)))
+    assert torch.equal(results[0][0], results[1][0])
+    assert torch.equal(results[0][1], results[1][1])
+    assert (results[1][0] != 0xEE).any()
+
+
+def test_direct_routes_equal_the_dispatched_token():
+    """One token, k routes, no dispatch: fc1 reads row 0 for every route (broadcast) and fc2 row
+    r for route r; expert ids come from the route table.  Equal, bit for bit, to the same token
+    run through the expert-major path."""
+    from nvfp4moe_b200 import gemm
+    from nvfp4moe_b200.kernels.gated import GatedEpilogue
+
+    experts, hidden, inter, k = 16, 512, 256, 4
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(1, hidden, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(experts, 2 * inter, hidden, generator=g) * hidden**-0.5).to(torch.bfloat16)
+    w2 = (torch.randn(experts, hidden, inter, generator=g) * inter**-0.5).to(torch.bfloat16)
+    routes = torch.tensor([9, 2, 14, 5], dtype=torch.int32)  # not sorted: route order is kept
+    order = torch.argsort(routes)
+    counts = torch.bincount(routes.long(), minlength=experts)
+    cu = torch.zeros(experts + 1, dtype=torch.int32)
+    cu[1:] = counts.cumsum(0)
+    rows = x.expand(k, hidden).contiguous()
+    qa, qb1, sfa, sfb1, alpha1 = gemm.quantize_grouped(rows.cuda(), w1.cuda(), cu.cuda())
+    pair = torch.tensor([0.004, 250.0], device="cuda")
+    policy = GatedEpilogue("swiglu")
+    sf_rows = 1 + experts
+
+    def buffers():
+        qh = torch.zeros(k, inter // 2, dtype=torch.uint8, device="cuda")
+        sfh = torch.zeros(1, sf_rows, inter // 64, 32, 4, 4, dtype=torch.float8_e4m3fn, device="cuda")
+        out = torch.zeros(k, hidden, dtype=torch.bfloat16, device="cuda")
+        return qh, sfh, out
+
+    # fc2 operands: packed once through the public helper (its activations are unused here)
+    _, qb2, _, sfb2, _ = gemm.quantize_grouped(torch.zeros(k, inter, dtype=torch.bfloat16, device="cuda"),
+                                                w2.cuda(), cu.cuda())
+    alpha2 = torch.tensor([0.5], device="cuda")
+    # expert-major path
+    qh, sfh, out = buffers()
+    fc1 = gemm.GroupedGemm(experts, 2 * inter, hidden, 128, 128, output_dtype=torch.float4_e2m1fn_x2,
+                           epilogue=policy)
+    fc1(qa, qb1, qh.view(torch.float4_e2m1fn_x2), cu.cuda(), sfa, sfb1, alpha1, output_sf=sfh, output_scale=pair)
+    fc2 = gemm.GroupedGemm(experts, hidden, inter, 128, 128)
+    fc2(qh.view(torch.float4_e2m1fn_x2), qb2, out, cu.cuda(), sfh, sfb2, alpha2)
+    torch.cuda.synchronize()
+    want = out[torch.argsort(order).cuda()].cpu()  # back to route order
+    # direct path: the token quantized once into row 0 / atom row 0
+    qx1 = qa[:1].contiguous()
+    sfx1 = torch.zeros(1, 1 + experts, hidden // 64, 32, 4, 4, dtype=torch.float8_e4m3fn, device="cuda")
+    first_tile = int(cu[int(routes.min())]) // 128 + int(routes.min())
+    # row 0 of the lowest expert's atom row holds this token's factors
+    sfx1.view(torch.uint8)[0, 0] = sfa.view(torch.uint8)[0, first_tile]
+    qh, sfh, out = buffers()
+    table = routes.cuda()
+    d1 = gemm.GroupedGemm(experts, 2 * inter, hidden, 128, 128, output_dtype=torch.float4_e2m1fn_x2,
+                          epilogue=policy, use_dynamic_sched=False, use_pdl=True, direct_routes=k,
+                          broadcast_a=True)
+    qx_rows = torch.zeros(k, hidden // 2, dtype=torch.uint8, device="cuda")
+    qx_rows[0] = qx1.view(torch.uint8)[0]
+    d1(qx_rows.view(torch.float4_e2m1fn_x2), qb1, qh.view(torch.float4_e2m1fn_x2), table, sfx1, sfb1, alpha1,
+       output_sf=sfh, output_scale=pair)
+    d2 = gemm.GroupedGemm(experts, hidden, inter, 128, 128, use_dynamic_sched=False, use_pdl=True,
+                          direct_routes=k)
+    d2(qh.view(torch.float4_e2m1fn_x2), qb2, out, table, sfh, sfb2, alpha2)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all() and float(out.float().abs().sum()) > 0
+    assert torch.equal(out.cpu(), want)
+
+
+# --------------------------------------------------------------------------
 # decode preparation: dispatch + plan + quantize in one launch
 # --------------------------------------------------------------------------
 
