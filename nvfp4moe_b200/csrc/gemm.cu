@@ -1435,6 +1435,7 @@ struct DecodePlanData {
 static_assert(sizeof(DecodePlanData) <= sizeof(lm_gemm_plan), "plan storage too small");
 constexpr uint32_t kDecodePlanMagic = 0x4C4D4444u;
 
+constexpr int kDecSmemPerCta = (233472 - 2 * 1024) / 2;  // two CTAs per SM, 1 KB reserved for each
 constexpr int dec_smem_bytes(int ring_stages, int stage_bytes) { return 1024 + ring_stages * stage_bytes + kMiscBytes; }
 
 template <int kOut, int kAct>
@@ -1444,7 +1445,7 @@ int launch_decode(const DecodePlanData& pd, cudaStream_t stream) {
   int device = 0;
   LM_CUDA(cudaGetDevice(&device));
   if (device < 0 || device >= kMaxDevices || !configured[device]) {
-    LM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    LM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemPerCta));
     if (device >= 0 && device < kMaxDevices) configured[device] = true;
   }
   cudaLaunchConfig_t config = {};
@@ -1502,7 +1503,10 @@ int prepare_decode(const lm_gemm_args* a, int out_atom_cols, lm_gemm_plan* plan)
   // no expert can hold more than `rows` rows: steps of up to 32 rows keep the deeper ring
   p.cap = a->rows <= 32 ? 32 : 64;
   p.stage_bytes = kTileBytes + p.cap * kStageKBytes + 2 * kSfBytes;
-  p.ring_stages = (kSmemLimit - 1024 - kMiscBytes) / p.stage_bytes;
+  // Two CTAs per SM, each with half the shared memory: twice the threads that issue copies and
+  // MMAs per SM (the issue rate of single threads bounds a step with few rows), at the same
+  // number of stages in flight per SM.
+  p.ring_stages = (kDecSmemPerCta - 1024 - kMiscBytes) / p.stage_bytes;
   if (p.ring_stages > 16) p.ring_stages = 16;
   p.rows = a->rows;
   p.m_indptr = a->m_indptr;
@@ -1519,7 +1523,7 @@ int prepare_decode(const lm_gemm_args* a, int out_atom_cols, lm_gemm_plan* plan)
   p.up_bias = a->up_bias;
   const int sms = sm_count();
   LM_REQUIRE(sms > 0, "gemm: no CUDA device");
-  pd.grid = a->max_ctas > 0 ? a->max_ctas : sms;
+  pd.grid = a->max_ctas > 0 ? a->max_ctas : 2 * sms;
   // quarter blocks bound the CTAs that can have work: (rows / cap + groups) row tiles at most
   const int64_t max_quarters = (a->rows / p.cap + p.groups) * static_cast<int64_t>(p.n_blocks) * 4;
   if (pd.grid > max_quarters) pd.grid = static_cast<int>(max_quarters);

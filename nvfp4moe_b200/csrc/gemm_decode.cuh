@@ -24,10 +24,10 @@
 // Programmatic dependent launch: a CTA waits for its predecessor (griddepcontrol.wait) before
 // it reads anything that kernel wrote, and lets its own dependents start once it is past that
 // wait.  With `prefetch` the routing table is older than the predecessor (the second
-// projection of a layer): then only the warp that loads the token rows waits, and the warp
-// that loads the weights streams ahead by the ring depth while the predecessor drains.
+// projection of a layer): then only the token loads wait, and each producer warp has the
+// weights of one ring stage on their way while the predecessor drains.
 
-constexpr int kDecThreads = 256;         // warp 0 weight producer, 1 MMA, 2 set-up, 3 token producer, 4..7 epilogue
+constexpr int kDecThreads = 256;         // warps 0, 2, 3 TMA producers (2 after the set-up), 1 MMA, 4..7 epilogue
 constexpr int kDecFirstEpilogueWarp = 4;
 constexpr uint32_t kDecTmemCols = 256;   // two accumulators of 64 columns, four scale-factor slots of 32
 constexpr uint32_t kDecAccCols = 64;
@@ -115,7 +115,17 @@ struct DecWalker {
       }
       return t;
     }
-    while (group + 1 < p.groups && m->prefix[group + 1] <= mt) ++group;
+    if (m->prefix[group + 1] <= mt) {
+      // the last group whose first row tile is not past mt (empty groups share their
+      // successor's value and are skipped): a binary search, since a step with one token
+      // leaves hundreds of experts empty
+      int lo = group + 1, hi = p.groups;  // prefix[lo] <= mt < prefix[hi]
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (m->prefix[mid] <= mt) lo = mid; else hi = mid;
+      }
+      group = lo;
+    }
     const int local = (mt - m->prefix[group]) * p.cap;
     const int begin = m->cu[group];
     const int count = m->cu[group + 1] - begin;
@@ -256,7 +266,7 @@ __device__ __forceinline__ void dec_store_nvfp4(const DecodeParams& p, float v, 
 }
 
 template <int kOut, int kAct>
-__global__ void __launch_bounds__(kDecThreads, 1)
+__global__ void __launch_bounds__(kDecThreads, 2)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w64,
                    const __grid_constant__ CUtensorMap tmap_w32,
                    const __grid_constant__ CUtensorMap tmap_t8, const __grid_constant__ CUtensorMap tmap_t16,
@@ -277,7 +287,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 16; ++s) {
-      mbar_init(smem_u32(&misc->full[s]), 2);  // one arrival (with its byte count) per producer warp
+      mbar_init(smem_u32(&misc->full[s]), 1);
       mbar_init(smem_u32(&misc->empty[s]), 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -348,11 +358,13 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   const uint32_t tmem_base = misc->tmem_base;
   const int total_units = misc->total_row_tiles * p.n_blocks;
 
-  if (warp == 0) {
-    // ===================================================== TMA producer: weights and their scale factors
-    // Nothing read here was written by the predecessor kernel (with `prefetch` the routing table
-    // is older than it, without it every warp has waited already), so this warp never waits for
-    // it: the weight stream runs ahead by up to the ring depth while the predecessor drains.
+  if (warp == 0 || warp == 2 || warp == 3) {
+    // ===================================================== TMA producers
+    // Three warps take the ring-stage fills in turn.  One thread needs 700-900 cycles to wait
+    // for a free stage and start the four or five bulk copies of a 16 KB stage (each of these
+    // instructions takes on the order of a hundred cycles to issue), which bounded the whole
+    // kernel when a single warp did it; the MMA warp needs about 400 cycles per stage.
+    const int me = warp == 0 ? 0 : warp - 1;  // 0, 1, 2
     DecFillIter iter;
     iter.init(total_units, blockIdx.x, gridDim.x);
     DecFill f;
@@ -360,67 +372,59 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     uint32_t phase = 0;
     int fills = 0;
     bool ok = true;
+    // With `prefetch` the token operand is the predecessor kernel's output while the weights
+    // (and the routing table) are older: each producer starts the weights of its first stage,
+    // then waits for the predecessor, then loads the token rows.
+    bool waited = p.prefetch == 0;
     while (ok && iter.next(misc, p, f)) {
-      ok = mbar_wait(smem_u32(&misc->empty[stage]), phase ^ 1u, abort_flag, kStatusProducerTimeout);
-      if (!ok) break;
-      if (elect_one()) {
+      if (fills % 3 == me) {
+        ok = mbar_wait(smem_u32(&misc->empty[stage]), phase ^ 1u, abort_flag, kStatusProducerTimeout);
+        if (!ok) break;
         const uint32_t dst = smem_base + stage * p.stage_bytes;
         const uint32_t bar = smem_u32(&misc->full[stage]);
-        mbar_expect_tx(bar, (f.qb - f.qa) * kDecQuarterBytes + f.sf_bytes);
-        const int w_row = f.t.expert * p.n + f.nb * kTileM;
-        if (f.qa == 0 && f.qb == 4) {
-          tma_load_2d(dst, &tmap_w, f.ks * kStageKBytes, w_row, bar);
-        } else {
-          // a partial block in at most two boxes: 64 rows where a half block is whole
-          int q = f.qa;
-          while (q < f.qb) {
-            if ((q & 1) == 0 && q + 2 <= f.qb) {
-              tma_load_2d(dst + q * kDecQuarterBytes, &tmap_w64, f.ks * kStageKBytes, w_row + 32 * q, bar);
-              q += 2;
-            } else {
-              tma_load_2d(dst + q * kDecQuarterBytes, &tmap_w32, f.ks * kStageKBytes, w_row + 32 * q, bar);
-              q += 1;
+        if (elect_one()) {
+          mbar_expect_tx(bar, (f.qb - f.qa) * kDecQuarterBytes + 2 * f.sf_bytes + f.box * kStageKBytes);
+          const int w_row = f.t.expert * p.n + f.nb * kTileM;
+          if (f.qa == 0 && f.qb == 4) {
+            tma_load_2d(dst, &tmap_w, f.ks * kStageKBytes, w_row, bar);
+          } else {
+            // a partial block in at most two boxes: 64 rows where a half block is whole
+            int q = f.qa;
+            while (q < f.qb) {
+              if ((q & 1) == 0 && q + 2 <= f.qb) {
+                tma_load_2d(dst + q * kDecQuarterBytes, &tmap_w64, f.ks * kStageKBytes, w_row + 32 * q, bar);
+                q += 2;
+              } else {
+                tma_load_2d(dst + q * kDecQuarterBytes, &tmap_w32, f.ks * kStageKBytes, w_row + 32 * q, bar);
+                q += 1;
+              }
             }
           }
+          bulk_load(dst + off_sfw,
+                    p.sfw + (static_cast<int64_t>(f.t.expert * p.n_blocks + f.nb) * p.atom_cols +
+                             f.ks * kChunksPerStage) * 512,
+                    f.sf_bytes, bar);
         }
-        bulk_load(dst + off_sfw,
-                  p.sfw + (static_cast<int64_t>(f.t.expert * p.n_blocks + f.nb) * p.atom_cols +
-                           f.ks * kChunksPerStage) * 512,
-                  f.sf_bytes, bar);
+        __syncwarp();
+        if (!waited) {
+          pdl_wait();
+          waited = true;
+        }
+        if (elect_one()) {
+          const CUtensorMap* map =
+              f.box == 8 ? &tmap_t8 : (f.box == 16 ? &tmap_t16 : (f.box == 32 ? &tmap_t32 : &tmap_t64));
+          tma_load_2d(dst + off_tok, map, f.ks * kStageKBytes, f.t.row0, bar);
+          bulk_load(dst + off_sft,
+                    p.sft + (static_cast<int64_t>(f.t.sf_row) * p.atom_cols + f.ks * kChunksPerStage) * 512,
+                    f.sf_bytes, bar);
+        }
+        __syncwarp();
       }
-      __syncwarp();
       ++fills;
       if (++stage == p.ring_stages) { stage = 0; phase ^= 1u; }
     }
-    if (lane == 0) misc->fills_issued = fills;
-  } else if (warp == 3) {
-    // ===================================================== TMA producer: token rows and their scale factors
-    // (a second issuing thread: one thread starts a bulk copy every fifty nanoseconds or so, and
-    // four to six copies per 16 KB stage from one thread bounded the whole kernel)
-    if (p.prefetch) pdl_wait();  // the token operand is the predecessor's output
-    DecFillIter iter;
-    iter.init(total_units, blockIdx.x, gridDim.x);
-    DecFill f;
-    int stage = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    while (ok && iter.next(misc, p, f)) {
-      ok = mbar_wait(smem_u32(&misc->empty[stage]), phase ^ 1u, abort_flag, kStatusProducerTimeout);
-      if (!ok) break;
-      if (elect_one()) {
-        const uint32_t dst = smem_base + stage * p.stage_bytes;
-        const uint32_t bar = smem_u32(&misc->full[stage]);
-        mbar_expect_tx(bar, f.box * kStageKBytes + f.sf_bytes);
-        const CUtensorMap* map =
-            f.box == 8 ? &tmap_t8 : (f.box == 16 ? &tmap_t16 : (f.box == 32 ? &tmap_t32 : &tmap_t64));
-        tma_load_2d(dst + off_tok, map, f.ks * kStageKBytes, f.t.row0, bar);
-        bulk_load(dst + off_sft,
-                  p.sft + (static_cast<int64_t>(f.t.sf_row) * p.atom_cols + f.ks * kChunksPerStage) * 512,
-                  f.sf_bytes, bar);
-      }
-      __syncwarp();
-      if (++stage == p.ring_stages) { stage = 0; phase ^= 1u; }
-    }
+    // (the abort path waits for the stages up to the last one any producer started)
+    if (lane == 0) atomicMax(&misc->fills_issued, fills);
   } else if (warp == 1) {
     // ===================================================== MMA issuer
     DecWalker walker;
