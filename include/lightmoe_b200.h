@@ -157,6 +157,25 @@ int lm_dispatch_quantize_decode(const void* x, const int32_t* topk_ids, const fl
                                 lm_stream_t stream);
 
 /*
+ * Decode step preparation for ONE token in one launch, without scratch: the routing metadata
+ * of lm_dispatch for its top_k routes and lm_quantize_decode of its row.
+ * Replaces nvfp4_decode_prepare and nvfp4_direct_decode_prepare
+ * (lightmoe/kernels/quantize/decode.py:946-1105, kernel :548-818).
+ *   direct == 0  expert-major: gather / slots / probs (top_k), cu = m_indptr (experts+1),
+ *                padded_offsets (experts); the row is written to each of its top_k
+ *                expert-major rows, scale factors as varlen atoms (expert e in atom row e).
+ *   direct != 0  route order is kept: slots[r] = r, cu[r] = expert of route r (top_k entries,
+ *                what lm_gemm_args.direct_routes reads as its table), probs[r] = weight of route
+ *                r; the row is quantized once into row 0 of q, scale factors into atom row 0.
+ *                padded_offsets is not written.
+ * x is (1, features) BF16; top_k <= min(experts, 32).
+ */
+int lm_decode_prepare(const void* x, const int32_t* topk_ids, const float* topk_weights, int top_k,
+                      int experts, int features, int direct, int32_t* gather, int32_t* slots,
+                      int32_t* cu, float* probs, int32_t* padded_offsets, const float* scale_pair,
+                      uint8_t* q, uint8_t* sf, lm_stream_t stream);
+
+/*
  * lm_dispatch for callers that have no device memory to give as scratch and
  * may not obtain any: a plugin inside a serving process whose memory pool
  * already owns the whole GPU, or a host runtime that forbids its extensions to

@@ -105,6 +105,11 @@ _SIGNATURES = {
         [c_ptr, c_ptr, c_ptr, c_i64, c_i32, c_i32, c_i32, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
          c_i64, c_i32, c_ptr, c_ptr, c_ptr, c_ptr],
     ),
+    "lm_decode_prepare": (
+        c_i32,
+        [c_ptr, c_ptr, c_ptr, c_i32, c_i32, c_i32, c_i32, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
+         c_ptr],
+    ),
     "lm_dispatch_static_max_rows": (c_i64, []),
     "lm_dispatch_static": (
         c_i32,

@@ -258,6 +258,103 @@ __global__ void __launch_bounds__(kThreads) dispatch_quantize_decode_kernel(Deco
   }
 }
 
+// ------------------------------------------------ one token: routing metadata + quantize, one launch
+// No sort is needed for the k <= 32 routes of a single token: thread r counts the routes that
+// come before route r in expert-major order.  `direct` keeps the routes in their own order
+// instead: the token is quantized once into row 0 and a table of expert ids replaces m_indptr.
+struct OneTokenParams {
+  const __nv_bfloat16* x;
+  const int32_t* topk_ids;
+  const float* topk_weights;
+  int top_k;
+  int experts;
+  int features;
+  int direct;
+  int32_t* gather;
+  int32_t* slots;
+  int32_t* cu;  // m_indptr (experts + 1), or with `direct` the expert id of every route (top_k)
+  float* probs;
+  int32_t* padded_offsets;
+  const float* scale_pair;
+  uint8_t* q;
+  uint8_t* sf;
+};
+
+__global__ void __launch_bounds__(kThreads) decode_prepare_one_kernel(OneTokenParams p) {
+  __shared__ int s_ids[32];
+  __shared__ int s_dst[32];   // expert-major row of route r
+  __shared__ int s_rank[32];  // its place among the routes of the same expert
+  const int k = p.top_k;
+  if (threadIdx.x < k) s_ids[threadIdx.x] = __ldg(p.topk_ids + threadIdx.x);
+  __syncthreads();
+  if (threadIdx.x < k) {
+    const int r = threadIdx.x, e = s_ids[r];
+    int dst = 0, rank = 0;
+    for (int o = 0; o < k; ++o) {
+      const int eo = s_ids[o];
+      dst += (eo < e) || (eo == e && o < r);
+      rank += (eo == e && o < r);
+    }
+    s_dst[r] = p.direct ? r : dst;
+    s_rank[r] = p.direct ? 0 : rank;
+    if (blockIdx.x == 0) {
+      const int row = s_dst[r];
+      p.slots[r] = row;
+      p.gather[row] = 0;
+      p.probs[row] = __ldg(p.topk_weights + r);
+      if (p.direct) p.cu[r] = e;
+    }
+  }
+  if (blockIdx.x == 0 && !p.direct) {
+    // m_indptr[e] = routes of experts below e; padded_offsets[e] = 128 x experts up to e with a route
+    for (int e = threadIdx.x; e <= p.experts; e += kThreads) {
+      int below = 0, used = 0;
+      for (int o = 0; o < k; ++o) {
+        const int eo = s_ids[o];
+        below += eo < e;
+        bool first = eo <= e;
+        for (int q = 0; q < o; ++q) first = first && s_ids[q] != eo;
+        used += first;
+      }
+      p.cu[e] = below;
+      if (e < p.experts) p.padded_offsets[e] = used * 128;
+    }
+  }
+  __syncthreads();
+  // quantize: each warp one 512-feature slice, written to every row of the token (row 0 only
+  // with `direct`); the scale factors of expert-major row d of expert e sit in atom row e
+  // (fewer than 128 rows in all), row `rank`
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = (blockIdx.x * (kThreads / 32) + warp) * 512 + lane * 16;
+  if (col - lane * 16 >= p.features) return;
+  const bool col_ok = col < p.features;
+  const float pts = __ldg(p.scale_pair);
+  const float inv_pts = __ldg(p.scale_pair + 1);
+  Slice<__nv_bfloat16> v;
+  uint2 packed = make_uint2(0, 0);
+  uint32_t sf_byte = 0;
+  if (col_ok) {
+    v.load(p.x + col);
+    sf_byte = quantize_group(v, pts, inv_pts, true, &packed);
+  }
+  uint32_t word = sf_byte;
+  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 1) << 8;
+  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 2) << 16;
+  word |= __shfl_down_sync(0xFFFFFFFFu, sf_byte, 3) << 24;
+  if (!col_ok) return;
+  const int atom_cols = p.features >> 6;
+  const int copies = p.direct ? 1 : k;
+  for (int r = 0; r < copies; ++r) {
+    const int row = p.direct ? 0 : s_dst[r];
+    const int atom_row = p.direct ? 0 : s_ids[r];
+    const int in_tile = p.direct ? 0 : s_rank[r];
+    *reinterpret_cast<uint2*>(p.q + static_cast<int64_t>(row) * (p.features >> 1) + (col >> 1)) = packed;
+    if ((lane & 3) == 0)
+      *reinterpret_cast<uint32_t*>(p.sf + (static_cast<int64_t>(atom_row) * atom_cols + (col >> 6)) * 512 +
+                                   (in_tile & 31) * 16 + (in_tile >> 5) * 4) = word;
+  }
+}
+
 // Scratch of the entry point that allocates nothing: room for the per-chunk
 // counts of 128 chunks x 256 experts (131072 assignments).  Every GPU that loads
 // the library holds these 128 KB until the process exits.
@@ -371,6 +468,27 @@ extern "C" int lm_dispatch_static(const int32_t* topk_ids, const float* topk_wei
     dispatch_scatter_kernel<false><<<chunks, kThreads, smem, s>>>(p);
     note_launch();
   }
+  LM_CUDA(cudaGetLastError());
+  return LM_OK;
+}
+
+extern "C" int lm_decode_prepare(const void* x, const int32_t* topk_ids, const float* topk_weights, int top_k,
+                                 int experts, int features, int direct, int32_t* gather, int32_t* slots,
+                                 int32_t* cu, float* probs, int32_t* padded_offsets, const float* scale_pair,
+                                 uint8_t* q, uint8_t* sf, lm_stream_t stream) {
+  using namespace lm;
+  LM_REQUIRE(x && topk_ids && topk_weights && gather && slots && cu && probs && scale_pair && q && sf,
+             "decode_prepare: null pointer");
+  LM_REQUIRE(direct || padded_offsets, "decode_prepare: null pointer");
+  LM_REQUIRE(experts > 0 && experts <= kMaxExperts, "decode_prepare: 1..256 experts");
+  LM_REQUIRE(top_k > 0 && top_k <= 32 && top_k <= experts, "decode_prepare: top_k must be 1..min(experts, 32)");
+  LM_REQUIRE(features > 0 && features % 64 == 0, "decode_prepare: features must be a multiple of 64");
+  OneTokenParams p{static_cast<const __nv_bfloat16*>(x), topk_ids, topk_weights, top_k, experts, features,
+                   direct ? 1 : 0, gather, slots, cu, probs, padded_offsets, scale_pair, q, sf};
+  const int slices = (features + 511) / 512;
+  const int grid = (slices + kThreads / 32 - 1) / (kThreads / 32);
+  decode_prepare_one_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(p);
+  note_launch();
   LM_CUDA(cudaGetLastError());
   return LM_OK;
 }

@@ -21,7 +21,8 @@ import torch
 from ._quantization import _DEN, quantize_expert_stack
 from .kernels.gated import GatedEpilogue
 from .kernels.grouped.runtime import GroupedNvfp4Gemm
-from .kernels.quantize.decode import nvfp4_dispatch_quantize_decode, nvfp4_quantize_decode
+from .kernels.quantize.decode import (nvfp4_direct_decode_prepare, nvfp4_dispatch_quantize_decode,
+                                      nvfp4_quantize_decode)
 from .kernels.quantize.runtime import nvfp4_quantize_rowwise
 from .kernels.routing.combine import moe_finalize
 from .kernels.routing.dispatch import MAX_ASSIGNMENTS, moe_dispatch, scratch_elems
@@ -309,6 +310,7 @@ class InferenceMoE:
         self._full_executions: dict[tuple[int, bool], _FullExecution] = {}
         self._routed_gemms: dict[tuple[str, int], GroupedNvfp4Gemm] = {}
         self._calibration_gemms: dict[int, GroupedNvfp4Gemm] = {}
+        self._direct_execution_plan: _FullExecution | None = None
 
     # ------------------------------------------------------------------ state
     @property
@@ -384,6 +386,7 @@ class InferenceMoE:
         self._full_executions.clear()
         self._routed_gemms.clear()
         self._calibration_gemms.clear()
+        self._direct_execution_plan = None
         if self._scales_ready:
             self._refresh_alphas()
         return self
@@ -519,6 +522,33 @@ class InferenceMoE:
         self._full_executions[key] = execution
         return execution
 
+    def _direct_execution(self) -> _FullExecution:
+        """The one-token step without a dispatch (``lightmoe/inference.py:656-721``): the token is
+        quantized once, both GEMMs walk the ``top_k`` routes in route order with the expert ids
+        in the first ``top_k`` words of ``_m_indptr``; fc1 reads row 0 for every route."""
+        execution = self._direct_execution_plan
+        if execution is not None:
+            return execution
+        rows = self.topk
+        qx, qh, sfx, sfh = self._views(rows)
+        routed_out = self._routed_out[:rows]
+        route_ids = self._m_indptr[: self.topk]
+        unary = self.activation == "relu2"
+        with torch.cuda.device(self.device):
+            fc1 = GroupedNvfp4Gemm(
+                self.experts, self.intermediate_size if unary else 2 * self.intermediate_size,
+                self.hidden_size, 128, 128, output_dtype=torch.float4_e2m1fn_x2, epilogue=self._epilogue(),
+                use_dynamic_sched=False, use_pdl=True, direct_routes=self.topk, broadcast_a=True)
+            fc2 = GroupedNvfp4Gemm(self.experts, self.hidden_size, self.intermediate_size, 128, 128,
+                                   use_dynamic_sched=False, use_pdl=True, direct_routes=self.topk)
+            fc2.weights_ahead = True
+        fc1.prepare(qx, self.qb1, qh, route_ids, sfx, self.sfb1, self._alpha1, output_sf=sfh,
+                    output_scale=self._h_scale)
+        fc2.prepare(qh, self.qb2, routed_out, route_ids, sfh, self.sfb2, self._alpha2)
+        execution = _FullExecution(fc1, fc2, qx, qh, sfx, sfh, routed_out)
+        self._direct_execution_plan = execution
+        return execution
+
     # ------------------------------------------------------------ calibration
     @torch.no_grad()
     def calibrate_routed(self, x, m_indptr, padded_offsets) -> "InferenceMoE":
@@ -651,6 +681,17 @@ class InferenceMoE:
         tokens = self._validate_full(x, topk_ids, topk_weights)
         rows = tokens * self.topk
         output = self._output_view(out, tokens, "out")
+        if tokens == 1 and self.topk <= 32 and self.tile_override is None:
+            # one token: no dispatch, the routes keep their order
+            execution = self._direct_execution()
+            nvfp4_direct_decode_prepare(x, topk_ids, topk_weights, self._gather[:rows], self._slots[:rows],
+                                        self._m_indptr[: self.topk], self._probs[:rows],
+                                        self._padded_offsets, self._x_scale, execution.qx, execution.sfx)
+            execution.fc1.launch()
+            execution.fc2.launch()
+            moe_finalize(execution.routed_out, self._slots[:rows], output, self.topk, tile_t=1,
+                         n_frag=2, weights=self._probs[:rows], use_pdl=True)
+            return output
         execution = self._full_execution(tokens, decode=True)
         if rows <= 1024:
             # one launch: dispatch + decode plan + quantize-once-and-scatter

@@ -13,6 +13,8 @@ _EXPORTS = {
     "grouped_nvfp4_gemm": (".grouped.runtime", "grouped_nvfp4_gemm"),
     "moe_dispatch": (".routing.dispatch", "moe_dispatch"),
     "moe_finalize": (".routing.combine", "moe_finalize"),
+    "nvfp4_decode_prepare": (".quantize.decode", "nvfp4_decode_prepare"),
+    "nvfp4_direct_decode_prepare": (".quantize.decode", "nvfp4_direct_decode_prepare"),
     "nvfp4_quantize_batched": (".quantize.runtime", "nvfp4_quantize_batched"),
     "nvfp4_quantize_decode": (".quantize.decode", "nvfp4_quantize_decode"),
     "nvfp4_quantize_rowwise": (".quantize.runtime", "nvfp4_quantize_rowwise"),

@@ -72,13 +72,20 @@ def _check(plan, x, ids, w, out, sample, *, decode=False):
     assert _lib.device_status() == 0
     assert torch.isfinite(out).all()
     # ---- integer stages of the whole batch, bit for bit
-    gather, cu, probs, slots, padded, _ = O.dispatch(ids.cpu(), w.cpu(), experts)
-    assert torch.equal(plan._gather[:rows].cpu(), gather)
-    assert torch.equal(plan._m_indptr.cpu(), cu)
-    assert torch.equal(plan._slots[:rows].cpu(), slots)
-    assert torch.equal(plan._probs[:rows].cpu(), probs)
-    if not decode:
-        assert torch.equal(plan._padded_offsets.cpu(), padded)
+    if decode and tokens == 1:
+        # the one-token step keeps the routes in their own order: identity slots, the expert
+        # ids in place of m_indptr (lightmoe/kernels/quantize/decode.py:629-637)
+        assert torch.equal(plan._slots[:rows].cpu(), torch.arange(rows, dtype=torch.int32))
+        assert torch.equal(plan._m_indptr[:k].cpu(), ids[0].cpu())
+        assert torch.equal(plan._probs[:rows].cpu(), w[0].cpu())
+    else:
+        gather, cu, probs, slots, padded, _ = O.dispatch(ids.cpu(), w.cpu(), experts)
+        assert torch.equal(plan._gather[:rows].cpu(), gather)
+        assert torch.equal(plan._m_indptr.cpu(), cu)
+        assert torch.equal(plan._slots[:rows].cpu(), slots)
+        assert torch.equal(plan._probs[:rows].cpu(), probs)
+        if not decode:
+            assert torch.equal(plan._padded_offsets.cpu(), padded)
     # ---- sampled tokens end to end
     sample = torch.as_tensor(sample, dtype=torch.long)
     xs, ids_s, w_s = x[sample.cuda()].cpu(), ids[sample.cuda()].cpu(), w[sample.cuda()].cpu()

@@ -691,6 +691,59 @@ def test_quantize_once_scatter_matches_oracle_bytes(tokens, experts, k, features
         assert torch.equal(O.sf_from_varlen(sf.cpu(), cu, features // 16), sf_want)
 
 
+@pytest.mark.parametrize(("experts", "k", "features"), ((8, 2, 256), (256, 8, 6144), (64, 32, 2048), (5, 5, 512)))
+def test_one_token_prepare_matches_oracle(experts, k, features):
+    """``nvfp4_decode_prepare`` / ``nvfp4_direct_decode_prepare``: one token, no scratch, one
+    launch.  Expert-major form: the oracle's dispatch and gathered-row quantizer, bit for bit.
+    Direct form: identity slots, the expert ids as the route table, the row quantized once."""
+    from nvfp4moe_b200.kernels import nvfp4_decode_prepare
+    from nvfp4moe_b200.kernels.quantize import nvfp4_direct_decode_prepare
+
+    g = torch.Generator().manual_seed(experts + k)
+    ids = torch.randperm(experts, generator=g)[:k].to(torch.int32).reshape(1, k)
+    w = torch.rand(1, k, generator=g)
+    x = torch.randn(1, features, generator=g).to(torch.bfloat16)
+    pts = O.tensor_scale(x)
+    pair = torch.cat((pts, 1.0 / pts)).cuda()
+    gather_ref, cu_ref, probs_ref, slots_ref, padded_ref, _ = O.dispatch(ids, w, experts)
+    q_ref, sf_ref = O.quantize_rows(x, pts, te_math=True)
+    dev = "cuda"
+    tiles = 1 + experts
+
+    def buffers(table):
+        return dict(gather=torch.full((k,), -1, dtype=torch.int32, device=dev),
+                    slots=torch.full((k,), -1, dtype=torch.int32, device=dev),
+                    table=torch.full((table,), -1, dtype=torch.int32, device=dev),
+                    probs=torch.full((k,), -1.0, device=dev),
+                    padded=torch.full((experts,), -1, dtype=torch.int32, device=dev),
+                    q=torch.zeros(k, features // 2, dtype=torch.uint8, device=dev),
+                    sf=torch.zeros(1, tiles, features // 64, 32, 4, 4, dtype=torch.uint8, device=dev))
+
+    b = buffers(experts + 1)
+    nvfp4_decode_prepare(x.cuda(), ids.cuda(), w.cuda(), b["gather"], b["slots"], b["table"], b["probs"],
+                         b["padded"], pair, b["q"], b["sf"].view(torch.float8_e4m3fn))
+    torch.cuda.synchronize()
+    for got, want in ((b["gather"], gather_ref), (b["slots"], slots_ref), (b["table"], cu_ref),
+                      (b["probs"], probs_ref), (b["padded"], padded_ref)):
+        assert torch.equal(got.cpu(), want)
+    assert torch.equal(b["q"].cpu(), q_ref.expand(k, -1))
+    assert torch.equal(O.sf_from_varlen(b["sf"].cpu(), cu_ref, features // 16), sf_ref.expand(k, -1))
+
+    d = buffers(k)
+    nvfp4_direct_decode_prepare(x.cuda(), ids.cuda(), w.cuda(), d["gather"], d["slots"], d["table"], d["probs"],
+                                d["padded"], pair, d["q"], d["sf"].view(torch.float8_e4m3fn))
+    torch.cuda.synchronize()
+    assert torch.equal(d["slots"].cpu(), torch.arange(k, dtype=torch.int32))
+    assert torch.equal(d["table"].cpu(), ids[0])
+    assert torch.equal(d["probs"].cpu(), w[0])
+    assert torch.equal(d["q"][0].cpu(), q_ref[0]) and not d["q"][1:].any()
+    assert torch.equal(O.sf_from_blocked(d["sf"][0, :1].cpu(), 1, features // 16), sf_ref)
+    with pytest.raises(ValueError, match="one token"):
+        nvfp4_decode_prepare(x.cuda().expand(2, -1).contiguous(), ids.cuda().expand(2, -1).contiguous(),
+                             w.cuda().expand(2, -1).contiguous(), b["gather"], b["slots"], b["table"],
+                             b["probs"], b["padded"], pair, b["q"], b["sf"].view(torch.float8_e4m3fn))
+
+
 # --------------------------------------------------------------------------
 # router step: softmax -> top-k -> renormalise
 # --------------------------------------------------------------------------
