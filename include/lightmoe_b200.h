@@ -271,11 +271,20 @@ typedef struct lm_gemm_args {
      when m_indptr, b, sfb and alpha were complete before the previous kernel began and that
      kernel is itself a swap_ab launch of this library (the second projection of a layer). */
   int32_t weights_ahead;
+  /* With out_row_ptrs (BF16 output that returns to the ranks of an expert-parallel group): whole
+     32-row blocks leave as one bulk tensor store each instead of row by row.  out_blocks is the
+     table lm_ep_plan writes; return_bases is a HOST array of `return_world` addresses, the
+     return buffer of every rank (return_rows rows of n BF16 values, 16-byte aligned).  Blocks
+     the table marks -1 still go through out_row_ptrs. */
+  const int32_t* out_blocks;
+  const uint64_t* return_bases;
+  int32_t return_world;
+  int64_t return_rows;
 } lm_gemm_args;
 
 /* Caller-provided storage for a prepared GEMM (tensor maps + arguments). */
 typedef struct lm_gemm_plan {
-  uint64_t opaque[160];
+  uint64_t opaque[320];
 } lm_gemm_plan;
 
 /* Host only: validates `args` and encodes the TMA descriptors into `plan`. */
@@ -314,13 +323,17 @@ int lm_route_topk(const void* logits, int logits_dtype, int64_t tokens, int expe
  *   dest_base    (experts) row on the owner where this rank's rows of expert e begin
  *   owner_start  (experts) row on the owner where expert e begins
  *   row_ptrs     (max_rows) address each received row's result goes to (lm_gemm_args.out_row_ptrs)
+ *   out_blocks   optional ((max_rows/128 + experts/world) * 4, 2) int32 for lm_gemm_args.out_blocks:
+ *                per 32-row block of every 128-row tile (atom row of the tile, quarter) the source
+ *                rank and the first row in that rank's return buffer when the block is 32 whole
+ *                rows of one (expert, source) segment, else -1
  *   valid        1, or 0 when some rank would receive more than max_rows rows: then own_indptr
  *                is all zero (the GEMMs compute nothing) and lm_ep_quantize_send sends nothing
  */
 int lm_ep_plan(const int32_t* counts_all, int world, int rank, int experts, int64_t max_rows,
                int64_t row_bytes, const uint64_t* return_base, int32_t* own_indptr,
-               int32_t* dest_base, int32_t* owner_start, uint64_t* row_ptrs, int32_t* valid,
-               lm_stream_t stream);
+               int32_t* dest_base, int32_t* owner_start, uint64_t* row_ptrs, int32_t* out_blocks,
+               int32_t* valid, lm_stream_t stream);
 
 /*
  * lm_quantize_decode whose destinations are the owners' operand buffers: each token is

@@ -56,11 +56,15 @@ class GemmArgs(ctypes.Structure):
         ("broadcast_a", c_i32),
         ("use_pdl", c_i32),
         ("weights_ahead", c_i32),
+        ("out_blocks", c_ptr),
+        ("return_bases", ctypes.POINTER(ctypes.c_uint64)),
+        ("return_world", c_i32),
+        ("return_rows", c_i64),
     ]
 
 
 class GemmPlan(ctypes.Structure):
-    _fields_ = [("opaque", ctypes.c_uint64 * 160)]
+    _fields_ = [("opaque", ctypes.c_uint64 * 320)]
 
 
 _SIGNATURES = {
@@ -82,7 +86,7 @@ _SIGNATURES = {
     "lm_ep_plan": (
         c_i32,
         [c_ptr, c_i32, c_i32, c_i32, c_i64, c_i64, ctypes.POINTER(ctypes.c_uint64), c_ptr, c_ptr, c_ptr,
-         c_ptr, c_ptr, c_ptr],
+         c_ptr, c_ptr, c_ptr, c_ptr],
     ),
     "lm_ep_quantize_send": (
         c_i32,

@@ -24,6 +24,7 @@ __device__ uint32_t g_ep_status = 0;
 constexpr int kMaxRanks = LM_EP_MAX_RANKS;
 constexpr int kMaxExperts = 256;
 constexpr int kPlanThreads = 256;
+constexpr int kPlanTileRows = 128;
 
 struct PlanParams {
   const int32_t* counts_all;  // [world, experts]: row g = rows rank g holds for every expert
@@ -38,6 +39,10 @@ struct PlanParams {
   int32_t* dest_base;     // [experts] owner row where this rank's rows of expert e begin
   int32_t* owner_start;   // [experts] owner row where expert e begins
   uint64_t* row_ptrs;     // [max_rows] where each received row's result goes
+  int32_t* out_blocks;    // optional [(max_rows/128 + local_experts) * 4][2]: per 32-row block of a
+                          // 128-row tile (atom row of its scale factors, quarter) the source rank and
+                          // the first row in that rank's return buffer, or -1 when the block is not
+                          // 32 whole rows of one (expert, source) segment
   int32_t* valid;         // 1 when every owner's rows fit max_rows
 };
 
@@ -133,6 +138,34 @@ __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(PlanParams p) {
     const int rows = s_cnt[g][e];
     for (int i = tid; i < rows; i += kPlanThreads)
       p.row_ptrs[first + i] = p.return_base[g] + static_cast<uint64_t>(src_row + i) * p.row_bytes;
+  }
+  if (p.out_blocks == nullptr) return;
+  // 32-row blocks that lie inside one segment leave the fc2 kernel as one bulk store each: the
+  // rows of a segment are consecutive in the source's return buffer
+  for (int l = blockIdx.x; l < L; l += gridDim.x) {
+    const int e = p.rank * L + l;
+    const int begin = s_owner_start[e];
+    const int total = s_total[e];
+    const int first_tile = begin / kPlanTileRows + l;
+    const int blocks = ((total + kPlanTileRows - 1) / kPlanTileRows) * 4;
+    for (int b = tid; b < blocks; b += kPlanThreads) {
+      const int lo = b * 32;  // first row of the block, counted from the expert's first row
+      int rank = -1, ret_row = 0;
+      if (lo + 32 <= total) {
+        int seg_lo = 0;
+        for (int g = 0; g < G; ++g) {
+          const int seg_hi = seg_lo + s_cnt[g][e];
+          if (lo >= seg_lo && lo + 32 <= seg_hi) {
+            rank = g;
+            ret_row = s_src_start[g][e] + (lo - seg_lo);
+            break;
+          }
+          seg_lo = seg_hi;
+        }
+      }
+      p.out_blocks[2 * (first_tile * 4 + b)] = rank;
+      p.out_blocks[2 * (first_tile * 4 + b) + 1] = ret_row;
+    }
   }
 }
 
@@ -345,8 +378,8 @@ int ep_status_clear() {
 
 extern "C" int lm_ep_plan(const int32_t* counts_all, int world, int rank, int experts, int64_t max_rows,
                           int64_t row_bytes, const uint64_t* return_base, int32_t* own_indptr,
-                          int32_t* dest_base, int32_t* owner_start, uint64_t* row_ptrs, int32_t* valid,
-                          lm_stream_t stream) {
+                          int32_t* dest_base, int32_t* owner_start, uint64_t* row_ptrs, int32_t* out_blocks,
+                          int32_t* valid, lm_stream_t stream) {
   using namespace lm;
   LM_REQUIRE(counts_all && return_base && own_indptr && dest_base && owner_start && row_ptrs && valid,
              "ep_plan: null pointer");
@@ -369,6 +402,7 @@ extern "C" int lm_ep_plan(const int32_t* counts_all, int world, int rank, int ex
   p.dest_base = dest_base;
   p.owner_start = owner_start;
   p.row_ptrs = row_ptrs;
+  p.out_blocks = out_blocks;
   p.valid = valid;
   const int segments = p.local_experts * world;
   ep_plan_kernel<<<segments < 296 ? segments : 296, kPlanThreads, 0, as_stream(stream)>>>(p);

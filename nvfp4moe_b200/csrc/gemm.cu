@@ -107,6 +107,7 @@ struct GemmParams {
   uint8_t* out_sf;
   const float* out_scale;
   const uint64_t* out_row_ptrs;  // BF16 output: optional address of every output row
+  const int32_t* out_blocks;     // with out_row_ptrs: (tile atom row * 4 + quarter) -> {rank, first row} or -1
   int tma_store;                 // BF16 output: whole 32-row blocks leave through TMA stores
   int out_atom_cols;  // NVFP4 output: out_n / 64
   float clamp_limit;
@@ -283,6 +284,12 @@ __host__ __device__ constexpr uint32_t make_idesc(int n) {
          (static_cast<uint32_t>(kTileM >> 4) << 24);
 }
 
+// Tensor maps of the return buffers of the ranks of an expert-parallel group (BF16 rows that go
+// back to the rank that sent them): 32-row x 64-column boxes like the local output map.
+struct ReturnMaps {
+  CUtensorMap rank[LM_EP_MAX_RANKS];
+};
+
 struct Misc {  // lives after the operand slots and the store staging
   uint64_t full[kMaxRing];         // ring stage filled by TMA
   uint64_t empty[kMaxRing];        // ring stage drained by the MMAs
@@ -396,6 +403,7 @@ struct DrainContext {
   uint32_t lane_base;        // TMEM address of the warp's 32 lanes, column 0
   uint32_t warp_store;       // the warp's BF16 staging in shared memory (1024-byte aligned)
   const CUtensorMap* out_map;  // BF16 output: tensor map of the output (32 x 64 boxes)
+  const ReturnMaps* return_maps;  // BF16 output through out_blocks: the ranks' return buffers
   uint32_t bar_shared_cols;  // signalled when the columns both accumulators use are in registers
   uint32_t bar_acc_empty;    // signalled when the whole accumulator is in registers
   bool remote;               // the two barriers are cluster addresses (the pair leader's)
@@ -440,8 +448,28 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
   const bool rows_any = t.valid > quarter * 32;  // this warp owns at least one valid row
   // rows may live anywhere (another GPU's buffer): lane l holds the address of row l
   unsigned long long row_base = 0;
-  if (kOut == LM_OUT_BF16 && p.out_row_ptrs != nullptr && quarter * 32 + lane < t.valid)
-    row_base = __ldg(reinterpret_cast<const unsigned long long*>(p.out_row_ptrs) + t.row0 + quarter * 32 + lane);
+  // where this warp's 32-row block goes when it leaves as one bulk store: the output itself, or
+  // the return buffer of the rank the route plan names for it
+  const CUtensorMap* block_map = nullptr;
+  int block_row = 0;
+  if (kOut == LM_OUT_BF16) {
+    if (p.out_row_ptrs == nullptr) {
+      if (p.tma_store && t.valid - quarter * 32 >= 32) {
+        block_map = c.out_map;
+        block_row = t.row0 + quarter * 32;
+      }
+    } else {
+      if (p.out_blocks != nullptr && t.valid - quarter * 32 >= 32) {
+        const int2 dst = __ldg(reinterpret_cast<const int2*>(p.out_blocks) + (t.sf_row * 4 + quarter));
+        if (dst.x >= 0) {
+          block_map = &c.return_maps->rank[dst.x];
+          block_row = dst.y;
+        }
+      }
+      if (block_map == nullptr && quarter * 32 + lane < t.valid)
+        row_base = __ldg(reinterpret_cast<const unsigned long long*>(p.out_row_ptrs) + t.row0 + quarter * 32 + lane);
+    }
+  }
   uint32_t va[32], vb[32];
   tc_load32(taddr + slice0 * 64, va);
   tc_load32(taddr + slice0 * 64 + 32, vb);
@@ -539,12 +567,11 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
       }
     } else if (kOut == LM_OUT_BF16) {
       const int rows_here = t.valid - quarter * 32;  // valid rows among this warp's 32
-      if (p.tma_store && p.out_row_ptrs == nullptr && rows_here >= 32) {
-        // the whole block belongs to this expert: one TMA store moves it
+      if (block_map != nullptr) {
+        // the whole block has one destination: one TMA store moves it
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0 && cols_ok)
-          tma_store_2d(c.out_map, warp_store, col64 * 64, t.row0 + quarter * 32);
+        if (lane == 0 && cols_ok) tma_store_2d(block_map, warp_store, col64 * 64, block_row);
         return;
       }
       // transposed read: a global store covers four whole 128-byte row pieces
@@ -623,7 +650,8 @@ template <int kOut, int kAct, int kNB>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64,
             const __grid_constant__ CUtensorMap tmap_a32, const __grid_constant__ CUtensorMap tmap_b,
-            const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
+            const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ ReturnMaps tmap_return,
+            const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -876,6 +904,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     ctx.lane_base = tmem_base + (static_cast<uint32_t>(ctx.quarter * 32) << 16);
     ctx.warp_store = store_base + (warp - kFirstEpilogueWarp) * kStoreBytesPerWarp;
     ctx.out_map = &tmap_out;
+    ctx.return_maps = &tmap_return;
     ctx.bar_shared_cols = smem_u32(&misc->shared_cols_free);
     ctx.remote = false;
     ctx.acc1_col = kWideAcc1Col;
@@ -1049,7 +1078,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64,
                  const __grid_constant__ CUtensorMap tmap_a32, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_sfa,
-                 const __grid_constant__ CUtensorMap tmap_sfb, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_sfb, const __grid_constant__ ReturnMaps tmap_return,
+                 const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -1271,6 +1301,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     ctx.lane_base = tmem_base + (static_cast<uint32_t>(ctx.quarter * 32) << 16);
     ctx.warp_store = store_base + (warp - kFirstEpilogueWarp) * kStoreBytesPerWarp;
     ctx.out_map = &tmap_out;
+    ctx.return_maps = &tmap_return;
     ctx.remote = !leader;
     ctx.acc1_col = kWideAcc1Col;
     const uint32_t cols_bar = smem_u32(&misc->shared_cols_free);
@@ -1348,6 +1379,7 @@ struct PlanData {
   alignas(64) CUtensorMap map_out;
   alignas(64) CUtensorMap map_sfa;  // CTA pairs: scale factors as 2 KB boxes per atom row
   alignas(64) CUtensorMap map_sfb;
+  alignas(64) ReturnMaps map_return;
 };
 static_assert(sizeof(PlanData) <= sizeof(lm_gemm_plan), "plan storage too small");
 constexpr uint32_t kPlanMagic = 0x4C4D4750u;
@@ -1556,7 +1588,7 @@ int launch_kernel(const PlanData& pd, cudaStream_t stream) {
     if (device >= 0 && device < kMaxDevices) configured[device] = true;
   }
   kernel<<<pd.grid, kThreads, smem_bytes(kOut), stream>>>(pd.map_a, pd.map_a64, pd.map_a32, pd.map_b,
-                                                          pd.map_out, pd.params);
+                                                          pd.map_out, pd.map_return, pd.params);
   note_launch();
   LM_CUDA(cudaGetLastError());
   return LM_OK;
@@ -1585,7 +1617,7 @@ int launch_pair(const PlanData& pd, cudaStream_t stream) {
   config.attrs = attr;
   config.numAttrs = 1;
   LM_CUDA(cudaLaunchKernelEx(&config, kernel, pd.map_a, pd.map_a64, pd.map_a32, pd.map_b, pd.map_out,
-                             pd.map_sfa, pd.map_sfb, pd.params));
+                             pd.map_sfa, pd.map_sfb, pd.map_return, pd.params));
   note_launch();
   return LM_OK;
 }
@@ -1671,6 +1703,20 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
     LM_REQUIRE(a->n % 8 == 0, "gemm: out_row_ptrs requires N to be a multiple of 8");
   }
   p.out_row_ptrs = a->out_row_ptrs;
+  if (a->out_blocks != nullptr) {
+    LM_REQUIRE(a->out_row_ptrs != nullptr, "gemm: out_blocks goes with out_row_ptrs");
+    LM_REQUIRE(a->return_bases != nullptr && a->return_world >= 1 && a->return_world <= LM_EP_MAX_RANKS &&
+                   a->return_rows > 0,
+               "gemm: out_blocks needs the return buffers of 1..8 ranks");
+    LM_REQUIRE(a->n >= 64, "gemm: out_blocks requires N of at least 64");
+    for (int g = 0; g < a->return_world; ++g) {
+      LM_REQUIRE((a->return_bases[g] & 15) == 0, "gemm: return buffers must be 16-byte aligned");
+      const int rc = encode_out_bf16(&pd.map_return.rank[g], reinterpret_cast<void*>(a->return_bases[g]),
+                                     static_cast<uint64_t>(a->n), static_cast<uint64_t>(a->return_rows));
+      if (rc != LM_OK) return rc;
+    }
+    p.out_blocks = a->out_blocks;
+  }
   p.clamp_limit = a->clamp_limit;
   p.sigmoid_alpha = a->sigmoid_alpha;
   p.up_bias = a->up_bias;

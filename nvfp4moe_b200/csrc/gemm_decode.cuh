@@ -285,20 +285,28 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < 16; ++s) {
-      mbar_init(smem_u32(&misc->full[s]), 1);
-      mbar_init(smem_u32(&misc->empty[s]), 1);
+  // One barrier per thread: a single thread initialising all 37 costs most of a microsecond,
+  // which counts in a step of a few dozen.
+  if (warp >= kDecFirstEpilogueWarp) {
+    const int t = threadIdx.x - 32 * kDecFirstEpilogueWarp;
+    if (t < 16) mbar_init(smem_u32(&misc->full[t]), 1);
+    else if (t < 32) mbar_init(smem_u32(&misc->empty[t - 16]), 1);
+    else if (t < 34) mbar_init(smem_u32(&misc->acc_full[t - 32]), 1);
+    else if (t < 36) mbar_init(smem_u32(&misc->acc_empty[t - 34]), 4);
+    else if (t == 36) mbar_init(smem_u32(&misc->drain), 1);
+    else if (t == 37) {
+      misc->abort_flag = 0;
+      misc->fills_issued = misc->fills_taken = 0;
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(&misc->acc_full[s]), 1);
-      mbar_init(smem_u32(&misc->acc_empty[s]), 4);
+    if (t < 37) {
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    mbar_init(smem_u32(&misc->drain), 1);
-    misc->abort_flag = 0;
-    misc->fills_issued = misc->fills_taken = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0 && lane < 3) {
+    // the descriptors the first copies need, fetched while the set-up runs
+    const CUtensorMap* map = lane == 0 ? &tmap_w : (lane == 1 ? &tmap_t8 : &tmap_w32);
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(

@@ -186,6 +186,13 @@ class GroupedNvfp4Gemm:
         # GPU's memory) instead of ``out``; the expert-parallel layer returns rows to their
         # source ranks this way.
         self.output_row_ptrs = None
+        # With ``output_row_ptrs``: whole 32-row blocks that the route plan's block table
+        # (``lm_ep_plan``) assigns to one rank leave as one bulk store into that rank's return
+        # buffer.  ``output_blocks`` = the int32 table, ``return_bases`` = a ctypes uint64 array of
+        # the ranks' return buffers, ``return_rows`` = rows of each of them.
+        self.output_blocks = None
+        self.return_bases = None
+        self.return_rows = 0
         self._plan = None
 
     def prepare(
@@ -290,6 +297,17 @@ class GroupedNvfp4Gemm:
                     or not output_row_ptrs.is_contiguous()):
                 raise ValueError(f"output_row_ptrs must be a contiguous int64 CUDA tensor of {rows} addresses")
             args.out_row_ptrs = output_row_ptrs.data_ptr()
+            if self.output_blocks is not None and not (self.swap_ab or self.direct_routes):
+                blocks = self.output_blocks
+                need = (rows // 128 + self.experts) * 4 * 2
+                if (not blocks.is_cuda or blocks.dtype != torch.int32 or blocks.numel() < need
+                        or not blocks.is_contiguous() or self.return_bases is None or self.return_rows <= 0):
+                    raise ValueError(f"output_blocks must be a contiguous int32 CUDA tensor of {need} entries "
+                                     "with return_bases and return_rows set")
+                args.out_blocks = blocks.data_ptr()
+                args.return_bases = ctypes.cast(self.return_bases, ctypes.POINTER(ctypes.c_uint64))
+                args.return_world = len(self.return_bases)
+                args.return_rows = int(self.return_rows)
         decode_shaped = self.swap_ab or self.direct_routes > 0
         args.swap_ab = int(decode_shaped)
         args.direct_routes = self.direct_routes
@@ -301,7 +319,8 @@ class GroupedNvfp4Gemm:
             _lib.check(_lib.lib().lm_gemm_prepare(ctypes.byref(args), ctypes.byref(plan)))
         self._plan = plan
         # keep operands alive for as long as the plan may launch
-        self._keepalive = (a, b, out, cu, sfa, sfb, alpha, output_sf, output_scale, output_row_ptrs)
+        self._keepalive = (a, b, out, cu, sfa, sfb, alpha, output_sf, output_scale, output_row_ptrs,
+                           self.output_blocks, self.return_bases)
 
     def launch(self):
         if self._plan is None:

@@ -1,8 +1,8 @@
-"""Expert-parallel layer on two GPUs (NCCL) against the single-GPU layer.
+"""Expert-parallel layer on two, four and eight GPUs (NCCL) against the single-GPU layer.
 
 Every exchanged row is computed by exactly one expert with the same packed
 operands and scales as on one GPU, and the combine order is fixed, so the
-two-rank result must equal the single-GPU result bit for bit.
+sharded result must equal the single-GPU result bit for bit.
 """
 
 import os
@@ -13,10 +13,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-pytestmark = [
-    pytest.mark.gpu,
-    pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs"),
-]
+pytestmark = [pytest.mark.gpu]
 
 HIDDEN, INTER, EXPERTS, TOPK, TOKENS = 512, 256, 16, 4, 384
 
@@ -95,12 +92,14 @@ def _worker(rank: int, world: int, port: int, results):
         dist.destroy_process_group()
 
 
-def test_two_rank_layer_equals_single_gpu_layer():
-    world = 2
+@pytest.mark.parametrize("world", (2, 4, 8))
+def test_sharded_layer_equals_single_gpu_layer(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     results = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
     for transport in ("peer", "collective"):
-        first, second = results[0][transport], results[1][transport]
-        assert first[:2] == (True, True) and first[3], transport
-        assert second[:2] == (True, True) and second[3], transport
-        assert first[2] + second[2] == 2 * TOKENS * TOPK, transport
+        for rank in range(world):
+            equal, stable, _, valid = results[rank][transport]
+            assert equal and stable and valid, (transport, rank)
+        assert sum(results[rank][transport][2] for rank in range(world)) == world * TOKENS * TOPK, transport

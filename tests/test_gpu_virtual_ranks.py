@@ -54,9 +54,11 @@ def test_route_plan_matches_restatement(world):
         start = torch.full((experts,), -1, dtype=torch.int32, device=dev)
         ptrs = torch.zeros(max_rows, dtype=torch.int64, device=dev)
         valid = torch.zeros(1, dtype=torch.int32, device=dev)
+        blocks = torch.full(((max_rows // 128 + local) * 4, 2), -9, dtype=torch.int32, device=dev)
         _lib.check(_lib.lib().lm_ep_plan(counts_dev.data_ptr(), world, rank, experts, max_rows, row_bytes,
                                          bases, own.data_ptr(), dest.data_ptr(), start.data_ptr(),
-                                         ptrs.data_ptr(), valid.data_ptr(), _lib.stream_handle()))
+                                         ptrs.data_ptr(), blocks.data_ptr(), valid.data_ptr(),
+                                         _lib.stream_handle()))
         torch.cuda.synchronize()
         own_r, dest_r, start_r, origin, owner_rows = O.ep_route_plan(counts.tolist(), rank)
         assert max(owner_rows) <= max_rows and int(valid) == 1
@@ -65,6 +67,19 @@ def test_route_plan_matches_restatement(world):
         assert start.tolist() == start_r
         expected = [((g_ + 1) << 32) + row * row_bytes for g_, row in origin]
         assert ptrs[: len(expected)].tolist() == expected
+        # block table: a 32-row block of a tile is marked with (rank, first row) exactly when its
+        # rows are 32 consecutive rows of one source, else -1; tiles start at atom row
+        # own_indptr[l] // 128 + l
+        table = blocks.cpu()
+        for l in range(local):
+            lo, hi = own_r[l], own_r[l + 1]
+            first_tile = lo // 128 + l
+            for b in range(-(-(hi - lo) // 128) * 4):
+                rows = origin[lo + 32 * b : min(lo + 32 * b + 32, hi)]
+                whole = (len(rows) == 32 and len({g_ for g_, _ in rows}) == 1
+                         and [r for _, r in rows] == list(range(rows[0][1], rows[0][1] + 32)))
+                want = [rows[0][0], rows[0][1]] if whole else [-1, 0]
+                assert table[first_tile * 4 + b].tolist() == want, (rank, l, b)
 
 
 def test_route_plan_flags_oversized_step():
@@ -79,7 +94,7 @@ def test_route_plan_flags_oversized_step():
     valid = torch.ones(1, dtype=torch.int32, device=dev)
     # rank 0 would receive 70 rows, the buffers hold 64
     _lib.check(_lib.lib().lm_ep_plan(counts.data_ptr(), 2, 1, 4, 64, 512, bases, own.data_ptr(),
-                                     other[0].data_ptr(), other[1].data_ptr(), ptrs.data_ptr(),
+                                     other[0].data_ptr(), other[1].data_ptr(), ptrs.data_ptr(), None,
                                      valid.data_ptr(), _lib.stream_handle()))
     torch.cuda.synchronize()
     assert int(valid) == 0
