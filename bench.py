@@ -366,6 +366,8 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
     name = args.workload
     s = _shape(name)
+    if args.tokens:
+        s["tokens"] = args.tokens
     hidden, inter, experts, k, tokens = s["hidden"], s["inter"], s["experts"], s["k"], s["tokens"]
     e_local = experts // world
     plan_kwargs = dict(activation=s["act"], activation_clamp=s["clamp"])
@@ -386,8 +388,7 @@ def run_ours(args):
         layer.calibrate(x, ids, w)
     else:
         layer = ExpertParallelMoE(hidden, inter, experts, k, tokens, group=None, device=device,
-                                  max_recv_rows=min(4 * tokens * k, world * tokens * k),
-                                  micro_batches=args.micro_batches, return_ctas=args.return_ctas, **plan_kwargs)
+                                  max_recv_rows=min(4 * tokens * k, world * tokens * k), **plan_kwargs)
         layer.load_weights(gate, up, down)
         # activations are N(0,1) and weights N(0,0.02) on every rank: fixed scales from rank-local data
         probe_tokens = min(1024, tokens)
@@ -495,10 +496,7 @@ def run_ours(args):
     extras = {}
     if world > 1:
         # per-phase device times (max over ranks) and the correctness of the sharded step
-        # (with micro-batches: the first part of the batch alone, nothing overlapping it)
-        timed = layer._parts[0] if layer._parts else layer
-        share = timed.max_tokens
-        phase_runs = [timed.run_phases(x[:share], ids[:share], w[:share])[0] for _ in range(5)]
+        phase_runs = [layer.run_phases(x, ids, w)[0] for _ in range(5)]
         names = list(phase_runs[0])
         med = torch.tensor([statistics.median(r[n] for r in phase_runs) for n in names], dtype=torch.float64,
                            device=device)
@@ -506,9 +504,7 @@ def run_ours(args):
         extras["phases_ms"] = {n: round(float(v), 4) for n, v in zip(names, med)}
         out = layer.run(x, ids, w)
         torch.cuda.synchronize()
-        plans = [part.local for part in layer._parts] or [layer.local]
-        recv = torch.tensor([float(sum(int(plan._m_indptr[-1]) for plan in plans))], dtype=torch.float64,
-                            device=device)
+        recv = torch.tensor([float(layer.local._m_indptr[-1])], dtype=torch.float64, device=device)
         recv_max, recv_sum = recv.clone(), recv.clone()
         dist.all_reduce(recv_max, op=dist.ReduceOp.MAX)
         dist.all_reduce(recv_sum, op=dist.ReduceOp.SUM)
@@ -520,12 +516,10 @@ def run_ours(args):
         return
 
     config = _config(name, world)
+    config["tokens_per_gpu"] = tokens
     config["l2"] = ("working set per step exceeds L2; no flush" if flush is None
                     else "512 MiB written between timed replays (the step's weights fit in L2)")
     config["launch"] = "cuda graph replay of one step"
-    if world > 1:
-        config["micro_batches"] = args.micro_batches
-        config["return_ctas"] = args.return_ctas
     config["empty_experts"] = int((counts == 0).sum())
     config["max_expert_share"] = round(float(counts.max()) / (tokens * k), 4)
     line = {
@@ -589,10 +583,7 @@ def main():
     parser.add_argument("--workload", default="c2",
                         choices=[n for n in WORKLOADS if n.startswith("c") and not n.endswith("_half")])
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    parser.add_argument("--micro-batches", type=int, default=1,
-                        help="N > 1: parts of the batch that run on streams of their own")
-    parser.add_argument("--return-ctas", type=int, default=0,
-                        help="N > 1: CTAs of the fc2 kernel that returns rows over NVLink (0 = all)")
+    parser.add_argument("--tokens", type=int, default=0, help="tokens per GPU instead of the workload's")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)

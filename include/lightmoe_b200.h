@@ -74,6 +74,7 @@ unsigned long long lm_launch_count(void);
  * *out == 0 means no kernel has reported a problem since the last lm_device_status_clear().
  */
 #define LM_STATUS_EP_TIMEOUT 16
+#define LM_STATUS_EP_OVERFLOW 32 /* lm_ep_plan: a rank would have received more rows than its buffers hold */
 int lm_device_status(uint32_t* out, lm_stream_t stream);
 int lm_device_status_clear(lm_stream_t stream);
 
@@ -111,6 +112,15 @@ int lm_quantize_decode(const void* x, int64_t tokens, int features, int top_k,
                        const int32_t* slots, const int32_t* topk_ids, const int32_t* m_indptr,
                        int experts, const float* scale_pair, uint8_t* q, uint8_t* sf,
                        lm_stream_t stream);
+
+/*
+ * Calibration: *out = max |act(preact)| over a BF16 first-projection result (rows, n), the
+ * activation applied in FP32 with exact exp / tanh; gated activations read (gate, up) from
+ * column pairs (2j, 2j+1).  Stands in for the torch chain of InferenceMoE.calibrate_routed
+ * (lightmoe/inference.py:763-779); the hidden scale is *out / 2688.  n must be a multiple of 8.
+ */
+int lm_activation_amax(const void* preact, int64_t rows, int n, int activation, float clamp_limit,
+                       float sigmoid_alpha, float up_bias, float* out, lm_stream_t stream);
 
 /*
  * Scratch size, in int32 elements, that lm_dispatch needs for `rows`
@@ -210,10 +220,13 @@ int lm_dispatch_static(const int32_t* topk_ids, const float* topk_weights, int64
  * Replaces moe_finalize (lightmoe/kernels/routing/combine.py:231-281).
  *   routed_out (rows, hidden) BF16; slots (tokens*top_k); weights (rows) or NULL
  *   out (tokens, hidden) BF16.  hidden must be a multiple of 8.
+ *   valid    optional device flag: when *valid == 0 the rows were not computed this step (an
+ *            expert-parallel step that lm_ep_plan skipped) and out is written as zeros
+ *   use_pdl  launch as a programmatic dependent of the previous kernel in the stream
  */
 int lm_finalize(const void* routed_out, const int32_t* slots, const float* weights, void* out,
                 int64_t tokens, int top_k, int hidden, int64_t routed_row_stride,
-                int64_t out_row_stride, lm_stream_t stream);
+                int64_t out_row_stride, const int32_t* valid, int use_pdl, lm_stream_t stream);
 
 /*
  * Grouped / dense block-scaled FP4 GEMM:  out[rows_e, :] = alpha_e * A_e @ B_e^T
@@ -291,6 +304,10 @@ typedef struct lm_gemm_plan {
 int lm_gemm_prepare(const lm_gemm_args* args, lm_gemm_plan* plan);
 /* Launches a prepared GEMM.  Safe inside CUDA Graph capture. */
 int lm_gemm_launch(const lm_gemm_plan* plan, lm_stream_t stream);
+/* What a prepared plan will launch: kernel 0 = 128 x 128 tiles, 1 = 128 x 256 tiles, 2 = 256 x 256
+   tiles on CTA pairs, 3 = the decode-shaped kernel; its grid; the depth of its operand ring
+   (the `stages` the reference's plans report, lightmoe/kernels/dense/runtime.py:88). */
+int lm_gemm_plan_info(const lm_gemm_plan* plan, int32_t* kernel, int32_t* grid, int32_t* ring_stages);
 
 /*
  * Router step in front of lm_dispatch: softmax over the experts, top-k, renormalise, as the

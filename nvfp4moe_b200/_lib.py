@@ -82,6 +82,7 @@ _SIGNATURES = {
         c_i32,
         [c_ptr, c_i64, c_i32, c_i32, c_ptr, c_ptr, c_ptr, c_i32, c_ptr, c_ptr, c_ptr, c_ptr],
     ),
+    "lm_activation_amax": (c_i32, [c_ptr, c_i64, c_i32, c_i32, c_f32, c_f32, c_f32, c_ptr, c_ptr]),
     "lm_route_topk": (c_i32, [c_ptr, c_i32, c_i64, c_i32, c_i32, c_ptr, c_ptr, c_ptr]),
     "lm_ep_plan": (
         c_i32,
@@ -119,9 +120,11 @@ _SIGNATURES = {
         c_i32,
         [c_ptr, c_ptr, c_i64, c_i32, c_i32, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i32, c_ptr],
     ),
-    "lm_finalize": (c_i32, [c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i32, c_i32, c_i64, c_i64, c_ptr]),
+    "lm_finalize": (c_i32, [c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i32, c_i32, c_i64, c_i64, c_ptr, c_i32, c_ptr]),
     "lm_gemm_prepare": (c_i32, [ctypes.POINTER(GemmArgs), ctypes.POINTER(GemmPlan)]),
     "lm_gemm_launch": (c_i32, [ctypes.POINTER(GemmPlan), c_ptr]),
+    "lm_gemm_plan_info": (c_i32, [ctypes.POINTER(GemmPlan), ctypes.POINTER(c_i32), ctypes.POINTER(c_i32),
+                                  ctypes.POINTER(c_i32)]),
 }
 
 
@@ -186,3 +189,13 @@ def device_status_clear() -> None:
 def launch_count() -> int:
     """Kernel launches made through the library so far in this process."""
     return int(lib().lm_launch_count())
+
+
+KERNEL_NAMES = ("128x128 tiles", "128x256 tiles", "256x256 tiles on CTA pairs", "decode-shaped")
+
+
+def plan_info(plan: GemmPlan) -> dict:
+    """Kernel, grid and ring depth a prepared GEMM plan launches with."""
+    kernel, grid, ring = c_i32(0), c_i32(0), c_i32(0)
+    check(lib().lm_gemm_plan_info(ctypes.byref(plan), ctypes.byref(kernel), ctypes.byref(grid), ctypes.byref(ring)))
+    return {"kernel": KERNEL_NAMES[kernel.value], "grid": grid.value, "stages": ring.value}

@@ -24,13 +24,17 @@ struct CombineParams {
   int64_t row_stride;
   int64_t out_stride;
   int vec_per_row;
+  const int32_t* valid;  // optional: 0 = the rows were not computed this step, write zeros
 };
 
 template <bool kWeighted>
 __global__ void __launch_bounds__(kThreads) combine_kernel(CombineParams p) {
+  // as a programmatic dependent the kernel may start while its predecessor drains
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t token = blockIdx.x;
   const int vec = blockIdx.y * kThreads + threadIdx.x;
   if (vec >= p.vec_per_row) return;
+  const bool live = p.valid == nullptr || __ldg(p.valid) != 0;
   const int col = vec * 8;
   float acc[8];
 #pragma unroll
@@ -38,7 +42,7 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(CombineParams p) {
 
   const int32_t* slot_ptr = p.slots + token * p.top_k;
   // Two gathers in flight: slot j+1 is loaded while slot j is accumulated.
-  int slot = __ldg(slot_ptr);
+  int slot = live ? __ldg(slot_ptr) : -1;
   uint4 cur = make_uint4(0, 0, 0, 0);
   float w = 0.0f;
   if (slot >= 0) {
@@ -50,7 +54,7 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(CombineParams p) {
     uint4 next = make_uint4(0, 0, 0, 0);
     float next_w = 0.0f;
     if (j + 1 < p.top_k) {
-      next_slot = __ldg(slot_ptr + j + 1);
+      next_slot = live ? __ldg(slot_ptr + j + 1) : -1;
       if (next_slot >= 0) {
         next = __ldg(reinterpret_cast<const uint4*>(p.rows + next_slot * p.row_stride + col));
         if (kWeighted) next_w = __ldg(p.weights + next_slot);
@@ -89,7 +93,8 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(CombineParams p) {
 
 extern "C" int lm_finalize(const void* routed_out, const int32_t* slots, const float* weights,
                            void* out, int64_t tokens, int top_k, int hidden,
-                           int64_t routed_row_stride, int64_t out_row_stride, lm_stream_t stream) {
+                           int64_t routed_row_stride, int64_t out_row_stride, const int32_t* valid,
+                           int use_pdl, lm_stream_t stream) {
   using namespace lm;
   LM_REQUIRE(routed_out && slots && out, "finalize: null pointer");
   LM_REQUIRE(hidden > 0 && hidden % 8 == 0, "finalize: hidden must be a multiple of 8");
@@ -100,15 +105,22 @@ extern "C" int lm_finalize(const void* routed_out, const int32_t* slots, const f
   if (tokens == 0) return LM_OK;
   CombineParams p{static_cast<const __nv_bfloat16*>(routed_out), slots, weights,
                   static_cast<__nv_bfloat16*>(out), tokens, top_k, hidden,
-                  routed_row_stride, out_row_stride, hidden / 8};
-  dim3 grid(static_cast<unsigned>(tokens), (p.vec_per_row + kThreads - 1) / kThreads);
+                  routed_row_stride, out_row_stride, hidden / 8, valid};
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>(tokens), (p.vec_per_row + kThreads - 1) / kThreads);
+  config.blockDim = dim3(kThreads);
+  config.stream = as_stream(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = use_pdl ? 1 : 0;
   if (weights != nullptr) {
-    combine_kernel<true><<<grid, kThreads, 0, as_stream(stream)>>>(p);
-    note_launch();
+    LM_CUDA(cudaLaunchKernelEx(&config, combine_kernel<true>, p));
   } else {
-    combine_kernel<false><<<grid, kThreads, 0, as_stream(stream)>>>(p);
-    note_launch();
+    LM_CUDA(cudaLaunchKernelEx(&config, combine_kernel<false>, p));
   }
+  note_launch();
   LM_CUDA(cudaGetLastError());
   return LM_OK;
 }

@@ -125,7 +125,10 @@ __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(PlanParams p) {
     // an oversized step computes nothing: empty experts, and the flag for the host
     for (int l = tid; l <= L; l += kPlanThreads)
       p.own_indptr[l] = !fits ? 0 : (l < L ? s_owner_start[p.rank * L + l] : s_owner_rows[p.rank]);
-    if (tid == 0) *p.valid = fits ? 1 : 0;
+    if (tid == 0) {
+      *p.valid = fits ? 1 : 0;
+      if (!fits) atomicOr(&g_ep_status, static_cast<uint32_t>(LM_STATUS_EP_OVERFLOW));
+    }
   }
   if (!fits) return;
   for (int seg = blockIdx.x; seg < L * G; seg += gridDim.x) {

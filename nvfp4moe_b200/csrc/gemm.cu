@@ -1803,6 +1803,28 @@ extern "C" int lm_gemm_launch(const lm_gemm_plan* plan, lm_stream_t stream) {
   return launch_plan(pd, as_stream(stream));
 }
 
+extern "C" int lm_gemm_plan_info(const lm_gemm_plan* plan, int32_t* kernel, int32_t* grid, int32_t* ring_stages) {
+  using namespace lm;
+  LM_REQUIRE(plan && kernel && grid && ring_stages, "gemm: null argument");
+  uint32_t magic;
+  memcpy(&magic, plan, sizeof(magic));
+  if (magic == kDecodePlanMagic) {
+    DecodePlanData dp;
+    memcpy(&dp, plan, sizeof(dp));
+    *kernel = 3;
+    *grid = dp.grid;
+    *ring_stages = dp.params.ring_stages;
+    return LM_OK;
+  }
+  PlanData pd;
+  memcpy(&pd, plan, sizeof(pd));
+  LM_REQUIRE(pd.magic == kPlanMagic, "gemm: plan was not prepared");
+  *kernel = pd.pair ? 2 : (pd.n_blocks == 2 ? 1 : 0);
+  *grid = pd.grid;
+  *ring_stages = pd.params.ring_stages;
+  return LM_OK;
+}
+
 extern "C" int lm_device_status(uint32_t* out, lm_stream_t stream) {
   using namespace lm;
   LM_REQUIRE(out, "device_status: null pointer");

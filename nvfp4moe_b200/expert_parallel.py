@@ -135,30 +135,16 @@ class ExpertParallelMoE:
     ``rank`` / ``world`` build a *virtual* rank that makes no ``torch.distributed`` call:
     several of them in one process, joined by :func:`connect_virtual_ranks`, run the
     peer transport on one GPU (tests, debugging).
-
-    ``micro_batches`` (peer transport, real ranks): the batch is cut into that many equal
-    parts, each with its own arena and signal pads, and the parts run on streams of their own.
-    The rows a rank returns cross NVLink inside the fc2 epilogue, which is bound by the link
-    (about 0.3 ms for 235 MB at eight ranks) while the tensor cores idle; with two parts the
-    return of one part overlaps the dispatch, send and fc1 of the other.  ``return_ctas``
-    limits the CTAs of every part's fc2 so that the other part's kernels find free SMs
-    (0 = all).  Every row is computed by the same kernels from the same operands, so the result
-    does not change by a bit.
     """
 
     def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top_k: int,
                  max_tokens: int, *, group=None, max_recv_rows: int | None = None,
                  device: torch.device | str = "cuda", transport: str | None = None,
                  rank: int | None = None, world: int | None = None, signals: str = "peer",
-                 signal_timeout_ms: int = 0, micro_batches: int = 1, return_ctas: int = 0, **plan_kwargs):
+                 signal_timeout_ms: int = 0, **plan_kwargs):
         from .inference import InferenceMoE
         from .kernels.routing.dispatch import MAX_ASSIGNMENTS, MoEDispatch
 
-        self.micro_batches = int(micro_batches)
-        self.return_ctas = int(return_ctas)
-        self._parts: list[ExpertParallelMoE] = []
-        if self.micro_batches < 1 or max_tokens % self.micro_batches:
-            raise ValueError("micro_batches must divide max_tokens")
         self.virtual = rank is not None
         if self.virtual:
             if world is None or not 0 <= rank < world or num_experts % world:
@@ -190,62 +176,31 @@ class ExpertParallelMoE:
         if max_recv_rows is None:
             max_recv_rows = min(self.world * rows, MAX_ASSIGNMENTS)
         self.max_recv_rows = max_recv_rows
+        # source side: sort local pairs by global expert
+        self.source = MoEDispatch(max_tokens, num_experts, top_k, device=self.device)
+        # owner side: a plan over the local experts whose "tokens" are received rows
+        self.local = InferenceMoE(hidden_size, intermediate_size, self.local_experts, 1,
+                                  max_recv_rows, device=self.device, **plan_kwargs)
         self._out = torch.empty(max_tokens, hidden_size, dtype=torch.bfloat16, device=self.device)
-        if self.micro_batches == 1:
-            # source side: sort local pairs by global expert
-            self.source = MoEDispatch(max_tokens, num_experts, top_k, device=self.device)
-            # owner side: a plan over the local experts whose "tokens" are received rows
-            self.local = InferenceMoE(hidden_size, intermediate_size, self.local_experts, 1,
-                                      max_recv_rows, device=self.device, **plan_kwargs)
-            self._ones = torch.ones(max_recv_rows, 1, dtype=torch.float32, device=self.device)
+        self._ones = torch.ones(max_recv_rows, 1, dtype=torch.float32, device=self.device)
         self.last_recv_rows = 0
         self.verify_splits = False  # collective transport: check the split lists across ranks first
         self._peer = None
-        if self.micro_batches > 1:
-            if transport != "peer" or self.virtual or self.world == 1:
-                raise ValueError("micro_batches needs the peer transport on real ranks")
-            part_rows = None if max_recv_rows is None else -(-self.max_recv_rows // self.micro_batches)
-            for _ in range(self.micro_batches):
-                self._parts.append(ExpertParallelMoE(
-                    hidden_size, intermediate_size, num_experts, top_k, max_tokens // self.micro_batches,
-                    group=group, max_recv_rows=part_rows, device=device, transport="peer", signals=signals,
-                    signal_timeout_ms=signal_timeout_ms, return_ctas=return_ctas, **plan_kwargs))
-            with torch.cuda.device(self.device):
-                self._part_streams = [torch.cuda.Stream() for _ in self._parts]
-                self._fork = torch.cuda.Event()
-                self._joins = [torch.cuda.Event() for _ in self._parts]
-            return
         if transport == "peer":
             self._build_peer_buffers()
 
     # weights and scales of the local expert shard: same calls as InferenceMoE
     def load_weights(self, *args):
-        if self._parts:
-            # packed once, shared by every part
-            first = self._parts[0].local.load_weights(*args)
-            for part in self._parts[1:]:
-                part.local.load_packed_weights(first.qb1, first.sfb1, first.p_w1, first.qb2, first.sfb2,
-                                               first.p_w2)
-            return self
         self.local.load_weights(*args)
         return self
 
     def load_packed_weights(self, *args):
-        for plan in ([part.local for part in self._parts] or [self.local]):
-            plan.load_packed_weights(*args)
+        self.local.load_packed_weights(*args)
         return self
 
     def set_activation_scales(self, input_scale, hidden_scale):
-        for plan in ([part.local for part in self._parts] or [self.local]):
-            plan.set_activation_scales(input_scale, hidden_scale)
+        self.local.set_activation_scales(input_scale, hidden_scale)
         return self
-
-    def __getattr__(self, name):
-        # with micro-batches the per-part members live in the parts; `local` (weights, scales)
-        # is the same for all of them
-        if name == "local" and self.__dict__.get("_parts"):
-            return self._parts[0].local
-        raise AttributeError(name)
 
     @property
     def output(self) -> torch.Tensor:
@@ -329,11 +284,12 @@ class ExpertParallelMoE:
                 fc2 = plan._new_gemm("fc2", m)
             fc1.prepare(peer["qx"], plan.qb1, qh, plan._m_indptr, peer["sfx"], plan.sfb1, plan._alpha1,
                         output_sf=sfh, output_scale=plan._h_scale)
+            # result rows go back from inside the fc2 epilogue: whole 32-row blocks of one source as
+            # bulk stores into that rank's return buffer, the rest row by row
             fc2.output_row_ptrs = peer["row_ptrs"]
             fc2.output_blocks = peer["out_blocks"]
             fc2.return_bases = peer["ret_base"]
             fc2.return_rows = self.max_tokens * self.topk
-            fc2.max_ctas = self.return_ctas
             fc2.prepare(qh, plan.qb2, plan._routed_out[:m], plan._m_indptr, sfh, plan.sfb2, plan._alpha2)
             peer["gemms"] = (fc1, fc2)
         return peer["gemms"]
@@ -389,8 +345,9 @@ class ExpertParallelMoE:
 
         tokens = self._ids.shape[0]
         output = self._out[:tokens] if out is None else out
+        # a step the route plan skipped (a rank would have overflowed) combines to zeros
         moe_finalize(self._peer["ret"][: tokens * self.topk], self.source.slots, output, self.topk,
-                     weights=self.source.ps)
+                     weights=self.source.ps, valid=self._peer["valid"])
         return output
 
     def _signal(self, m_indptr=None):
@@ -480,29 +437,7 @@ class ExpertParallelMoE:
     def step_is_valid(self) -> bool:
         """False when the last step was skipped because a rank would have received more than
         ``max_recv_rows`` rows (reads one flag from the device: a synchronisation)."""
-        if self._parts:
-            return all(part.step_is_valid() for part in self._parts)
         return self._peer is None or bool(self._peer["valid"].item())
-
-    @torch.no_grad()
-    def _run_parts(self, x, topk_ids, topk_weights, out):
-        """The micro-batches on their own streams, forked from and joined to the current one."""
-        tokens = x.shape[0]
-        if tokens != self.max_tokens:
-            raise ValueError("the token count must match the configured per-rank batch")
-        output = self._out[:tokens] if out is None else out
-        share = tokens // len(self._parts)
-        main = torch.cuda.current_stream(self.device)
-        self._fork.record(main)
-        for i, (part, stream) in enumerate(zip(self._parts, self._part_streams)):
-            rows = slice(i * share, (i + 1) * share)
-            stream.wait_event(self._fork)
-            with torch.cuda.stream(stream):
-                part._run_peer(x[rows], topk_ids[rows], topk_weights[rows], output[rows])
-                self._joins[i].record(stream)
-        for join in self._joins:
-            main.wait_event(join)
-        return output
 
     @torch.no_grad()
     def run(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
@@ -511,8 +446,6 @@ class ExpertParallelMoE:
         if self.transport == "peer":
             if self.virtual:
                 raise RuntimeError("virtual ranks are stepped together by run_virtual_ranks")
-            if self._parts:
-                return self._run_parts(x, topk_ids, topk_weights, out)
             return self._run_peer(x, topk_ids, topk_weights, out)
         return self._run_collective(x, topk_ids, topk_weights, out)
 

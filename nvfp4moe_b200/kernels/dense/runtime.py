@@ -25,14 +25,21 @@ class DenseNvfp4Gemm:
             raise ValueError("dense GEMM supports M tiles 128/256 and N tiles 64/128/192/256")
         if output_dtype not in (torch.bfloat16, torch.float32):
             raise ValueError("dense GEMM output must use BF16 or FP32")
+        if tile_n in (64, 192):
+            raise NotImplementedError("the kernels of this build have 128- and 256-column tiles; "
+                                      "tile_n 64 and 192 are not built")
         self.n = n
         self.k = k
         self.tile_m = tile_m
         self.tile_n = tile_n
         self.output_dtype = output_dtype
         self.device = torch.cuda.current_device()
-        self.stages = 6
         self._plan = None
+
+    @property
+    def stages(self) -> int:
+        """Depth of the operand ring of the prepared plan (0 before ``prepare``)."""
+        return 0 if self._plan is None else _lib.plan_info(self._plan)["stages"]
 
     def prepare(self, a, b, out, sfa, sfb, alpha):
         tensors = {"A": a, "B": b, "output": out, "SFA": sfa, "SFB": sfb, "alpha": alpha}
@@ -84,7 +91,8 @@ class DenseNvfp4Gemm:
     def launch(self):
         if self._plan is None:
             raise RuntimeError("prepare must run before launch")
-        _lib.check(_lib.lib().lm_gemm_launch(ctypes.byref(self._plan), _lib.stream_handle()))
+        with torch.cuda.device(self.device):  # the plan belongs to this device's context and stream
+            _lib.check(_lib.lib().lm_gemm_launch(ctypes.byref(self._plan), _lib.stream_handle()))
 
     def __call__(self, a, b, out, sfa, sfb, alpha):
         self.prepare(a, b, out, sfa, sfb, alpha)

@@ -322,10 +322,16 @@ class GroupedNvfp4Gemm:
         self._keepalive = (a, b, out, cu, sfa, sfb, alpha, output_sf, output_scale, output_row_ptrs,
                            self.output_blocks, self.return_bases)
 
+    @property
+    def stages(self) -> int:
+        """Depth of the operand ring of the prepared plan (0 before ``prepare``)."""
+        return 0 if self._plan is None else _lib.plan_info(self._plan)["stages"]
+
     def launch(self):
         if self._plan is None:
             raise RuntimeError("prepare must run before launch")
-        _lib.check(_lib.lib().lm_gemm_launch(ctypes.byref(self._plan), _lib.stream_handle()))
+        with torch.cuda.device(self.device):  # the plan belongs to this device's context and stream
+            _lib.check(_lib.lib().lm_gemm_launch(ctypes.byref(self._plan), _lib.stream_handle()))
 
     def __call__(self, a, b, out, cu, sfa, sfb, alpha, output_sf=None, output_scale=None,
                  preact=None, aux=None, decode_plan=None, gather_idx=None):

@@ -24,12 +24,15 @@ def moe_finalize(
     direct: bool = False,
     num_threads: int = 256,
     broadcast_slots: bool = False,
+    valid: Tensor | None = None,
 ) -> None:
     """out[t] = sum over this token's non-negative slots of yw rows (times weights).
 
-    ``tile_t``, ``n_frag``, ``num_threads``, ``use_pdl`` and ``broadcast_slots``
-    are scheduling knobs in the reference; the result does not depend on them
-    and this implementation ignores them.
+    ``tile_t``, ``n_frag``, ``num_threads`` and ``broadcast_slots`` are scheduling knobs of the
+    reference's kernel; the result does not depend on them and this kernel has no use for
+    them.  ``use_pdl`` launches the kernel as a programmatic dependent of the previous one.
+    ``valid`` (not in the reference): an int32 device flag; when it holds 0 the rows were not
+    computed this step and ``out`` is written as zeros.
     """
     assert yw.stride(-1) == 1 and out.stride(-1) == 1
     if yw.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
@@ -52,7 +55,7 @@ def moe_finalize(
     _lib.check(
         _lib.lib().lm_finalize(
             yw.data_ptr(), slots.data_ptr(), _lib.ptr(weights), out.data_ptr(), tokens, topk,
-            hidden, yw.stride(0), out.stride(0), _lib.stream_handle(),
+            hidden, yw.stride(0), out.stride(0), _lib.ptr(valid), int(bool(use_pdl)), _lib.stream_handle(),
         )
     )
 

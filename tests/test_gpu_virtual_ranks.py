@@ -100,6 +100,10 @@ def test_route_plan_flags_oversized_step():
     assert int(valid) == 0
     assert own.tolist() == [0, 0, 0]
     assert int(ptrs.abs().sum()) == 0
+    # the skipped step shows in the device status word until it is cleared
+    assert _lib.device_status() & 32
+    _lib.device_status_clear()
+    assert _lib.device_status() == 0
 
 
 @pytest.mark.parametrize(("world", "skew"), ((2, False), (4, False), (4, True), (8, False)))
@@ -201,10 +205,21 @@ def test_virtual_ranks_skip_an_oversized_step():
         w = torch.full((tokens, k), 0.5, device=dev)
         batches.append((torch.randn(tokens, hidden, device=dev).to(torch.bfloat16), ids, w))
     connect_virtual_ranks(layers)
-    run_virtual_ranks(layers, batches)
+    from nvfp4moe_b200 import _lib
+
+    _lib.device_status_clear()
+    for layer in layers:  # stale rows from an earlier step must not leak into the result
+        layer._peer["ret"].fill_(7.0)
+    outs = run_virtual_ranks(layers, batches)
     torch.cuda.synchronize()
     assert not layers[0].step_is_valid() and not layers[1].step_is_valid()
     assert layers[0].local._m_indptr.tolist() == [0] * 5
+    # the skipped step has a defined result (zeros) and shows in the device status word
+    for out in outs:
+        assert not out.any()
+    assert _lib.device_status() & 32
+    _lib.device_status_clear()
+    assert _lib.device_status() == 0
 
 
 @pytest.mark.parametrize("features", (256, 2048, 6144))
