@@ -18,34 +18,40 @@ _DEN = E4M3_MAX * F4_MAX  # 2688
 
 
 class TensorScale:
-    """Track amax and expose quantization / dequantization scale pairs."""
+    """An amax kept on the device and the quantization scale pair derived from it.
+
+    Mirrors ``TensorScale`` of the reference (``lightmoe/_quantization.py:14-67``): ``update``
+    and ``set_amax`` never read the device, ``pair`` is ``[pts, 1 / pts]`` with
+    ``pts = amax / 2688`` floored at the smallest normal FP32 (an all-zero tensor must not
+    produce an infinite reciprocal).  ``pts`` and ``inv_pts`` are views of ``pair``: a later
+    update shows through views taken earlier.
+    """
 
     def __init__(self, device="cuda", te_rht=False):
         if te_rht:
             raise NotImplementedError("the RHT scale convention belongs to the training path")
+        self.te_rht = False
+        self._ready = False
         self._amax = torch.zeros(1, dtype=torch.float32, device=device)
         self._pair = torch.empty(2, dtype=torch.float32, device=device)
-        self._ready = False
-        self.te_rht = False
+
+    @torch.no_grad()
+    def _publish(self, amax: torch.Tensor) -> None:
+        self._amax.copy_(amax.reshape(1))
+        torch.div(self._amax, _DEN, out=self._pair[:1])
+        self._pair[:1].clamp_(min=torch.finfo(torch.float32).tiny)
+        torch.reciprocal(self._pair[:1], out=self._pair[1:])
+        self._ready = True
 
     @torch.no_grad()
     def update(self, t: torch.Tensor):
         """Update amax without a host synchronization."""
-        mn, mx = torch.aminmax(t.detach())
-        self._amax.copy_(torch.maximum(mn.neg_(), mx).reshape(1).float())
-        self._refresh()
+        low, high = torch.aminmax(t.detach())
+        self._publish(torch.maximum(low.neg(), high).float())
 
     @torch.no_grad()
     def set_amax(self, amax: torch.Tensor):
-        self._amax.copy_(amax.reshape(1))
-        self._refresh()
-
-    @torch.no_grad()
-    def _refresh(self):
-        p = (self._amax / _DEN).clamp_(min=torch.finfo(torch.float32).tiny)
-        self._pair[0:1].copy_(p)
-        self._pair[1:2].copy_(1.0 / p)
-        self._ready = True
+        self._publish(amax.to(device=self._amax.device, dtype=torch.float32))
 
     @property
     def pair(self) -> torch.Tensor:

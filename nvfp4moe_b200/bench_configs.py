@@ -43,6 +43,15 @@ WORKLOADS = {
     "shard_deepseek_v4_flash": (4096, 2048, 8, 6, 8192, "swiglu", 10.0, "uniform", False),
     "shard_glm_5_2": (6144, 2048, 16, 8, 8192, "swiglu", None, "uniform", False),
     "shard_minimax_m3": (6144, 3072, 8, 4, 8192, "swiglu_oai", None, "uniform", False),
+    # the same shards at 1 and 128 tokens (the reference's layer table, BENCHMARKS.md:92-97)
+    "shard_qwen35_35b_m1": (2048, 512, 16, 8, 1, "swiglu", None, "uniform", True),
+    "shard_qwen35_35b_m128": (2048, 512, 16, 8, 128, "swiglu", None, "uniform", True),
+    "shard_deepseek_v4_flash_m1": (4096, 2048, 8, 6, 1, "swiglu", 10.0, "uniform", True),
+    "shard_deepseek_v4_flash_m128": (4096, 2048, 8, 6, 128, "swiglu", 10.0, "uniform", True),
+    "shard_glm_5_2_m1": (6144, 2048, 16, 8, 1, "swiglu", None, "uniform", True),
+    "shard_glm_5_2_m128": (6144, 2048, 16, 8, 128, "swiglu", None, "uniform", True),
+    "shard_minimax_m3_m1": (6144, 3072, 8, 4, 1, "swiglu_oai", None, "uniform", True),
+    "shard_minimax_m3_m128": (6144, 3072, 8, 4, 128, "swiglu_oai", None, "uniform", True),
     # half-size cases for profiler captures
     "c2_half": (2048, 512, 128, 8, 4096, "swiglu", None, "uniform", False),
     "shard_deepseek_v4_flash_half": (4096, 2048, 8, 6, 4096, "swiglu", 10.0, "uniform", False),
@@ -172,7 +181,92 @@ def run_steps(name: str, steps: int, virtual_ranks: bool = False) -> None:
     print("ok", float(plan.output[:tokens].float().abs().mean()))
 
 
+# GEMM-only cases: name -> (kind, experts, rows, n, k)
+GEMM_CASES = {
+    # the grouped GEMM correctness case: 8 experts (two of them empty), 512 rows, N 1024, K 2048
+    "c1": ("grouped", 8, 512, 1024, 2048),
+    "dense_8192x4096x4096": ("dense", 1, 8192, 4096, 4096),
+    "dense_8192x2048x6144": ("dense", 1, 8192, 2048, 6144),
+}
+
+
+def _gated(stats: dict, wall_us: float, repeat: list[float]) -> dict:
+    """The reference's two validity gates (benchmarks/nvfp4_gemm.py:385-449,934-959): host wall
+    time over CUDA-event time of the timed loop at most 1.5, and the medians of repeated
+    measurements within 5 % of one another."""
+    stats["host_wall_over_event"] = round(wall_us / max(stats["median_us"], 1e-9), 3)
+    spread = (max(repeat) - min(repeat)) / max(min(repeat), 1e-9)
+    stats["repeat_deviation_pct"] = round(100.0 * spread, 2)
+    stats["gates_pass"] = bool(stats["host_wall_over_event"] <= 1.5 and spread <= 0.05)
+    return stats
+
+
+def _timed_with_gates(replay) -> dict:
+    import time
+
+    stats = _timed(replay)
+    # wall clock of a loop of replays against its event time
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    start.record()
+    for _ in range(50):
+        replay()
+    stop.record()
+    stop.synchronize()
+    wall_us = (time.perf_counter() - t0) * 1e6 / 50
+    event_us = start.elapsed_time(stop) * 1e3 / 50
+    repeats = [statistics.median(_samples(replay, count=11, warmup=2)) for _ in range(3)]
+    stats = _gated(stats, wall_us * stats["median_us"] / max(event_us, 1e-9), repeats)
+    return stats
+
+
+def run_gemm(name: str) -> dict:
+    """One GEMM of GEMM_CASES through the public ``lightmoe.gemm`` calls: TFLOP/s counted as
+    2 * rows * N * K without padding."""
+    from nvfp4moe_b200 import gemm
+
+    kind, experts, rows, n, k = GEMM_CASES[name]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(0)
+    a = torch.randn(rows, k, generator=g, device=dev).to(torch.bfloat16)
+    if kind == "dense":
+        b = (torch.randn(n, k, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        qa, sfa, pa = gemm.quantize(a)
+        qb, sfb, pb = gemm.quantize(b)
+        out = torch.empty(rows, n, dtype=torch.bfloat16, device=dev)
+        plan = gemm.DenseGemm(n, k, 128, 256 if n % 256 == 0 else 128)
+        plan.prepare(qa, qb, out, sfa, sfb, (pa * pb).reshape(1))
+    else:
+        b = (torch.randn(experts, n, k, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        counts = torch.zeros(experts, dtype=torch.int64)
+        allowed = [e for e in range(experts) if e not in (3, 6)]
+        picks = torch.randint(0, len(allowed), (rows,), generator=torch.Generator().manual_seed(0))
+        for p in picks.tolist():
+            counts[allowed[p]] += 1
+        cu = torch.zeros(experts + 1, dtype=torch.int32)
+        cu[1:] = counts.cumsum(0)
+        qa, qb, sfa, sfb, alpha = gemm.quantize_grouped(a, b, cu.to(dev))
+        out = torch.empty(rows, n, dtype=torch.bfloat16, device=dev)
+        plan = gemm.GroupedGemm(experts, n, k, 128, 256 if n % 256 == 0 else 128)
+        plan.prepare(qa, qb, out, cu.to(dev), sfa, sfb, alpha)
+    plan.launch()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        plan.launch()
+    stats = _timed_with_gates(graph.replay)
+    stats["tflops"] = round(2.0 * rows * n * k / (stats["median_us"] * 1e-6) / 1e12, 1)
+    stats["pct_of_9000"] = round(stats["tflops"] / 90.0, 2)
+    from nvfp4moe_b200 import _lib
+
+    return {"workload": name, "kind": kind, "experts": experts, "rows": rows, "n": n, "k": k, "gemm": stats,
+            "kernel": _lib.plan_info(plan._plan), "device_status": _lib.device_status()}
+
+
 def run(name: str) -> dict:
+    if name in GEMM_CASES:
+        return run_gemm(name)
     hidden, inter, experts, k, tokens, act, clamp, routing, graph = WORKLOADS[name]
     unary = act == "relu2"
     plan, x, ids, w = build(name)
@@ -188,10 +282,11 @@ def run(name: str) -> dict:
     with torch.cuda.graph(cuda_graph):
         plan.run(x, ids, w)
     result["timed_as"] = "cuda graph replay"
-    result["layer"] = _timed(cuda_graph.replay)
+    result["layer"] = _timed_with_gates(cuda_graph.replay)
     result["tokens_per_s"] = round(tokens / (result["layer"]["median_us"] * 1e-6))
     decode = rows <= 16 * experts
-    ex = plan._full_execution(tokens, decode=decode)
+    ex = (plan._direct_execution() if (decode and tokens == 1 and k <= 32)
+          else plan._full_execution(tokens, decode=decode))
     n1 = inter if unary else 2 * inter
     for label, gemm, n, kk in (("fc1", ex.fc1, n1, hidden), ("fc2", ex.fc2, hidden, inter)):
         # one launch per graph: a replay costs the host a few microseconds, a launch through the
@@ -221,7 +316,7 @@ def main(argv):
             raise SystemExit("--steps takes exactly one workload name")
         run_steps(names[0], steps, virtual)
         return
-    names = argv or [n for n in WORKLOADS if not n.endswith("_half")]
+    names = argv or [n for n in list(WORKLOADS) + list(GEMM_CASES) if not n.endswith("_half")]
     for name in names:
         print(json.dumps(run(name)), flush=True)
         torch.cuda.empty_cache()

@@ -1,8 +1,8 @@
 // Deterministic top-k combine (HBM-bound gather-reduce).
 //
-// One thread owns eight BF16 columns (16 bytes) of one token: it walks the
-// token's slots in route order, keeps the FP32 sum in registers and stores the
-// BF16 result once.  The product with the routing weight is rounded before the
+// One thread owns eight BF16 columns (16 bytes) of one token: it loads the
+// token's rows eight routes at a time, adds them in route order to an FP32 sum in
+// registers and stores the BF16 result once.  The product with the routing weight is rounded before the
 // add (mul.rn then add.rn, never fused), so the result is independent of the
 // launch shape and bit-identical from run to run.
 #include "common.cuh"
@@ -41,42 +41,41 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(CombineParams p) {
   for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
 
   const int32_t* slot_ptr = p.slots + token * p.top_k;
-  // Two gathers in flight: slot j+1 is loaded while slot j is accumulated.
-  int slot = live ? __ldg(slot_ptr) : -1;
-  uint4 cur = make_uint4(0, 0, 0, 0);
-  float w = 0.0f;
-  if (slot >= 0) {
-    cur = __ldg(reinterpret_cast<const uint4*>(p.rows + slot * p.row_stride + col));
-    if (kWeighted) w = __ldg(p.weights + slot);
-  }
-  for (int j = 0; j < p.top_k; ++j) {
-    int next_slot = -1;
-    uint4 next = make_uint4(0, 0, 0, 0);
-    float next_w = 0.0f;
-    if (j + 1 < p.top_k) {
-      next_slot = live ? __ldg(slot_ptr + j + 1) : -1;
-      if (next_slot >= 0) {
-        next = __ldg(reinterpret_cast<const uint4*>(p.rows + next_slot * p.row_stride + col));
-        if (kWeighted) next_w = __ldg(p.weights + next_slot);
+  // Eight routes at a time: their slots, then their rows and weights, are loaded together and
+  // summed in route order afterwards, so a token costs two memory round trips per eight routes
+  // instead of two per route (a decode step is a handful of tokens: nothing else hides them).
+  constexpr int kBatch = 8;
+  for (int j0 = 0; j0 < p.top_k; j0 += kBatch) {
+    int slot[kBatch];
+    uint4 row[kBatch];
+    float w[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) slot[j] = (live && j0 + j < p.top_k) ? __ldg(slot_ptr + j0 + j) : -1;
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      row[j] = make_uint4(0, 0, 0, 0);
+      w[j] = 0.0f;
+      if (slot[j] >= 0) {
+        row[j] = __ldg(reinterpret_cast<const uint4*>(p.rows + slot[j] * p.row_stride + col));
+        if (kWeighted) w[j] = __ldg(p.weights + slot[j]);
       }
     }
-    if (slot >= 0) {
-      uint32_t words[4] = {cur.x, cur.y, cur.z, cur.w};
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (slot[j] < 0) continue;
+      const uint32_t words[4] = {row[j].x, row[j].y, row[j].z, row[j].w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float lo = __uint_as_float(words[i] << 16);
         float hi = __uint_as_float(words[i] & 0xFFFF0000u);
         if (kWeighted) {
-          lo = __fmul_rn(lo, w);
-          hi = __fmul_rn(hi, w);
+          lo = __fmul_rn(lo, w[j]);
+          hi = __fmul_rn(hi, w[j]);
         }
         acc[2 * i] = __fadd_rn(acc[2 * i], lo);
         acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], hi);
       }
     }
-    slot = next_slot;
-    cur = next;
-    w = next_w;
   }
   uint4 packed;
   uint32_t* pw = reinterpret_cast<uint32_t*>(&packed);

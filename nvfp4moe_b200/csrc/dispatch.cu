@@ -200,6 +200,9 @@ struct DecodePrepareParams {
 };
 
 __global__ void __launch_bounds__(kThreads) dispatch_quantize_decode_kernel(DecodePrepareParams p) {
+  // the first projection, launched as a programmatic dependent, may set itself up meanwhile
+  // (it waits for this kernel to finish before it reads anything)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   extern __shared__ int s_dyn[];
   const int E = p.d.experts;
   int* s_seg = s_dyn;
@@ -281,6 +284,9 @@ struct OneTokenParams {
 };
 
 __global__ void __launch_bounds__(kThreads) decode_prepare_one_kernel(OneTokenParams p) {
+  // the first projection, launched as a programmatic dependent, may set itself up meanwhile
+  // (it waits for this kernel to finish before it reads anything)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ int s_ids[32];
   __shared__ int s_dst[32];   // expert-major row of route r
   __shared__ int s_rank[32];  // its place among the routes of the same expert

@@ -11,8 +11,9 @@ combine.  Which kernels carry a step:
 
     prefill            two-launch dispatch, quantize-once-scatter, 128 x 256 tiles or CTA pairs
     decode (rows <= 16 per expert on average)
-                       fused dispatch + quantize (up to 1024 routes), the decode-shaped GEMM
-                       (weights on the 128-row side of the MMA) as programmatic dependents
+                       fused dispatch + quantize (up to 1024 routes); up to 128 routes the
+                       decode-shaped GEMM (weights on the 128-row side of the MMA) as programmatic
+                       dependents, beyond that 128 x 256 tiles
     one token          no dispatch at all: direct routes
 """
 
@@ -33,8 +34,8 @@ from .kernels.quantize.runtime import nvfp4_quantize_rowwise
 from .kernels.routing.combine import moe_finalize
 from .kernels.routing.dispatch import MAX_ASSIGNMENTS, moe_dispatch
 from .kernels.unary import UnaryEpilogue
-from .policy import (DECODE_ROWS_PER_EXPERT, FAST_DECODE_ROWS, FUSED_PREPARE_MAX_ROWS, _decode_tile_rows,  # noqa: F401
-                     _tile_m, _use_swapped_fc2, pick_tiles)
+from .policy import (DECODE_ROWS_PER_EXPERT, FAST_DECODE_ROWS, FUSED_PREPARE_MAX_ROWS, SWAPPED_MAX_ROWS,  # noqa: F401
+                     _decode_tile_rows, _tile_m, _use_swapped_fc2, pick_tiles)
 from .workspace import InferenceWorkspace
 
 _ACTIVATIONS = ("swiglu", "swiglu_oai", "geglu", "reglu", "relu2")
@@ -313,10 +314,10 @@ class InferenceMoE:
         fused = first and output_dtype == _FP4
         # decode steps keep the static schedule unless the caller asked otherwise
         schedule = False if (decode and self.use_dynamic_sched is None) else self.use_dynamic_sched
-        swapped = decode and self.tile_override is None
+        swapped = decode and self.tile_override is None and rows <= SWAPPED_MAX_ROWS
         if self.tile_override is not None:
             tile_m, tile_n = self.tile_override
-        elif decode:
+        elif swapped:
             # the decode-shaped kernel: weights on the 128-row side of the MMA
             tile_m, tile_n = 128, _decode_tile_rows(max(rows // self.topk, 1), self.hidden_size,
                                                     self.intermediate_size, self.experts)

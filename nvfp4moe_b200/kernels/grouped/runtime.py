@@ -97,59 +97,50 @@ class GroupedNvfp4Gemm:
         gather_b: bool = False,
     ):
         activation, dactivation = resolve_gemm_epilogue(epilogue, activation, dactivation)
-        save_preact = isinstance(epilogue, (GatedEpilogue, UnaryEpilogue)) and epilogue.save_preact
-        gated_policy = isinstance(epilogue, (GatedEpilogue, GatedBackwardEpilogue))
-        self.gated_clamp_limit = (
-            float(epilogue.clamp_limit) if gated_policy and epilogue.clamp_limit is not None else 0.0
-        )
-        self.activation_sigmoid_alpha = epilogue.sigmoid_alpha if gated_policy else 1.0
-        self.activation_up_bias = epilogue.up_bias if gated_policy else 0.0
         if epilogue is None and activation is not None:
             epilogue = UnaryEpilogue(activation) if activation == "relu2" else GatedEpilogue(activation)
-            if isinstance(epilogue, GatedEpilogue):
-                self.gated_clamp_limit = float(epilogue.clamp_limit or 0.0)
-                self.activation_sigmoid_alpha = epilogue.sigmoid_alpha
-                self.activation_up_bias = epilogue.up_bias
-        if experts <= 0 or n <= 0 or k <= 0:
-            raise ValueError("experts, N, and K must be positive")
-        if experts > 256:
-            raise ValueError("grouped GEMM supports at most 256 local experts")
-        if k % 64:
-            raise ValueError("grouped GEMM requires K aligned to 64")
-        if tile_m not in (128, 256) or tile_n < 8 or tile_n > 256 or tile_n % 8:
-            raise ValueError("grouped GEMM supports M=128/256 and N=8..256 aligned to 8")
-        if output_dtype not in (torch.bfloat16, torch.float32, torch.int32, torch.float4_e2m1fn_x2):
-            raise ValueError("grouped GEMM output must be BF16, FP32, Int32, or NVFP4")
-        activations = (None, "swiglu", "swiglu_oai", "geglu", "reglu", "relu2")
-        if activation not in activations:
-            raise ValueError("unsupported grouped GEMM activation")
-        if dactivation not in activations:
-            raise ValueError("unsupported grouped GEMM derivative")
-        if activation is not None and dactivation is not None:
-            raise ValueError("activation and dactivation are mutually exclusive")
-        if dactivation is not None or save_preact or output_dtype == torch.int32:
-            raise NotImplementedError("backward epilogues belong to the training path")
-        if output_dtype == torch.float4_e2m1fn_x2 and activation is None:
-            raise ValueError("NVFP4 output requires an activation epilogue")
-        if output_dtype == torch.float4_e2m1fn_x2 and n % 128:
-            raise ValueError("gated NVFP4 output requires N aligned to 128")
-        if activation is not None and output_dtype != torch.float4_e2m1fn_x2:
-            raise NotImplementedError("activation epilogues write NVFP4 in the inference path")
+        gated_policy = isinstance(epilogue, (GatedEpilogue, GatedBackwardEpilogue))
+        save_preact = isinstance(epilogue, (GatedEpilogue, UnaryEpilogue)) and epilogue.save_preact
+        self.gated_clamp_limit = float(epilogue.clamp_limit or 0.0) if gated_policy else 0.0
+        self.activation_sigmoid_alpha = epilogue.sigmoid_alpha if gated_policy else 1.0
+        self.activation_up_bias = epilogue.up_bias if gated_policy else 0.0
+
+        fp4 = torch.float4_e2m1fn_x2
+        known = (None, "swiglu", "swiglu_oai", "geglu", "reglu", "relu2")
         gated = activation is not None and activation != "relu2"
-        gated_tile = tile_m if swap_ab else tile_n
-        if gated and (n % 2 or gated_tile % 128):
-            axis = "tile_M" if swap_ab else "tile_N"
-            raise ValueError(f"gated GEMM requires even N and {axis} aligned to 128")
-        if swap_ab and activation is not None and tile_n > 64:
-            raise ValueError("operand-swapped activation GEMM requires tile_N at most 64")
-        self.experts = experts
-        self.n = n
-        self.k = k
-        self.tile_m = tile_m
-        self.tile_n = tile_n
+        # (failed, exception, message) in the order the reference checks them
+        # (lightmoe/kernels/grouped/runtime.py:226-290): its callers and tests meet the first
+        # message that applies
+        rules = (
+            (experts <= 0 or n <= 0 or k <= 0, ValueError, "experts, N, and K must be positive"),
+            (experts > 256, ValueError, "grouped GEMM supports at most 256 local experts"),
+            (k % 64, ValueError, "grouped GEMM requires K aligned to 64"),
+            (tile_m not in (128, 256) or not 8 <= tile_n <= 256 or tile_n % 8, ValueError,
+             "grouped GEMM supports M=128/256 and N=8..256 aligned to 8"),
+            (output_dtype not in (torch.bfloat16, torch.float32, torch.int32, fp4), ValueError,
+             "grouped GEMM output must be BF16, FP32, Int32, or NVFP4"),
+            (activation not in known, ValueError, "unsupported grouped GEMM activation"),
+            (dactivation not in known, ValueError, "unsupported grouped GEMM derivative"),
+            (activation is not None and dactivation is not None, ValueError,
+             "activation and dactivation are mutually exclusive"),
+            (dactivation is not None or save_preact or output_dtype == torch.int32, NotImplementedError,
+             "backward epilogues belong to the training path"),
+            (output_dtype == fp4 and activation is None, ValueError, "NVFP4 output requires an activation epilogue"),
+            (output_dtype == fp4 and n % 128, ValueError, "gated NVFP4 output requires N aligned to 128"),
+            (activation is not None and output_dtype != fp4, NotImplementedError,
+             "activation epilogues write NVFP4 in the inference path"),
+            (gated and (n % 2 or (tile_m if swap_ab else tile_n) % 128), ValueError,
+             f"gated GEMM requires even N and {'tile_M' if swap_ab else 'tile_N'} aligned to 128"),
+            (swap_ab and activation is not None and tile_n > 64, ValueError,
+             "operand-swapped activation GEMM requires tile_N at most 64"),
+        )
+        for failed, error, message in rules:
+            if failed:
+                raise error(message)
+        self.experts, self.n, self.k = experts, n, k
+        self.tile_m, self.tile_n = tile_m, tile_n
         self.output_dtype = output_dtype
-        self.activation = activation
-        self.dactivation = dactivation
+        self.activation, self.dactivation = activation, dactivation
         self.save_preact = save_preact
         self.epilogue = epilogue
         self.use_dynamic_sched = _resolve_dynamic_schedule(use_dynamic_sched, k)

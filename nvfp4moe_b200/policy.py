@@ -14,6 +14,12 @@ import math
 DECODE_ROWS_PER_EXPERT = 16  # a step with at most this many rows per expert on average is a decode step
 FAST_DECODE_ROWS = 64
 FUSED_PREPARE_MAX_ROWS = 1024  # dispatch + quantize in one launch up to this many routes
+# Decode steps of up to this many routes run on the decode-shaped GEMM (weights on the 128-row
+# side of the MMA, work dealt in quarter blocks); larger ones on 128 x 256 tiles.  Measured on
+# hidden 6144 / intermediate 2048 / 256 experts / top-8: 8 tokens 205 vs 220 us, 32 tokens 542 vs
+# 523 us, 64 tokens 739 vs 710 us: once every SM has several whole tiles, the wide tile streams
+# the weights a little faster, and the balance the decode-shaped kernel buys no longer matters.
+SWAPPED_MAX_ROWS = 128
 
 
 # ---- the reference's tables (pinned by tests/test_imports.py:36-40, tests/test_inference.py:310-323)
@@ -73,5 +79,6 @@ def pick_tiles(rows: int, experts: int, n: int, k: int, *, nvfp4_out: bool) -> t
     return (256 if pays else 128), 256
 
 
-__all__ = ["DECODE_ROWS_PER_EXPERT", "FAST_DECODE_ROWS", "FUSED_PREPARE_MAX_ROWS", "expected_padded_rows",
+__all__ = ["DECODE_ROWS_PER_EXPERT", "FAST_DECODE_ROWS", "FUSED_PREPARE_MAX_ROWS", "SWAPPED_MAX_ROWS",
+           "expected_padded_rows",
            "pick_tiles"]
