@@ -61,10 +61,21 @@ constexpr int kStoreBytes = kEpilogueWarps * kStoreBytesPerWarp;
 constexpr int kMiscBytes = 4096;
 constexpr int kSmemLimit = 232448;
 constexpr uint32_t kSfCol = 2 * kTileN;  // TMEM: two accumulators, then 32 columns per ring stage
-// TMEM with 256-column tiles: accumulator 0 at [0, 256), accumulator 1 at [160, 416), two
-// scale-factor slots of 48 columns from 416.  The accumulators share columns [160, 256).
-constexpr uint32_t kWideAcc1Col = 160;
-constexpr uint32_t kWideSfCol = 416;
+// TMEM with 256-column tiles: two 256-column accumulators and the scale factors do not fit in
+// 512 columns side by side, so the accumulators overlap, and the slices of a tile that touch the
+// overlap stand between the end of its MMAs and the start of the next tile's.
+//  * NVFP4 output: accumulator 0 at [0, 256), accumulator 1 at [192, 448), the scale factors of
+//    one stage in 48 columns from 448.  The overlap is exactly one 64-column slice (slice 3 of
+//    accumulator 0, slice 0 of accumulator 1), which one epilogue group owns.  (An accumulator
+//    that does not start on a multiple of 32 columns made every TMEM load slower.)
+//  * BF16 / FP32 output: accumulator 1 at [160, 416) and two scale-factor slots from 416 that
+//    alternate per stage: these kernels have short K loops and lost 5 % with a single slot;
+//    the overlap of 96 columns touches two slices, one per epilogue group.
+__host__ __device__ constexpr uint32_t wide_acc1_col(int out_kind) { return out_kind == LM_OUT_NVFP4 ? 192 : 160; }
+__host__ __device__ constexpr uint32_t wide_sf_col(int out_kind) { return out_kind == LM_OUT_NVFP4 ? 448 : 416; }
+__host__ __device__ constexpr uint32_t wide_sf_slots(int out_kind) { return out_kind == LM_OUT_NVFP4 ? 1 : 2; }
+// epilogue warps of one CTA that arrive on `shared_cols_free` per tile
+__host__ __device__ constexpr uint32_t wide_shared_owners(int out_kind) { return out_kind == LM_OUT_NVFP4 ? 4 : 8; }
 constexpr uint32_t kWideSfSlotCols = 48;
 static_assert(kSlotBytes % 1024 == 0, "operand slots must keep 1024-byte alignment");
 static_assert(kSfCol + kMaxRing * 32 <= kTmemCols, "TMEM budget");
@@ -360,8 +371,13 @@ __device__ __forceinline__ float gated_value(float g, float u, float clamp_limit
     u = fmaxf(fminf(u, clamp_limit), -clamp_limit);
   }
   if (kAct == LM_ACT_SWIGLU || kAct == LM_ACT_SWIGLU_OAI) {
-    float sig;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(sig) : "f"(1.0f + __expf(-sigmoid_alpha * g)));
+    // exp(-a g) as fast-math exp computes it, 2^(x log2 e) with both roundings.  The flushing
+    // form of ex2 only differs where the result is a denormal, which the add of 1 absorbs, and
+    // it spares the scaling instructions around the plain form; plain swiglu has a = 1.
+    const float x = kAct == LM_ACT_SWIGLU ? -g : -sigmoid_alpha * g;
+    float e, sig;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(sig) : "f"(1.0f + e));
     return g * sig * (u + up_bias);
   }
   if (kAct == LM_ACT_GEGLU) {
@@ -372,6 +388,14 @@ __device__ __forceinline__ float gated_value(float g, float u, float clamp_limit
     return 0.5f * g * (1.0f + th) * u;
   }
   return fmaxf(g, 0.0f) * u;  // reglu
+}
+
+// Two FP32 products in one instruction (round to nearest, as two separate multiplies give).
+__device__ __forceinline__ void mul_pair(float& a, float& b, float s) {
+  asm("{\n\t.reg .b64 v, f;\n\tmov.b64 v, {%0, %1};\n\tmov.b64 f, {%2, %2};\n\t"
+      "mul.rn.f32x2 v, v, f;\n\tmov.b64 {%0, %1}, v;\n\t}"
+      : "+f"(a), "+f"(b)
+      : "f"(s));
 }
 
 // Requantize 16 post-activation values: returns the E4M3 byte, packs 8 bytes.
@@ -386,7 +410,11 @@ __device__ __forceinline__ uint32_t requant16(const float* h, float inv_pts, uin
   rescale = fminf(rescale * inv_pts, kFltMax);
   float s[16];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) s[i] = h[i] * rescale;
+  for (int i = 0; i < 16; i += 2) {
+    s[i] = h[i];
+    s[i + 1] = h[i + 1];
+    mul_pair(s[i], s[i + 1], rescale);
+  }
   packed[0] = f32x8_to_e2m1(s);
   packed[1] = f32x8_to_e2m1(s + 8);
   return sf;
@@ -440,11 +468,38 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
   const int64_t out_row = static_cast<int64_t>(t.row0) + quarter * 32 + lane;
   const uint32_t taddr = lane_base + acc * (kNB == 1 ? kTileN : c.acc1_col);
 
-  // Software pipeline over the four 32-column chunks of the warp's two slices: while
-  // a chunk is converted, the load of the chunk after next is in flight (a TMEM load
-  // takes several hundred cycles from issue to data).
-  const int slice0 = kNB == 1 ? 0 : ((acc == 0) ? 2 + group : group);
-  const int slice1 = kNB == 1 ? 1 : ((acc == 0) ? group : 2 + group);
+  // The 64-column slices this warp drains, first to last, four bits each.  With 256-column
+  // tiles the MMAs of the next tile wait until the slices that touch the columns the other
+  // accumulator also uses are in registers.
+  //  * NVFP4 output: the gated activation and the requantization keep the warps of both groups
+  //    busy on the special-function unit of their scheduler for most of a tile's duration, and
+  //    a warp that is still converting the previous tile cannot release the next one.  So group
+  //    1 drains nothing but the shared slice (it is idle again long before the next tile ends)
+  //    and group 0 the other three; the conversion work of a scheduler is the same as with an
+  //    even split, since both of its epilogue warps feed the same unit.
+  //  * BF16 / FP32 output (staging and stores, bound per warp): two slices each, the one that
+  //    touches the overlap first.
+  constexpr bool kUneven = kNB == 2 && kOut == LM_OUT_NVFP4;
+  uint32_t slices = 0;  // uneven split only
+  int count = 2;
+  bool owns_shared = kNB == 2;
+  int first;
+  if (kUneven) {
+    if (group == 1) {
+      slices = acc == 0 ? 0x3u : 0x0u;
+      count = 1;
+    } else {
+      slices = acc == 0 ? 0x210u : 0x321u;
+      count = 3;
+      owns_shared = false;
+    }
+    first = static_cast<int>(slices & 0xFu);
+  } else {
+    // 128-column tiles: slices 0 and 1.  256-column tiles: the overlap touches slices 2 and 3 of
+    // accumulator 0 and slices 0 and 1 of accumulator 1; group g takes slices g and g + 2.
+    first = kNB == 1 ? 0 : ((acc == 0) ? 2 + group : group);
+  }
+  auto slice_at = [&](int s) { return static_cast<int>((slices >> (4 * s)) & 0xFu); };
   const bool rows_any = t.valid > quarter * 32;  // this warp owns at least one valid row
   // rows may live anywhere (another GPU's buffer): lane l holds the address of row l
   unsigned long long row_base = 0;
@@ -471,14 +526,19 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
     }
   }
   uint32_t va[32], vb[32];
-  tc_load32(taddr + slice0 * 64, va);
-  tc_load32(taddr + slice0 * 64 + 32, vb);
+  int cur = first;
+  tc_load32(taddr + cur * 64, va);
+  tc_load32(taddr + cur * 64 + 32, vb);
   tc_wait_ld_regs(va);
   tc_wait_ld_regs(vb);
-  // slice 0 is in registers: the columns shared with the other accumulator are free
+  // the first slice is in registers: if it is the shared one, the next tile's MMAs may start;
+  // if it is the only one, the warp is done reading the accumulator
   tc_fence_before();
   __syncwarp();
-  if (kNB == 2 && lane == 0) signal_barrier(c.bar_shared_cols, c.remote);
+  if (lane == 0) {
+    if (kNB == 2 && owns_shared) signal_barrier(c.bar_shared_cols, c.remote);
+    if (count == 1) signal_barrier(c.bar_acc_empty, c.remote);
+  }
 
   // ---- per-slice state and the two halves of the work
   constexpr bool kGated = kAct != LM_ACT_RELU2;
@@ -492,9 +552,11 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
         // 32 accumulator columns = 16 (gate, up) pairs -> 16 outputs: 8 bytes, one factor
         float h[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          h[i] = gated_value<kAct>(__uint_as_float(v[2 * i]) * alpha, __uint_as_float(v[2 * i + 1]) * alpha,
-                                   p.clamp_limit, p.sigmoid_alpha, p.up_bias);
+        for (int i = 0; i < 16; ++i) {
+          float g = __uint_as_float(v[2 * i]), u = __uint_as_float(v[2 * i + 1]);
+          mul_pair(g, u, alpha);
+          h[i] = gated_value<kAct>(g, u, p.clamp_limit, p.sigmoid_alpha, p.up_bias);
+        }
         const uint32_t sf = requant16(h, inv_h, &q[2 * half]);
         sfw = half == 0 ? sf : (sfw | (sf << 8));
       } else {
@@ -601,22 +663,36 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
     }
   };
 
-  const int col_a = nt * 2 * kNB + slice0;
-  const int col_b = nt * 2 * kNB + slice1;
-  convert(va, 0, col_a);
-  tc_load32(taddr + slice1 * 64, va);
-  convert(vb, 1, col_a);
-  tc_load32(taddr + slice1 * 64 + 32, vb);
-  finish(col_a);
-  tc_wait_ld_regs(va);
-  tc_wait_ld_regs(vb);
-  // the whole accumulator has been read
-  tc_fence_before();
-  __syncwarp();
-  if (lane == 0) signal_barrier(c.bar_acc_empty, c.remote);
-  convert(va, 0, col_b);
-  convert(vb, 1, col_b);
-  finish(col_b);
+  // Software pipeline over the 32-column halves of the slices: while a half is converted, the
+  // load of the half after next is in flight (a TMEM load takes several hundred cycles from
+  // issue to data).
+  auto step = [&](const bool more, const bool last_load, const int next) {
+    const int col = nt * 2 * kNB + cur;
+    convert(va, 0, col);
+    if (more) tc_load32(taddr + next * 64, va);
+    convert(vb, 1, col);
+    if (more) tc_load32(taddr + next * 64 + 32, vb);
+    finish(col);
+    if (more) {
+      tc_wait_ld_regs(va);
+      tc_wait_ld_regs(vb);
+      if (last_load) {
+        // the warp's last slice is in registers: it has read all it reads of the accumulator
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) signal_barrier(c.bar_acc_empty, c.remote);
+      }
+      cur = next;
+    }
+  };
+  if (!kUneven) {
+    // always two slices: straight-line code
+    step(true, true, kNB == 1 ? 1 : ((acc == 0) ? group : 2 + group));
+    step(false, false, 0);
+  } else {
+#pragma unroll 1
+    for (int s = 0; s < count; ++s) step(s + 1 < count, s + 2 == count, s + 1 < count ? slice_at(s + 1) : 0);
+  }
 }
 
 // Shared-memory descriptor of one 512-byte scale-factor atom: 32 rows of 16 bytes, no swizzle,
@@ -642,10 +718,10 @@ __device__ __forceinline__ void tc_copy_sf(uint32_t taddr, uint64_t sdesc) {
 //    stage; epilogue group g drains accumulator g (every other tile).
 // 2: 128 x 256 tiles, which move a quarter less data through shared memory per FLOP (the
 //    resource that binds the main loop).  Two 256-column accumulators and the scale factors
-//    do not fit in 512 TMEM columns side by side, so the accumulators overlap in 96 columns:
-//    both epilogue groups work on every tile, read the 64-column slices that touch the
-//    overlap first and signal `shared_cols_free`; the MMAs of the next tile start then, while
-//    the rest of the tile is still being converted and stored.
+//    do not fit in 512 TMEM columns side by side, so the accumulators overlap in 48 columns:
+//    both epilogue groups work on every tile, the owner of the 64-column slice that touches
+//    the overlap reads it first and signals `shared_cols_free`; the MMAs of the next tile
+//    start then, while the rest of the tile is still being converted and stored.
 template <int kOut, int kAct, int kNB>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64,
@@ -686,7 +762,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       mbar_init(smem_u32(&misc->acc_full[s]), 1);
       mbar_init(smem_u32(&misc->acc_empty[s]), kNB == 1 ? 4 : 8);
     }
-    mbar_init(smem_u32(&misc->shared_cols_free), 8);
+    mbar_init(smem_u32(&misc->shared_cols_free), wide_shared_owners(kOut));
     mbar_init(smem_u32(&misc->drain), 1);
     misc->abort_flag = 0;
     misc->fills_issued = misc->fills_taken = misc->a_fills_issued = misc->a_fills_taken = 0;
@@ -816,7 +892,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else if (warp == 1) {
     // ===================================================== MMA issuer
     constexpr uint32_t idesc = make_idesc(kNB * kTileN);
-    uint32_t sf_slot = 0;  // 256-column tiles: scale-factor slot, alternates per stage
+    uint32_t sf_slot = 0;  // 256-column tiles with two scale-factor slots: alternates per stage
     int stage = 0;
     uint32_t phase = 0;
     uint32_t a_phase = 0;
@@ -832,7 +908,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           ok = mbar_wait(smem_u32(&misc->shared_cols_free), (it - 1) & 1u, abort_flag, kStatusMmaTimeout);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * (kNB == 1 ? kTileN : kWideAcc1Col);
+        const uint32_t d_tmem = tmem_base + acc * (kNB == 1 ? kTileN : wide_acc1_col(kOut));
         for (int ks = 0; ks < p.k_stages; ++ks) {
           ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusMmaTimeout);
           if (ok) ++taken;
@@ -846,9 +922,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const uint32_t b_smem = ring_base + stage * ring_stride;
           const uint32_t a_smem = resident ? smem_base + ks * kSlotBytes : b_smem + kAOffset;
           const uint32_t sfa_t =
-              tmem_base + (kNB == 1 ? kSfCol + stage * 32 : kWideSfCol + sf_slot * kWideSfSlotCols);
+              tmem_base + (kNB == 1 ? kSfCol + stage * 32 : wide_sf_col(kOut) + sf_slot * kWideSfSlotCols);
           const uint32_t sfb_t = sfa_t + 16;
-          sf_slot ^= 1u;
+          if (wide_sf_slots(kOut) == 2) sf_slot ^= 1u;
           const uint64_t a_desc = desc_sw128(a_smem);
           const uint64_t b_desc = desc_sw128(b_smem);
           const uint64_t sfa_desc = desc_sf_atom(a_smem + kTileBytes);
@@ -894,8 +970,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // ===================================================== epilogue
     // Two groups of four warps.  The unit of work is a 64-column slice of an accumulator:
     // 128-column tiles: group g drains accumulator g (every other tile), slices 0 and 1;
-    // 256-column tiles: both groups work on every tile, group g on slices g and g + 2, and
-    // take the slice that touches the columns shared with the other accumulator first.
+    // 256-column tiles: both groups work on every tile (`drain_tile` has the split).
     const int group = (warp - kFirstEpilogueWarp) >> 2;
     DrainContext ctx;
     ctx.group = group;
@@ -907,7 +982,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     ctx.return_maps = &tmap_return;
     ctx.bar_shared_cols = smem_u32(&misc->shared_cols_free);
     ctx.remote = false;
-    ctx.acc1_col = kWideAcc1Col;
+    ctx.acc1_col = wide_acc1_col(kOut);
     ctx.inv_h = kOut == LM_OUT_NVFP4 ? __ldg(p.out_scale + 1) : 0.0f;
     TileWalker walker;
     int it = 0;
@@ -977,10 +1052,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 //               peer's TMA loads name the leader's barrier), so scale factors come through
 //               tensor maps here as well (eight-byte elements, boxes of 2 KB per atom row).
 //   empty[s], acc_full[a]  local in both CTAs, signalled by multicast tcgen05.commit.
-//   acc_empty[a], shared_cols_free  leader's; the sixteen epilogue warps of both CTAs arrive.
+//   acc_empty[a]                    leader's; the sixteen epilogue warps of both CTAs arrive.
+//   shared_cols_free                leader's; the eight warps that own the shared slice arrive.
 constexpr int kPairStageBytes = 2 * kTileBytes + 3 * kSfBytes;  // B half, SFB x2, A, SFA = 38912
-// TMEM of a pair CTA: as for 128 x 256 tiles (accumulators at 0 and kWideAcc1Col, two
-// scale-factor slots from kWideSfCol).
+// TMEM of a pair CTA: as for 128 x 256 tiles (`wide_acc1_col` and its neighbours).
 static_assert(kPairStageBytes % 1024 == 0, "pair ring stages must keep 1024-byte alignment");
 // The pair's ring is cut from the raw shared-memory budget, not from 18 KB operand slots: five
 // stages fit with either output kind (with BF16 staging they fill the 227 KB exactly).
@@ -1109,7 +1184,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       mbar_init(smem_u32(&misc->acc_full[s]), 1);
       mbar_init(smem_u32(&misc->acc_empty[s]), 16);
     }
-    mbar_init(smem_u32(&misc->shared_cols_free), 16);
+    mbar_init(smem_u32(&misc->shared_cols_free), 2 * wide_shared_owners(kOut));  // both CTAs' owners
     mbar_init(smem_u32(&misc->drain), 1);
     misc->abort_flag = 0;
     misc->fills_issued = misc->fills_taken = 0;
@@ -1245,7 +1320,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             ok = mbar_wait(smem_u32(&misc->shared_cols_free), (it - 1) & 1u, abort_flag, kStatusMmaTimeout);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base + acc * kWideAcc1Col;
+          const uint32_t d_tmem = tmem_base + acc * wide_acc1_col(kOut);
           for (int ks = 0; ks < p.k_stages; ++ks) {
             ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusMmaTimeout);
             if (!ok) break;
@@ -1253,9 +1328,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tc_fence_after();
             const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
             const uint32_t stage_smem = smem_base + stage * kPairStageBytes;
-            const uint32_t sfa_t = tmem_base + kWideSfCol + sf_slot * kWideSfSlotCols;
+            const uint32_t sfa_t = tmem_base + wide_sf_col(kOut) + sf_slot * kWideSfSlotCols;
             const uint32_t sfb_t = sfa_t + 16;
-            sf_slot ^= 1u;
+            if (wide_sf_slots(kOut) == 2) sf_slot ^= 1u;
             const uint64_t a_desc = desc_sw128(stage_smem + kOffA);
             const uint64_t b_desc = desc_sw128(stage_smem + kOffB);
             const uint64_t sfa_desc = desc_sf_atom(stage_smem + kOffSfa);
@@ -1303,7 +1378,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     ctx.out_map = &tmap_out;
     ctx.return_maps = &tmap_return;
     ctx.remote = !leader;
-    ctx.acc1_col = kWideAcc1Col;
+    ctx.acc1_col = wide_acc1_col(kOut);
     const uint32_t cols_bar = smem_u32(&misc->shared_cols_free);
     ctx.bar_shared_cols = leader ? cols_bar : map_to_cta(cols_bar, 0);
     ctx.inv_h = kOut == LM_OUT_NVFP4 ? __ldg(p.out_scale + 1) : 0.0f;
