@@ -23,6 +23,7 @@ from __future__ import annotations
 import json
 import statistics
 import sys
+import time
 
 import torch
 
@@ -320,6 +321,10 @@ def main(argv):
     for name in names:
         print(json.dumps(run(name)), flush=True)
         torch.cuda.empty_cache()
+        # every workload starts from an idle GPU, as if it ran in a process of its own: right
+        # after a long prefill workload the clocks stay at the power-capped level for a while,
+        # and a step of 20 us measured then came out 40 % slower than the same step alone
+        time.sleep(2.0)
 
 
 if __name__ == "__main__":

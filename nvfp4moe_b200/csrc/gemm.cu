@@ -62,21 +62,15 @@ constexpr int kMiscBytes = 4096;
 constexpr int kSmemLimit = 232448;
 constexpr uint32_t kSfCol = 2 * kTileN;  // TMEM: two accumulators, then 32 columns per ring stage
 // TMEM with 256-column tiles: two 256-column accumulators and the scale factors do not fit in
-// 512 columns side by side, so the accumulators overlap, and the slices of a tile that touch the
-// overlap stand between the end of its MMAs and the start of the next tile's.
-//  * NVFP4 output: accumulator 0 at [0, 256), accumulator 1 at [192, 448), the scale factors of
-//    one stage in 48 columns from 448.  The overlap is exactly one 64-column slice (slice 3 of
-//    accumulator 0, slice 0 of accumulator 1), which one epilogue group owns.  (An accumulator
-//    that does not start on a multiple of 32 columns made every TMEM load slower.)
-//  * BF16 / FP32 output: accumulator 1 at [160, 416) and two scale-factor slots from 416 that
-//    alternate per stage: these kernels have short K loops and lost 5 % with a single slot;
-//    the overlap of 96 columns touches two slices, one per epilogue group.
-__host__ __device__ constexpr uint32_t wide_acc1_col(int out_kind) { return out_kind == LM_OUT_NVFP4 ? 192 : 160; }
-__host__ __device__ constexpr uint32_t wide_sf_col(int out_kind) { return out_kind == LM_OUT_NVFP4 ? 448 : 416; }
-__host__ __device__ constexpr uint32_t wide_sf_slots(int out_kind) { return out_kind == LM_OUT_NVFP4 ? 1 : 2; }
-// epilogue warps of one CTA that arrive on `shared_cols_free` per tile
-__host__ __device__ constexpr uint32_t wide_shared_owners(int out_kind) { return out_kind == LM_OUT_NVFP4 ? 4 : 8; }
-constexpr uint32_t kWideSfSlotCols = 48;
+// 512 columns side by side, so the accumulators overlap: accumulator 0 at [0, 256), accumulator
+// 1 at [192, 448), the scale factors of one stage in 48 columns from 448.  The overlap is
+// exactly one 64-column slice (slice 3 of accumulator 0, slice 0 of accumulator 1): it alone
+// stands between the end of a tile's MMAs and the start of the next tile's, and four epilogue
+// warps own it.  (An accumulator that does not start on a multiple of 32 columns made every
+// TMEM load slower.)
+constexpr uint32_t kWideAcc1Col = 192;
+constexpr uint32_t kWideSfCol = 448;
+constexpr uint32_t kWideSharedOwners = 4;  // epilogue warps of one CTA that arrive on `shared_cols_free`
 static_assert(kSlotBytes % 1024 == 0, "operand slots must keep 1024-byte alignment");
 static_assert(kSfCol + kMaxRing * 32 <= kTmemCols, "TMEM budget");
 
@@ -120,6 +114,7 @@ struct GemmParams {
   const uint64_t* out_row_ptrs;  // BF16 output: optional address of every output row
   const int32_t* out_blocks;     // with out_row_ptrs: (tile atom row * 4 + quarter) -> {rank, first row} or -1
   int tma_store;                 // BF16 output: whole 32-row blocks leave through TMA stores
+  int uneven;                    // BF16 / FP32 output, 256-column tiles: uneven split of the epilogue
   int out_atom_cols;  // NVFP4 output: out_n / 64
   float clamp_limit;
   float sigmoid_alpha;
@@ -469,36 +464,39 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
   const uint32_t taddr = lane_base + acc * (kNB == 1 ? kTileN : c.acc1_col);
 
   // The 64-column slices this warp drains, first to last, four bits each.  With 256-column
-  // tiles the MMAs of the next tile wait until the slices that touch the columns the other
-  // accumulator also uses are in registers.
-  //  * NVFP4 output: the gated activation and the requantization keep the warps of both groups
-  //    busy on the special-function unit of their scheduler for most of a tile's duration, and
-  //    a warp that is still converting the previous tile cannot release the next one.  So group
-  //    1 drains nothing but the shared slice (it is idle again long before the next tile ends)
-  //    and group 0 the other three; the conversion work of a scheduler is the same as with an
-  //    even split, since both of its epilogue warps feed the same unit.
-  //  * BF16 / FP32 output (staging and stores, bound per warp): two slices each, the one that
-  //    touches the overlap first.
-  constexpr bool kUneven = kNB == 2 && kOut == LM_OUT_NVFP4;
-  uint32_t slices = 0;  // uneven split only
+  // tiles the MMAs of the next tile wait until the slice that holds the columns the other
+  // accumulator also uses (slice 3 of accumulator 0, slice 0 of accumulator 1) is in registers,
+  // and a warp that is still busy with the previous tile cannot release the next one.
+  //  * uneven split: group 1 drains nothing but the shared slice, so it is idle again long
+  //    before the next tile ends, and group 0 the other three.  NVFP4 output always: the gated
+  //    activation and the requantization keep both warps of a scheduler on its
+  //    special-function unit, whose work per tile is the same however the slices are dealt.
+  //    BF16 / FP32 output when the K loop is long enough to cover a three-slice drain
+  //    (`p.uneven`, set by the host): 3 to 8 % faster at K = 2048, 9 % slower at K = 512.
+  //  * even split: two slices each; the group whose first slice is the shared one owns it.
+  const bool uneven = kNB == 2 && (kOut == LM_OUT_NVFP4 || p.uneven != 0);
+  uint32_t slices;
   int count = 2;
-  bool owns_shared = kNB == 2;
-  int first;
-  if (kUneven) {
+  bool owns_shared = false;
+  if (kNB == 1) {
+    slices = 0x10u;
+  } else if (uneven) {
     if (group == 1) {
       slices = acc == 0 ? 0x3u : 0x0u;
       count = 1;
+      owns_shared = true;
     } else {
       slices = acc == 0 ? 0x210u : 0x321u;
       count = 3;
-      owns_shared = false;
     }
-    first = static_cast<int>(slices & 0xFu);
+  } else if (acc == 0) {
+    slices = group == 1 ? 0x13u : 0x02u;
+    owns_shared = group == 1;
   } else {
-    // 128-column tiles: slices 0 and 1.  256-column tiles: the overlap touches slices 2 and 3 of
-    // accumulator 0 and slices 0 and 1 of accumulator 1; group g takes slices g and g + 2.
-    first = kNB == 1 ? 0 : ((acc == 0) ? 2 + group : group);
+    slices = group == 1 ? 0x31u : 0x20u;
+    owns_shared = group == 0;
   }
+  const int first = static_cast<int>(slices & 0xFu);
   auto slice_at = [&](int s) { return static_cast<int>((slices >> (4 * s)) & 0xFu); };
   const bool rows_any = t.valid > quarter * 32;  // this warp owns at least one valid row
   // rows may live anywhere (another GPU's buffer): lane l holds the address of row l
@@ -685,9 +683,9 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const RowTile& t
       cur = next;
     }
   };
-  if (!kUneven) {
-    // always two slices: straight-line code
-    step(true, true, kNB == 1 ? 1 : ((acc == 0) ? group : 2 + group));
+  if (count == 2) {
+    // straight-line code for the common case
+    step(true, true, slice_at(1));
     step(false, false, 0);
   } else {
 #pragma unroll 1
@@ -762,7 +760,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       mbar_init(smem_u32(&misc->acc_full[s]), 1);
       mbar_init(smem_u32(&misc->acc_empty[s]), kNB == 1 ? 4 : 8);
     }
-    mbar_init(smem_u32(&misc->shared_cols_free), wide_shared_owners(kOut));
+    mbar_init(smem_u32(&misc->shared_cols_free), kWideSharedOwners);
     mbar_init(smem_u32(&misc->drain), 1);
     misc->abort_flag = 0;
     misc->fills_issued = misc->fills_taken = misc->a_fills_issued = misc->a_fills_taken = 0;
@@ -892,7 +890,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else if (warp == 1) {
     // ===================================================== MMA issuer
     constexpr uint32_t idesc = make_idesc(kNB * kTileN);
-    uint32_t sf_slot = 0;  // 256-column tiles with two scale-factor slots: alternates per stage
     int stage = 0;
     uint32_t phase = 0;
     uint32_t a_phase = 0;
@@ -908,7 +905,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           ok = mbar_wait(smem_u32(&misc->shared_cols_free), (it - 1) & 1u, abort_flag, kStatusMmaTimeout);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * (kNB == 1 ? kTileN : wide_acc1_col(kOut));
+        const uint32_t d_tmem = tmem_base + acc * (kNB == 1 ? kTileN : kWideAcc1Col);
         for (int ks = 0; ks < p.k_stages; ++ks) {
           ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusMmaTimeout);
           if (ok) ++taken;
@@ -921,10 +918,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
           const uint32_t b_smem = ring_base + stage * ring_stride;
           const uint32_t a_smem = resident ? smem_base + ks * kSlotBytes : b_smem + kAOffset;
-          const uint32_t sfa_t =
-              tmem_base + (kNB == 1 ? kSfCol + stage * 32 : wide_sf_col(kOut) + sf_slot * kWideSfSlotCols);
+          const uint32_t sfa_t = tmem_base + (kNB == 1 ? kSfCol + stage * 32 : kWideSfCol);
           const uint32_t sfb_t = sfa_t + 16;
-          if (wide_sf_slots(kOut) == 2) sf_slot ^= 1u;
           const uint64_t a_desc = desc_sw128(a_smem);
           const uint64_t b_desc = desc_sw128(b_smem);
           const uint64_t sfa_desc = desc_sf_atom(a_smem + kTileBytes);
@@ -982,7 +977,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     ctx.return_maps = &tmap_return;
     ctx.bar_shared_cols = smem_u32(&misc->shared_cols_free);
     ctx.remote = false;
-    ctx.acc1_col = wide_acc1_col(kOut);
+    ctx.acc1_col = kWideAcc1Col;
     ctx.inv_h = kOut == LM_OUT_NVFP4 ? __ldg(p.out_scale + 1) : 0.0f;
     TileWalker walker;
     int it = 0;
@@ -1055,7 +1050,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 //   acc_empty[a]                    leader's; the sixteen epilogue warps of both CTAs arrive.
 //   shared_cols_free                leader's; the eight warps that own the shared slice arrive.
 constexpr int kPairStageBytes = 2 * kTileBytes + 3 * kSfBytes;  // B half, SFB x2, A, SFA = 38912
-// TMEM of a pair CTA: as for 128 x 256 tiles (`wide_acc1_col` and its neighbours).
+// TMEM of a pair CTA: as for 128 x 256 tiles (`kWideAcc1Col`, `kWideSfCol`).
 static_assert(kPairStageBytes % 1024 == 0, "pair ring stages must keep 1024-byte alignment");
 // The pair's ring is cut from the raw shared-memory budget, not from 18 KB operand slots: five
 // stages fit with either output kind (with BF16 staging they fill the 227 KB exactly).
@@ -1184,7 +1179,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       mbar_init(smem_u32(&misc->acc_full[s]), 1);
       mbar_init(smem_u32(&misc->acc_empty[s]), 16);
     }
-    mbar_init(smem_u32(&misc->shared_cols_free), 2 * wide_shared_owners(kOut));  // both CTAs' owners
+    mbar_init(smem_u32(&misc->shared_cols_free), 2 * kWideSharedOwners);  // both CTAs' owners
     mbar_init(smem_u32(&misc->drain), 1);
     misc->abort_flag = 0;
     misc->fills_issued = misc->fills_taken = 0;
@@ -1305,7 +1300,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // ===================================================== MMA issuer (leader only)
     if (leader) {
       constexpr uint32_t idesc = make_idesc_pair(2 * kTileN);
-      uint32_t sf_slot = 0;
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -1320,7 +1314,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             ok = mbar_wait(smem_u32(&misc->shared_cols_free), (it - 1) & 1u, abort_flag, kStatusMmaTimeout);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base + acc * wide_acc1_col(kOut);
+          const uint32_t d_tmem = tmem_base + acc * kWideAcc1Col;
           for (int ks = 0; ks < p.k_stages; ++ks) {
             ok = mbar_wait(smem_u32(&misc->full[stage]), phase, abort_flag, kStatusMmaTimeout);
             if (!ok) break;
@@ -1328,9 +1322,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tc_fence_after();
             const int chunks = min(kChunksPerStage, p.atom_cols - ks * kChunksPerStage);
             const uint32_t stage_smem = smem_base + stage * kPairStageBytes;
-            const uint32_t sfa_t = tmem_base + wide_sf_col(kOut) + sf_slot * kWideSfSlotCols;
+            const uint32_t sfa_t = tmem_base + kWideSfCol;
             const uint32_t sfb_t = sfa_t + 16;
-            if (wide_sf_slots(kOut) == 2) sf_slot ^= 1u;
             const uint64_t a_desc = desc_sw128(stage_smem + kOffA);
             const uint64_t b_desc = desc_sw128(stage_smem + kOffB);
             const uint64_t sfa_desc = desc_sf_atom(stage_smem + kOffSfa);
@@ -1378,7 +1371,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     ctx.out_map = &tmap_out;
     ctx.return_maps = &tmap_return;
     ctx.remote = !leader;
-    ctx.acc1_col = wide_acc1_col(kOut);
+    ctx.acc1_col = kWideAcc1Col;
     const uint32_t cols_bar = smem_u32(&misc->shared_cols_free);
     ctx.bar_shared_cols = leader ? cols_bar : map_to_cta(cols_bar, 0);
     ctx.inv_h = kOut == LM_OUT_NVFP4 ? __ldg(p.out_scale + 1) : 0.0f;
@@ -1843,6 +1836,7 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   // whole 32-row blocks of a BF16 result leave through TMA stores (the SM's plain store path
   // was the bottleneck of short-K GEMMs); rows through a pointer table cannot
   p.tma_store = (a->out_kind == LM_OUT_BF16 && a->out_row_ptrs == nullptr && a->n >= 64) ? 1 : 0;
+  p.uneven = p.k_stages >= 6 ? 1 : 0;  // K >= 1536: the main loop of a tile outlasts a three-slice drain
   if (p.tma_store) {
     rc = encode_out_bf16(&pd.map_out, a->out, static_cast<uint64_t>(a->n), static_cast<uint64_t>(a->rows));
     if (rc != LM_OK) return rc;
