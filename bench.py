@@ -299,8 +299,8 @@ def _stage_times(plan, x, ids, w, iters=20):
 
 # DRAM bytes (read + write) of one launch from the committed ncu captures (profiles/): the
 # half-size C2 case (128 experts, 4096 tokens) scaled by the units processed (x2).
-NCU_DRAM_BYTES = {"c2": {"fc1": 2 * (189.9 + 8.6) * 1e6, "fc2": 2 * (85.3 + 80.1) * 1e6,
-                         "combine": 2 * (134.5 + 9.3) * 1e6, "quantize": 2 * 17.03 * 1e6,
+NCU_DRAM_BYTES = {"c2": {"fc1": 2 * (189.9 + 8.0) * 1e6, "fc2": 2 * (85.3 + 78.6) * 1e6,
+                         "combine": 2 * (134.5 + 9.7) * 1e6, "quantize": 2 * 17.2 * 1e6,
                          "dispatch": 2 * 0.44 * 1e6}}
 
 
