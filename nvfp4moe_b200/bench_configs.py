@@ -1,13 +1,14 @@
 """Latency of the MoE layer and its two grouped GEMMs on the named workloads.
 
     python -m nvfp4moe_b200.bench_configs [name ...]
-    python -m nvfp4moe_b200.bench_configs --steps 3 [--virtual-ranks] name
+    python -m nvfp4moe_b200.bench_configs --steps 3 [--virtual-ranks] [--nvtx] name
 
 The second form runs ``--steps`` plain steps of one workload and times nothing: the command
 line a profiler wraps (the ``*_half`` workloads keep the per-expert shapes of their parents at
 half the size, so that operands still exceed the L2 while a capture that replays every launch
 dozens of times ends in a minute or two).  ``--virtual-ranks`` sends the batch through two
-expert-parallel ranks that live in this process (peer-memory transport on one GPU).
+expert-parallel ranks that live in this process (peer-memory transport on one GPU); ``--nvtx``
+opens an NVTX range per stage (``nvfp4moe_b200.tracing``).
 
 Prints one JSON line per workload: median [IQR] of 21 CUDA-event samples after
 warm-up (the reference's protocol, BENCHMARKS.md:19-25), layer tokens/s, and
@@ -312,6 +313,10 @@ def main(argv):
         steps = int(argv[at + 1])
         del argv[at : at + 2]
         virtual = "--virtual-ranks" in argv
+        if "--nvtx" in argv:  # NVTX ranges around the stages, for a timeline capture
+            from nvfp4moe_b200 import tracing
+
+            tracing.enable()
         names = [a for a in argv if not a.startswith("--")]
         if len(names) != 1:
             raise SystemExit("--steps takes exactly one workload name")

@@ -31,6 +31,8 @@ from typing import Callable
 import torch
 import torch.distributed as dist
 
+from .tracing import traced
+
 
 def owner_splits(m_indptr: torch.Tensor, world: int) -> torch.Tensor:
     """Rows this rank sends to each owner rank, from the global-expert prefix."""
@@ -300,6 +302,7 @@ class ExpertParallelMoE:
         torch.sub(m_indptr[1:], m_indptr[:-1], out=self._peer["counts"])
         return self._peer["counts"]
 
+    @traced("lightmoe.ep_plan_quantize_send")
     def _phase_send(self, x):
         """Route plan from the gathered counts, then quantize once and store to the owners."""
         from . import _lib
@@ -321,6 +324,7 @@ class ExpertParallelMoE:
                                                peer["valid"].data_ptr(), plan._x_scale.data_ptr(),
                                                peer["q_base"], peer["sf_base"], stream))
 
+    @traced("lightmoe.ep_compute_and_return")
     def _phase_compute(self, mark=None):
         from . import _lib
 

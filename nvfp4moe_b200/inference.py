@@ -339,6 +339,7 @@ class InferenceMoE:
         routed_out = self._routed_out[:rows]
         fc1.prepare(qx, self.qb1, qh, cu, sfx, self.sfb1, self._alpha1, output_sf=sfh, output_scale=self._h_scale)
         fc2.prepare(qh, self.qb2, routed_out, cu, sfh, self.sfb2, self._alpha2)
+        fc1.trace_name, fc2.trace_name = "lightmoe.fc1", "lightmoe.fc2"
         return _FullExecution(fc1, fc2, qx, qh, sfx, sfh, routed_out)
 
     def _full_execution(self, tokens: int, *, decode: bool) -> _FullExecution:

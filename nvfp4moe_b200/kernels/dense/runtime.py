@@ -11,7 +11,7 @@ import ctypes
 
 import torch
 
-from ... import _lib
+from ... import _lib, tracing
 
 
 class DenseNvfp4Gemm:
@@ -91,8 +91,12 @@ class DenseNvfp4Gemm:
     def launch(self):
         if self._plan is None:
             raise RuntimeError("prepare must run before launch")
-        with torch.cuda.device(self.device):  # the plan belongs to this device's context and stream
-            _lib.check(_lib.lib().lm_gemm_launch(ctypes.byref(self._plan), _lib.stream_handle()))
+        opened = tracing.push("lightmoe.dense_gemm")
+        try:
+            with torch.cuda.device(self.device):  # the plan belongs to this device's context and stream
+                _lib.check(_lib.lib().lm_gemm_launch(ctypes.byref(self._plan), _lib.stream_handle()))
+        finally:
+            tracing.pop(opened)
 
     def __call__(self, a, b, out, sfa, sfb, alpha):
         self.prepare(a, b, out, sfa, sfb, alpha)

@@ -14,7 +14,7 @@ import ctypes
 
 import torch
 
-from ... import _lib
+from ... import _lib, tracing
 from ..gated import GatedBackwardEpilogue, GatedEpilogue, resolve_gemm_epilogue
 from ..unary import UnaryBackwardEpilogue, UnaryEpilogue
 
@@ -172,6 +172,7 @@ class GroupedNvfp4Gemm:
         # in the stream has finished.  Only for a second projection that directly follows its
         # first projection (cu, B, SFB and alpha are older than that kernel).
         self.weights_ahead = False
+        self.trace_name = "lightmoe.grouped_gemm"  # NVTX range of a launch (nvfp4moe_b200.tracing)
         # Set before ``prepare``: int64 CUDA tensor with one 16-byte aligned address per row.
         # Every BF16 output row is then written to its own address (which may lie in a peer
         # GPU's memory) instead of ``out``; the expert-parallel layer returns rows to their
@@ -321,8 +322,12 @@ class GroupedNvfp4Gemm:
     def launch(self):
         if self._plan is None:
             raise RuntimeError("prepare must run before launch")
-        with torch.cuda.device(self.device):  # the plan belongs to this device's context and stream
-            _lib.check(_lib.lib().lm_gemm_launch(ctypes.byref(self._plan), _lib.stream_handle()))
+        opened = tracing.push(self.trace_name)
+        try:
+            with torch.cuda.device(self.device):  # the plan belongs to this device's context and stream
+                _lib.check(_lib.lib().lm_gemm_launch(ctypes.byref(self._plan), _lib.stream_handle()))
+        finally:
+            tracing.pop(opened)
 
     def __call__(self, a, b, out, cu, sfa, sfb, alpha, output_sf=None, output_scale=None,
                  preact=None, aux=None, decode_plan=None, gather_idx=None):

@@ -11,8 +11,10 @@ import torch
 from torch import Tensor
 
 from ... import _lib
+from ...tracing import traced
 
 
+@traced("lightmoe.quantize")
 def nvfp4_quantize_decode(
     x: Tensor,
     topk_ids: Tensor,
@@ -39,6 +41,7 @@ def nvfp4_quantize_decode(
     )
 
 
+@traced("lightmoe.decode_prepare")
 def nvfp4_dispatch_quantize_decode(
     x: Tensor,
     topk_ids: Tensor,
@@ -78,6 +81,7 @@ def nvfp4_dispatch_quantize_decode(
     )
 
 
+@traced("lightmoe.decode_prepare")
 def _one_token_prepare(x, topk_ids, topk_weights, gather, slots, table, probs, padded_offsets, scale,
                        q_out, sf_out, direct: bool, label: str) -> None:
     tokens, features = x.shape

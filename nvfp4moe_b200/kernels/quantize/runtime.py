@@ -11,6 +11,7 @@ import torch
 from torch import Tensor
 
 from ... import _lib
+from ...tracing import traced
 
 
 def _prep(pts) -> Tensor:
@@ -50,6 +51,7 @@ def _dtype_code(t: Tensor) -> int:
     raise ValueError("quantizer input must use BF16 or FP32")
 
 
+@traced("lightmoe.quantize")
 def nvfp4_quantize_rowwise(
     z: Tensor,
     cu: Tensor,
@@ -96,6 +98,7 @@ def nvfp4_quantize_rowwise(
     )
 
 
+@traced("lightmoe.quantize_weights")
 def nvfp4_quantize_batched(w: Tensor, pts, q_out: Tensor, sf_out: Tensor) -> None:
     """Quantize an (E, N, K) weight stack in one launch.
 

@@ -10,8 +10,10 @@ import torch
 from torch import Tensor
 
 from ... import _lib
+from ...tracing import traced
 
 
+@traced("lightmoe.combine")
 def moe_finalize(
     yw: Tensor,
     slots: Tensor,

@@ -10,6 +10,7 @@ import torch
 from torch import Tensor
 
 from ... import _lib
+from ...tracing import traced
 
 CHUNK = 1024
 B_MAX = 128  # scratch rows the reference always allocates; larger inputs get more
@@ -21,6 +22,7 @@ def scratch_elems(rows: int, experts: int) -> int:
     return max(B_MAX, -(-rows // CHUNK)) * experts
 
 
+@traced("lightmoe.dispatch")
 def moe_dispatch(
     topi: Tensor,
     topv: Tensor,

@@ -252,3 +252,40 @@ def test_tensor_scale_tracks_amax_without_host_reads():
     assert float(pts_view) == 2.0
     with pytest.raises(NotImplementedError):
         TensorScale(device="cpu", te_rht=True)
+
+
+def test_tracing_ranges_only_when_enabled(monkeypatch):
+    """``tracing.traced`` opens and closes one NVTX range per call while enabled, none otherwise,
+    and closes it when the call raises."""
+    import torch
+
+    from nvfp4moe_b200 import tracing
+
+    events = []
+    monkeypatch.setattr(torch.cuda.nvtx, "range_push", lambda name: events.append(("push", name)))
+    monkeypatch.setattr(torch.cuda.nvtx, "range_pop", lambda: events.append(("pop",)))
+
+    @tracing.traced("lightmoe.stage")
+    def stage(value, fail=False):
+        if fail:
+            raise ValueError("boom")
+        return value + 1
+
+    assert stage(1) == 2 and events == []
+    tracing.enable()
+    try:
+        assert stage(2) == 3
+        with pytest.raises(ValueError):
+            stage(0, fail=True)
+        opened = tracing.push("lightmoe.fc1")
+        tracing.pop(opened)
+    finally:
+        tracing.enable(False)
+    assert events == [("push", "lightmoe.stage"), ("pop",), ("push", "lightmoe.stage"), ("pop",),
+                      ("push", "lightmoe.fc1"), ("pop",)]
+    assert tracing.push("x") is False and not tracing.enabled()
+    # the wrappers of the path carry their stage names
+    from nvfp4moe_b200.kernels.routing.combine import moe_finalize
+    from nvfp4moe_b200.kernels.routing.dispatch import moe_dispatch
+
+    assert moe_dispatch.__name__ == "moe_dispatch" and moe_finalize.__name__ == "moe_finalize"
