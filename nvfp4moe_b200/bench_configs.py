@@ -237,7 +237,10 @@ def run_gemm(name: str) -> dict:
         qa, sfa, pa = gemm.quantize(a)
         qb, sfb, pb = gemm.quantize(b)
         out = torch.empty(rows, n, dtype=torch.bfloat16, device=dev)
-        plan = gemm.DenseGemm(n, k, 128, 256 if n % 256 == 0 else 128)
+        # a caller's choice in the reference too (tile_m 128 or 256): tall tiles on CTA pairs
+        # once the matrix has rows for them
+        wide = n % 256 == 0
+        plan = gemm.DenseGemm(n, k, 256 if (wide and rows >= 2048) else 128, 256 if wide else 128)
         plan.prepare(qa, qb, out, sfa, sfb, (pa * pb).reshape(1))
     else:
         b = (torch.randn(experts, n, k, generator=g, device=dev) * 0.02).to(torch.bfloat16)

@@ -398,6 +398,12 @@ def test_dense_gemm_matches_oracle():
     qb_r, sfb_r = O.quantize_rows(b, pb.cpu())
     ref = O.dense_gemm(qa_r, sfa_r, qb_r, sfb_r, pa.cpu() * pb.cpu())
     assert O.rel_frobenius(out.cpu().float(), ref.to(torch.bfloat16).float()) <= GEMM_REL_TOL
+    # the other tilings the constructor admits (wide tiles, CTA pairs) give the same bits
+    for tile_m, tile_n in ((128, 256), (256, 256)):
+        other = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda")
+        gemm.DenseGemm(n, k, tile_m, tile_n)(qa, qb, other, sfa, sfb, pa * pb)
+        torch.cuda.synchronize()
+        assert torch.equal(other, out), (tile_m, tile_n)
     with pytest.raises(RuntimeError, match="prepare must run before launch"):
         gemm.DenseGemm(n, k, 128, 128).launch()
 
