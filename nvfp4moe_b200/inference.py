@@ -477,6 +477,13 @@ class InferenceMoE:
         rows = tokens * self.topk
         output = self._output_view(out, tokens, "out")
         execution = self._full_execution(tokens, decode=False)
+        if rows <= FUSED_PREPARE_MAX_ROWS:
+            # a short prefill step (a few rows on few experts) is a handful of launches of a few
+            # microseconds each: dispatch and quantization in one
+            nvfp4_dispatch_quantize_decode(x, topk_ids, topk_weights, self._parts, self._gather[:rows],
+                                           self._m_indptr, self._probs[:rows], self._slots[:rows],
+                                           self._padded_offsets, self._x_scale, execution.qx, execution.sfx)
+            return self._finish(execution, rows, output)
         self._dispatch(topk_ids, topk_weights, rows)
         # each token is quantized once and its codes and scale factors are written to all of
         # its expert-major rows: same bits as quantizing the gathered rows, 1/top_k of the math

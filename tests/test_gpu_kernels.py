@@ -321,10 +321,12 @@ def test_grouped_gemm_ragged_shapes(lens, n, k):
 
 @pytest.mark.parametrize("out_dtype", (torch.bfloat16, torch.float32))
 @pytest.mark.parametrize("max_ctas", (0, 3))
-def test_grouped_gemm_wide_tiles_bit_identical(out_dtype, max_ctas):
-    """128 x 256 tiles accumulate every output in the same order as 128 x 128 tiles."""
+@pytest.mark.parametrize("k", (1280, 2048))
+def test_grouped_gemm_wide_tiles_bit_identical(out_dtype, max_ctas, k):
+    """128 x 256 tiles accumulate every output in the same order as 128 x 128 tiles, with the
+    even split of the epilogue (K = 1280) and the uneven one (K >= 1536)."""
     lens = [130, 0, 257, 5, 128, 300, 0, 64]
-    cu, a, b = _grouped_case(lens, 1024, 1280, seed=77, b_std=0.05)
+    cu, a, b = _grouped_case(lens, 1024, k, seed=77, b_std=0.05)
     narrow, _ = _run_grouped(cu, a, b, out_dtype=out_dtype)
     wide, _ = _run_grouped(cu, a, b, out_dtype=out_dtype, tile_n=256, max_ctas=max_ctas)
     ref, _ = _oracle_grouped(cu, a, b)
@@ -340,10 +342,12 @@ def test_grouped_gemm_wide_tiles_bit_identical(out_dtype, max_ctas):
 
 @pytest.mark.parametrize("out_dtype", (torch.bfloat16, torch.float32))
 @pytest.mark.parametrize("max_ctas", (0, 4))
-def test_grouped_gemm_cta_pairs_bit_identical(out_dtype, max_ctas):
-    """256 x 256 tiles on CTA pairs accumulate every output in the same order as 128 x 128 tiles."""
+@pytest.mark.parametrize("k", (1280, 2048))
+def test_grouped_gemm_cta_pairs_bit_identical(out_dtype, max_ctas, k):
+    """256 x 256 tiles on CTA pairs accumulate every output in the same order as 128 x 128 tiles
+    (both splits of the epilogue, as above)."""
     lens = [130, 0, 257, 5, 128, 300, 0, 64, 513, 256]
-    cu, a, b = _grouped_case(lens, 1024, 1280, seed=78, b_std=0.05)
+    cu, a, b = _grouped_case(lens, 1024, k, seed=78, b_std=0.05)
     narrow, _ = _run_grouped(cu, a, b, out_dtype=out_dtype)
     pairs, _ = _run_grouped(cu, a, b, out_dtype=out_dtype, tile_n=256, tile_m=256, max_ctas=max_ctas)
     assert torch.isfinite(pairs).all()
