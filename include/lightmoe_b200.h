@@ -222,7 +222,9 @@ int lm_dispatch_static(const int32_t* topk_ids, const float* topk_weights, int64
  *   out (tokens, hidden) BF16.  hidden must be a multiple of 8.
  *   valid    optional device flag: when *valid == 0 the rows were not computed this step (an
  *            expert-parallel step that lm_ep_plan skipped) and out is written as zeros
- *   use_pdl  launch as a programmatic dependent of the previous kernel in the stream
+ *   use_pdl  launch as a programmatic dependent of the previous kernel in the stream: the kernel
+ *            reads slots and weights while that kernel may still run and waits for it before
+ *            it reads routed_out, so slots, weights and valid must not be that kernel's output
  */
 int lm_finalize(const void* routed_out, const int32_t* slots, const float* weights, void* out,
                 int64_t tokens, int top_k, int hidden, int64_t routed_row_stride,
@@ -280,9 +282,12 @@ typedef struct lm_gemm_args {
   /* Launch as a programmatic dependent of the previous kernel in the stream (use_pdl of the
      reference's constructor).  swap_ab only; other kernels ignore it. */
   int32_t use_pdl;
-  /* use_pdl only: start the weight stream before waiting for the previous kernel.  Allowed
-     when m_indptr, b, sfb and alpha were complete before the previous kernel began and that
-     kernel is itself a swap_ab launch of this library (the second projection of a layer). */
+  /* use_pdl only: read the routing table and start the weight stream before waiting for the
+     previous kernel.  Allowed when m_indptr, b, sfb and alpha were complete before the previous
+     kernel began, and that kernel either is a use_pdl launch of this library (it releases its
+     dependents only after its own wait: the second projection after the first) or was launched
+     the plain way and releases its dependents early (lm_decode_prepare before a first
+     projection whose direct routes are read from the caller's topk_ids). */
   int32_t weights_ahead;
   /* With out_row_ptrs (BF16 output that returns to the ranks of an expert-parallel group): whole
      32-row blocks leave as one bulk tensor store each instead of row by row.  out_blocks is the

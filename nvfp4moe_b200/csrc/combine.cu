@@ -29,11 +29,15 @@ struct CombineParams {
 
 template <bool kWeighted>
 __global__ void __launch_bounds__(kThreads) combine_kernel(CombineParams p) {
-  // as a programmatic dependent the kernel may start while its predecessor drains
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // As a programmatic dependent the kernel may start while its predecessor drains.  The routed
+  // rows are that kernel's output and are read after the wait below; slots and weights are older
+  // (the dispatch wrote them before the GEMMs began) and are read while it still runs.
   const int64_t token = blockIdx.x;
   const int vec = blockIdx.y * kThreads + threadIdx.x;
-  if (vec >= p.vec_per_row) return;
+  if (vec >= p.vec_per_row) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    return;
+  }
   const bool live = p.valid == nullptr || __ldg(p.valid) != 0;
   const int col = vec * 8;
   float acc[8];
@@ -53,12 +57,21 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(CombineParams p) {
     for (int j = 0; j < kBatch; ++j) slot[j] = (live && j0 + j < p.top_k) ? __ldg(slot_ptr + j0 + j) : -1;
 #pragma unroll
     for (int j = 0; j < kBatch; ++j) {
-      row[j] = make_uint4(0, 0, 0, 0);
       w[j] = 0.0f;
-      if (slot[j] >= 0) {
-        row[j] = __ldg(reinterpret_cast<const uint4*>(p.rows + slot[j] * p.row_stride + col));
-        if (kWeighted) w[j] = __ldg(p.weights + slot[j]);
-      }
+      if (kWeighted && slot[j] >= 0) w[j] = __ldg(p.weights + slot[j]);
+    }
+    if (j0 == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Plain loads in volatile asm, not __ldg: a load the compiler knows as invariant may be
+    // hoisted above the wait now that its address (the slot) is known before it, and would
+    // then read rows the previous kernel has not written yet.
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      row[j] = make_uint4(0, 0, 0, 0);
+      if (slot[j] >= 0)
+        asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(row[j].x), "=r"(row[j].y), "=r"(row[j].z), "=r"(row[j].w)
+                     : "l"(p.rows + slot[j] * p.row_stride + col)
+                     : "memory");
     }
 #pragma unroll
     for (int j = 0; j < kBatch; ++j) {

@@ -315,16 +315,21 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // The routing table comes from an earlier kernel.  With `prefetch` that kernel finished
-  // before this one's predecessor began (every CTA of the predecessor waited for it), so the
-  // table is read at once and only the token operand waits; otherwise everything waits.
-  if (!p.prefetch) pdl_wait();
-  // Dependents may start from here on.  Not earlier: a dependent that prefetches trusts that
-  // everything older than THIS kernel is complete, which holds once every CTA of this kernel
-  // is past its own wait (or, with `prefetch`, was launched after such a kernel).
-  pdl_launch_dependents();
+  // The routing table comes from an earlier kernel.  With `prefetch` it was complete before
+  // this one's predecessor began (the predecessor waited for it, or was launched the plain way
+  // after it), so the table is read at once and only the token operand waits (in the producer
+  // warps); otherwise everything waits here.
+  // Dependents may start once this CTA is past its wait, not earlier: a dependent that
+  // prefetches trusts that everything older than THIS kernel is complete, which holds once
+  // every CTA of this kernel has waited for its own predecessor.
+  if (!p.prefetch) {
+    pdl_wait();
+    pdl_launch_dependents();
+  }
   const int table = p.direct ? p.groups : p.groups + 1;
-  for (int e = threadIdx.x; e < table; e += kDecThreads) misc->cu[e] = __ldg(p.m_indptr + e);
+  // (a volatile load: one the compiler knows as invariant could move above the wait)
+  for (int e = threadIdx.x; e < table; e += kDecThreads)
+    misc->cu[e] = *reinterpret_cast<const volatile int32_t*>(p.m_indptr + e);
   __syncthreads();
   if (warp == 2) {
     if (p.direct) {
@@ -416,6 +421,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         __syncwarp();
         if (!waited) {
           pdl_wait();
+          pdl_launch_dependents();
           waited = true;
         }
         if (elect_one()) {

@@ -158,7 +158,8 @@ class InferenceMoE:
         self._full_executions: dict[tuple[int, bool], _FullExecution] = {}
         self._routed_gemms: dict[tuple[str, int], GroupedNvfp4Gemm] = {}
         self._calibration_gemms: dict[int, GroupedNvfp4Gemm] = {}
-        self._direct_execution_plan: _FullExecution | None = None
+        self._direct_execution_plan: _FullExecution | None = None  # the one used last
+        self._direct_plans: dict[int | None, _FullExecution] = {}
 
     # ------------------------------------------------------------------ state
     @property
@@ -186,6 +187,7 @@ class InferenceMoE:
         self._routed_gemms.clear()
         self._calibration_gemms.clear()
         self._direct_execution_plan = None
+        self._direct_plans.clear()
 
     # ---------------------------------------------------------------- weights
     @torch.no_grad()
@@ -333,11 +335,13 @@ class InferenceMoE:
             fast_decode_sched=first and decode and not schedule and self.hidden_size >= 2048,
         )
 
-    def _pair_of_gemms(self, fc1, fc2, rows, cu) -> _FullExecution:
-        """Prepare fc1 -> fc2 over the plan's own buffers for ``rows`` rows routed by ``cu``."""
+    def _pair_of_gemms(self, fc1, fc2, rows, cu, *, first_cu=None) -> _FullExecution:
+        """Prepare fc1 -> fc2 over the plan's own buffers for ``rows`` rows routed by ``cu``
+        (``first_cu``: fc1 reads the same routing from another tensor)."""
         qx, qh, sfx, sfh = self._views(rows)
         routed_out = self._routed_out[:rows]
-        fc1.prepare(qx, self.qb1, qh, cu, sfx, self.sfb1, self._alpha1, output_sf=sfh, output_scale=self._h_scale)
+        fc1.prepare(qx, self.qb1, qh, cu if first_cu is None else first_cu, sfx, self.sfb1, self._alpha1,
+                    output_sf=sfh, output_scale=self._h_scale)
         fc2.prepare(qh, self.qb2, routed_out, cu, sfh, self.sfb2, self._alpha2)
         fc1.trace_name, fc2.trace_name = "lightmoe.fc1", "lightmoe.fc2"
         return _FullExecution(fc1, fc2, qx, qh, sfx, sfh, routed_out)
@@ -358,19 +362,33 @@ class InferenceMoE:
             execution = self._full_executions[key] = self._pair_of_gemms(fc1, fc2, rows, self._m_indptr)
         return execution
 
-    def _direct_execution(self) -> _FullExecution:
+    def _direct_execution(self, topk_ids=None) -> _FullExecution:
         """The one-token step without a dispatch (``lightmoe/inference.py:656-721``): the token is
         quantized once, both GEMMs walk the ``top_k`` routes in route order with the expert ids
-        in the first ``top_k`` words of ``_m_indptr``; fc1 reads row 0 for every route."""
-        if self._direct_execution_plan is None:
+        in the first ``top_k`` words of ``_m_indptr``; fc1 reads row 0 for every route.
+
+        With ``topk_ids`` fc1 reads the expert ids from the caller's tensor instead, which the
+        prepare launch only copies: the ids are older than that launch, so fc1 may read them and
+        start its weight stream while the prepare launch still quantizes.  The prepared GEMM holds
+        the tensor's address, hence one plan per address (a handful: a serving loop or a captured
+        graph passes the same buffers every step)."""
+        key = None if topk_ids is None else topk_ids.data_ptr()
+        execution = self._direct_plans.get(key)
+        if execution is None:
             common = dict(use_dynamic_sched=False, use_pdl=True, direct_routes=self.topk)
             with torch.cuda.device(self.device):
                 fc1 = GroupedNvfp4Gemm(self.experts, self._first_projection_rows, self.hidden_size, 128, 128,
                                        output_dtype=_FP4, epilogue=self._epilogue(), broadcast_a=True, **common)
                 fc2 = GroupedNvfp4Gemm(self.experts, self.hidden_size, self.intermediate_size, 128, 128, **common)
             fc2.weights_ahead = True
-            self._direct_execution_plan = self._pair_of_gemms(fc1, fc2, self.topk, self._m_indptr[: self.topk])
-        return self._direct_execution_plan
+            fc1.weights_ahead = topk_ids is not None
+            execution = self._pair_of_gemms(fc1, fc2, self.topk, self._m_indptr[: self.topk],
+                                            first_cu=None if topk_ids is None else topk_ids.view(-1))
+            while len(self._direct_plans) >= 16:
+                self._direct_plans.pop(next(iter(self._direct_plans)))
+            self._direct_plans[key] = execution
+        self._direct_execution_plan = execution
+        return execution
 
     # ------------------------------------------------------------ calibration
     @torch.no_grad()
@@ -500,7 +518,7 @@ class InferenceMoE:
         output = self._output_view(out, tokens, "out")
         if tokens == 1 and self.topk <= 32 and self.tile_override is None:
             # one token: no dispatch, the routes keep their order
-            execution = self._direct_execution()
+            execution = self._direct_execution(topk_ids)
             nvfp4_direct_decode_prepare(x, topk_ids, topk_weights, self._gather[:rows], self._slots[:rows],
                                         self._m_indptr[: self.topk], self._probs[:rows],
                                         self._padded_offsets, self._x_scale, execution.qx, execution.sfx)
