@@ -280,7 +280,9 @@ typedef struct lm_gemm_args {
   int32_t direct_routes;
   int32_t broadcast_a;
   /* Launch as a programmatic dependent of the previous kernel in the stream (use_pdl of the
-     reference's constructor).  swap_ab only; other kernels ignore it. */
+     reference's constructor): the kernel sets itself up while that kernel may still run and
+     waits for it before it reads m_indptr or an operand; its own dependents are released after
+     that wait. */
   int32_t use_pdl;
   /* use_pdl only: read the routing table and start the weight stream before waiting for the
      previous kernel.  Allowed when m_indptr, b, sfb and alpha were complete before the previous

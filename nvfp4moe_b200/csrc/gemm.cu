@@ -710,6 +710,16 @@ __device__ __forceinline__ void tc_copy_sf(uint32_t taddr, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 
+// Programmatic dependent launch of the prefill kernels (short steps: a handful of launches of a
+// few microseconds each, where a kernel's set-up can run beside its predecessor).  The wait comes
+// after barriers and TMEM are set up and before anything an earlier kernel wrote is read; the
+// kernel's own dependents are released only after it, so a kernel past its wait knows that
+// every older kernel is complete.  Launched the plain way both instructions do nothing.
+__device__ __forceinline__ void prefill_pdl_wait_and_release() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ------------------------------------------------------------------ kernel
 // kNB = 128-column blocks per tile.
 // 1: 128 x 128 tiles, two accumulators of 128 TMEM columns, one scale-factor slot per ring
@@ -774,14 +784,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // expert boundaries -> shared memory
+  prefill_pdl_wait_and_release();
+  // expert boundaries -> shared memory (volatile loads: one the compiler knows as invariant
+  // could move above the wait)
   if (p.dense) {
     if (threadIdx.x == 0) {
       misc->cu[0] = 0;
       misc->cu[1] = static_cast<int>(p.rows);
     }
   } else {
-    for (int e = threadIdx.x; e <= p.experts; e += kThreads) misc->cu[e] = __ldg(p.m_indptr + e);
+    for (int e = threadIdx.x; e <= p.experts; e += kThreads)
+      misc->cu[e] = *reinterpret_cast<const volatile int32_t*>(p.m_indptr + e);
   }
   __syncthreads();
   if (warp == 2) {
@@ -1195,13 +1208,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
+  prefill_pdl_wait_and_release();
   if (p.dense) {
     if (threadIdx.x == 0) {
       misc->cu[0] = 0;
       misc->cu[1] = static_cast<int>(p.rows);
     }
   } else {
-    for (int e = threadIdx.x; e <= p.experts; e += kThreads) misc->cu[e] = __ldg(p.m_indptr + e);
+    for (int e = threadIdx.x; e <= p.experts; e += kThreads)
+      misc->cu[e] = *reinterpret_cast<const volatile int32_t*>(p.m_indptr + e);
   }
   __syncthreads();
   if (warp == 2) {
@@ -1439,6 +1454,7 @@ struct PlanData {
   int32_t grid;
   int32_t n_blocks;  // 128-column blocks per tile: 1 or 2
   int32_t pair;      // 1: CTA pairs compute 256 x 256 tiles
+  int32_t use_pdl;   // launch as a programmatic dependent of the previous kernel
   GemmParams params;
   alignas(64) CUtensorMap map_a;
   alignas(64) CUtensorMap map_a64;
@@ -1655,10 +1671,19 @@ int launch_kernel(const PlanData& pd, cudaStream_t stream) {
     LM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(kOut)));
     if (device >= 0 && device < kMaxDevices) configured[device] = true;
   }
-  kernel<<<pd.grid, kThreads, smem_bytes(kOut), stream>>>(pd.map_a, pd.map_a64, pd.map_a32, pd.map_b,
-                                                          pd.map_out, pd.map_return, pd.params);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(pd.grid);
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = smem_bytes(kOut);
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = pd.use_pdl ? 1 : 0;
+  LM_CUDA(cudaLaunchKernelEx(&config, kernel, pd.map_a, pd.map_a64, pd.map_a32, pd.map_b, pd.map_out,
+                             pd.map_return, pd.params));
   note_launch();
-  LM_CUDA(cudaGetLastError());
   return LM_OK;
 }
 
@@ -1677,13 +1702,15 @@ int launch_pair(const PlanData& pd, cudaStream_t stream) {
   config.blockDim = dim3(kThreads);
   config.dynamicSmemBytes = pair_smem_bytes(kOut);
   config.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
-  config.numAttrs = 1;
+  config.numAttrs = pd.use_pdl ? 2 : 1;
   LM_CUDA(cudaLaunchKernelEx(&config, kernel, pd.map_a, pd.map_a64, pd.map_a32, pd.map_b, pd.map_out,
                              pd.map_sfa, pd.map_sfb, pd.map_return, pd.params));
   note_launch();
@@ -1752,6 +1779,7 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   pd.n_blocks = (a->tile_n == 256 && a->n % 256 == 0) ? 2 : 1;
   // 256 x 256 tiles on CTA pairs when 256-row tiles are asked for as well
   pd.pair = (pd.n_blocks == 2 && a->tile_m == 256) ? 1 : 0;
+  pd.use_pdl = a->use_pdl ? 1 : 0;
   p.n_tiles = (a->n + pd.n_blocks * kTileN - 1) / (pd.n_blocks * kTileN);
   p.atom_cols = a->k / 64;
   p.k_stages = (p.atom_cols + kChunksPerStage - 1) / kChunksPerStage;

@@ -66,9 +66,10 @@ class GroupedNvfp4Gemm:
                            dispatch, on the same kernel: ``cu`` holds the expert id of each
                            route, route r reads row r of A (row 0 with ``broadcast_a``) and
                            writes row r of the output.
-    ``use_pdl``            the decode-shaped kernel launches as a programmatic dependent of the
-                           previous kernel; the prefill kernels launch normally (measured: no
-                           gain there).  ``weights_ahead`` (attribute, set before ``prepare``)
+    ``use_pdl``            the launch is a programmatic dependent of the previous kernel: its
+                           set-up runs beside that kernel and it waits for it before reading
+                           operands.  Pays in steps of a few short launches; on a long prefill
+                           chain it measured slower (``InferenceMoE`` asks for it accordingly).  ``weights_ahead`` (attribute, set before ``prepare``)
                            lets it start its weight stream before the previous kernel ends.
     ``fast_decode_sched``  a scheduling hint of the reference (tiles read from the dispatch
                            plan); every kernel here derives its tiles from ``cu`` on the device,
@@ -304,7 +305,7 @@ class GroupedNvfp4Gemm:
         args.swap_ab = int(decode_shaped)
         args.direct_routes = self.direct_routes
         args.broadcast_a = int(self.broadcast_a)
-        args.use_pdl = int(self.use_pdl and decode_shaped)
+        args.use_pdl = int(self.use_pdl)
         args.weights_ahead = int(self.weights_ahead and self.use_pdl and decode_shaped)
         plan = _lib.GemmPlan()
         with torch.cuda.device(self.device):
