@@ -121,6 +121,30 @@ def test_policy_tables():
     assert _decode_grid_mode(True, 6144, 6144, 8, 128) == DECODE_GRID_DOUBLE
 
 
+def test_measured_tile_policy():
+    """The tiles this build launches (``policy.pick_tiles``): wide tiles whenever N splits into
+    256 columns, CTA pairs when padding every expert to 256 rows costs less than the pair wins."""
+    from nvfp4moe_b200.policy import (FUSED_PREPARE_MAX_ROWS, SWAPPED_MAX_ROWS, expected_padded_rows,
+                                      pick_tiles)
+
+    # N not a multiple of 256 (Nemotron's 1920 / 2688): 128 x 128
+    assert pick_tiles(49152, 8, 1920, 2688, nvfp4_out=True) == (128, 128)
+    # fewer than 128 rows per expert: never the tall tile
+    assert pick_tiles(1024, 16, 1024, 2048, nvfp4_out=True) == (128, 256)
+    # C2: 256 rows per expert pad to 2.5 tiles of 128 or to 3 x 128 in tall tiles: stays on 128 x 256
+    assert pick_tiles(65536, 256, 1024, 2048, nvfp4_out=True) == (128, 256)
+    assert pick_tiles(65536, 256, 2048, 512, nvfp4_out=False) == (128, 256)
+    # C3 (192 rows per expert), C5 and the published shards (thousands of rows per expert): pairs
+    assert pick_tiles(49152, 256, 4096, 4096, nvfp4_out=True) == (256, 256)
+    assert pick_tiles(65536, 16, 1024, 2048, nvfp4_out=True) == (256, 256)
+    assert pick_tiles(49152, 8, 4096, 2048, nvfp4_out=False) == (256, 256)
+    # padded rows: a tile boundary in the middle of the distribution costs half a tile on average
+    assert abs(expected_padded_rows(256.0, 128) - 320.0) < 8.0
+    assert abs(expected_padded_rows(256.0, 256) - 384.0) < 8.0
+    assert expected_padded_rows(4096.0, 256) < 4096.0 + 256.0 + 1.0
+    assert SWAPPED_MAX_ROWS == 128 and FUSED_PREPARE_MAX_ROWS == 1024
+
+
 def test_epilogue_policies():
     from lightmoe.kernels.gated import (GatedBackwardEpilogue, GatedEpilogue, gated_output_n,
                                         resolve_gemm_epilogue, validate_gated_tile_n)
