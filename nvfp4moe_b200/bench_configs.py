@@ -45,6 +45,8 @@ WORKLOADS = {
     "shard_deepseek_v4_flash": (4096, 2048, 8, 6, 8192, "swiglu", 10.0, "uniform", False),
     "shard_glm_5_2": (6144, 2048, 16, 8, 8192, "swiglu", None, "uniform", False),
     "shard_minimax_m3": (6144, 3072, 8, 4, 8192, "swiglu_oai", None, "uniform", False),
+    "shard_qwen35_397b": (4096, 1024, 16, 10, 8192, "swiglu", None, "uniform", False),
+    "shard_nemotron_35": (2688, 1920, 8, 6, 8192, "relu2", None, "uniform", False),
     # the same shards at 1 and 128 tokens (the reference's layer table, BENCHMARKS.md:92-97)
     "shard_qwen35_35b_m1": (2048, 512, 16, 8, 1, "swiglu", None, "uniform", True),
     "shard_qwen35_35b_m128": (2048, 512, 16, 8, 128, "swiglu", None, "uniform", True),
@@ -54,6 +56,10 @@ WORKLOADS = {
     "shard_glm_5_2_m128": (6144, 2048, 16, 8, 128, "swiglu", None, "uniform", True),
     "shard_minimax_m3_m1": (6144, 3072, 8, 4, 1, "swiglu_oai", None, "uniform", True),
     "shard_minimax_m3_m128": (6144, 3072, 8, 4, 128, "swiglu_oai", None, "uniform", True),
+    "shard_qwen35_397b_m1": (4096, 1024, 16, 10, 1, "swiglu", None, "uniform", True),
+    "shard_qwen35_397b_m128": (4096, 1024, 16, 10, 128, "swiglu", None, "uniform", True),
+    "shard_nemotron_35_m1": (2688, 1920, 8, 6, 1, "relu2", None, "uniform", True),
+    "shard_nemotron_35_m128": (2688, 1920, 8, 6, 128, "relu2", None, "uniform", True),
     # half-size cases for profiler captures
     "c2_half": (2048, 512, 128, 8, 4096, "swiglu", None, "uniform", False),
     "shard_deepseek_v4_flash_half": (4096, 2048, 8, 6, 4096, "swiglu", 10.0, "uniform", False),

@@ -1775,8 +1775,10 @@ extern "C" int lm_gemm_prepare(const lm_gemm_args* a, lm_gemm_plan* plan) {
   LM_REQUIRE(a->direct_routes == 0 && !a->broadcast_a, "gemm: direct routes require swap_ab");
   p.experts = a->experts;
   p.n = a->n;
-  // 256-column tiles on request, when N splits into them evenly
-  pd.n_blocks = (a->tile_n == 256 && a->n % 256 == 0) ? 2 : 1;
+  // 256-column tiles on request, when N is whole 128-column blocks and more than one of them:
+  // an odd block count leaves half of the last tile empty (its loads fall into the next
+  // expert's rows or past the tensor, where TMA fills zeros, and nothing of it is stored)
+  pd.n_blocks = (a->tile_n == 256 && a->n % 128 == 0 && a->n >= 256) ? 2 : 1;
   // 256 x 256 tiles on CTA pairs when 256-row tiles are asked for as well
   pd.pair = (pd.n_blocks == 2 && a->tile_m == 256) ? 1 : 0;
   pd.use_pdl = a->use_pdl ? 1 : 0;

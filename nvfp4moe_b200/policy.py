@@ -69,7 +69,7 @@ def pick_tiles(rows: int, experts: int, n: int, k: int, *, nvfp4_out: bool) -> t
     pair wins (with about 256 rows per expert the taller tile pads 20 % more and loses; with
     192, or with 512 and more, it wins).
     """
-    if n % 256:
+    if n % 128 or n < 256:
         return 128, 128
     if rows < 128 * experts:
         return 128, 256

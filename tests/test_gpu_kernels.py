@@ -357,6 +357,27 @@ def test_grouped_gemm_cta_pairs_bit_identical(out_dtype, max_ctas, k):
     assert _lib.device_status() == 0
 
 
+@pytest.mark.parametrize("out_dtype", (torch.bfloat16, torch.float32))
+@pytest.mark.parametrize("n", (384, 640))
+@pytest.mark.parametrize("tile_m", (128, 256))
+def test_grouped_gemm_half_empty_last_wide_tile(out_dtype, n, tile_m):
+    """N of an odd number of 128-column blocks on 256-column tiles: the last tile's second half
+    has no weights (its loads reach into the next expert or past the tensor) and stores nothing;
+    every stored value equals the 128 x 128 result, and nothing beyond column N is written."""
+    lens = [130, 0, 257, 5, 128, 300, 64]
+    cu, a, b = _grouped_case(lens, n, 1280, seed=90 + n, b_std=0.05)
+    narrow, _ = _run_grouped(cu, a, b, out_dtype=out_dtype)
+    wide, _ = _run_grouped(cu, a, b, out_dtype=out_dtype, tile_n=256, tile_m=tile_m)
+    ref, _ = _oracle_grouped(cu, a, b)
+    assert torch.isfinite(wide).all()
+    assert torch.equal(wide, narrow)
+    tol = GEMM_REL_TOL if out_dtype == torch.bfloat16 else 1e-5
+    assert O.rel_frobenius(wide.cpu().float(), ref.to(out_dtype).float()) <= tol
+    from nvfp4moe_b200 import _lib
+
+    assert _lib.device_status() == 0
+
+
 @pytest.mark.parametrize(("n", "k"), ((256, 2688), (512, 64), (768, 192)))
 def test_grouped_gemm_cta_pairs_ragged_k(n, k):
     """CTA pairs when K is not a multiple of the 256-element stage: the last stage holds fewer
@@ -423,13 +444,16 @@ def test_dense_gemm_matches_oracle():
      ("relu2", None)),
 )
 @pytest.mark.parametrize(("tile_m", "tile_n"), ((128, 128), (128, 256), (256, 256)))
-def test_fused_epilogue_matches_oracle(activation, clamp, tile_m, tile_n):
+@pytest.mark.parametrize("inter", (256, 384))
+def test_fused_epilogue_matches_oracle(activation, clamp, tile_m, tile_n, inter):
+    """``inter`` 384: N = 768 (gated) is whole 256-column tiles, N = 384 (ReLU squared) leaves
+    half of the last wide tile empty."""
     from nvfp4moe_b200 import gemm
     from nvfp4moe_b200.kernels.gated import GatedEpilogue
     from nvfp4moe_b200.kernels.unary import UnaryEpilogue
 
     lens = [40, 0, 200, 129]
-    inter, hidden = 256, 512
+    hidden = 512
     n = inter if activation == "relu2" else 2 * inter
     cu, a, b = _grouped_case(lens, n, hidden, seed=11, b_std=hidden**-0.5)
     rows = a.shape[0]
