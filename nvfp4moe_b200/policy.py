@@ -62,7 +62,8 @@ def pick_tiles(rows: int, experts: int, n: int, k: int, *, nvfp4_out: bool) -> t
 
     128 x 256 tiles pull a quarter less data into the SM per FLOP than 128 x 128 tiles and
     were 1.25x to 1.7x faster on every prefill shape measured (K from 512 to 4096), so the wide
-    tile is taken whenever N splits into it.  256 x 256 tiles on CTA pairs move another 30 %
+    tile is taken whenever N is two or more whole 128-column blocks (with an odd count the last
+    tile is half empty: N = 1920 as 7.5 wide tiles ran 1.9x faster than as 15 narrow ones).  256 x 256 tiles on CTA pairs move another 30 %
     fewer bytes through each SM's shared memory and issue half as many MMAs: about 1.25x
     faster per padded row on a first projection with K >= 4096, about 1.1x elsewhere -- but they
     pad every expert to 256 rows, so they are taken only when that padding costs less than the
