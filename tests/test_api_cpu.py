@@ -122,13 +122,18 @@ def test_policy_tables():
 
 
 def test_measured_tile_policy():
-    """The tiles this build launches (``policy.pick_tiles``): wide tiles whenever N splits into
-    256 columns, CTA pairs when padding every expert to 256 rows costs less than the pair wins."""
+    """The tiles this build launches (``policy.pick_tiles``): wide tiles whenever N is two or more
+    128-column blocks, CTA pairs when padding every expert to 256 rows costs less than the pair
+    wins."""
     from nvfp4moe_b200.policy import (FUSED_PREPARE_MAX_ROWS, SWAPPED_MAX_ROWS, expected_padded_rows,
                                       pick_tiles)
 
-    # N not a multiple of 256 (Nemotron's 1920 / 2688): 128 x 128
-    assert pick_tiles(49152, 8, 1920, 2688, nvfp4_out=True) == (128, 128)
+    # N must be two or more whole 128-column blocks for the wide tile; an odd count is fine
+    # (Nemotron's 1920 / 2688: the last tile is half empty)
+    assert pick_tiles(49152, 8, 136, 2688, nvfp4_out=False) == (128, 128)
+    assert pick_tiles(49152, 8, 128, 2688, nvfp4_out=False) == (128, 128)
+    assert pick_tiles(49152, 8, 1920, 2688, nvfp4_out=True) == (256, 256)
+    assert pick_tiles(512, 8, 2688, 1920, nvfp4_out=False) == (128, 256)
     # fewer than 128 rows per expert: never the tall tile
     assert pick_tiles(1024, 16, 1024, 2048, nvfp4_out=True) == (128, 256)
     # C2: 256 rows per expert pad to 2.5 tiles of 128 or to 3 x 128 in tall tiles: stays on 128 x 256
