@@ -160,6 +160,7 @@ class InferenceMoE:
         self._calibration_gemms: dict[int, GroupedNvfp4Gemm] = {}
         self._direct_execution_plan: _FullExecution | None = None  # the one used last
         self._direct_plans: dict[int | None, _FullExecution] = {}
+        self._direct_seen: set[int] = set()
 
     # ------------------------------------------------------------------ state
     @property
@@ -188,6 +189,7 @@ class InferenceMoE:
         self._calibration_gemms.clear()
         self._direct_execution_plan = None
         self._direct_plans.clear()
+        self._direct_seen.clear()
 
     # ---------------------------------------------------------------- weights
     @torch.no_grad()
@@ -376,6 +378,13 @@ class InferenceMoE:
         the tensor's address, hence one plan per address (a handful: a serving loop or a captured
         graph passes the same buffers every step)."""
         key = None if topk_ids is None else topk_ids.data_ptr()
+        if key is not None and key not in self._direct_plans and key not in self._direct_seen:
+            # an address met for the first time runs on the shared plan: only one that comes
+            # back (a serving loop's buffer, a captured graph) is worth a plan of its own
+            if len(self._direct_seen) >= 64:
+                self._direct_seen.clear()
+            self._direct_seen.add(key)
+            key, topk_ids = None, None
         execution = self._direct_plans.get(key)
         if execution is None:
             common = dict(use_dynamic_sched=False, use_pdl=True, direct_routes=self.topk)
@@ -388,7 +397,7 @@ class InferenceMoE:
             execution = self._pair_of_gemms(fc1, fc2, self.topk, self._m_indptr[: self.topk],
                                             first_cu=None if topk_ids is None else topk_ids.view(-1))
             while len(self._direct_plans) >= 16:
-                self._direct_plans.pop(next(iter(self._direct_plans)))
+                self._direct_plans.pop(next(k for k in self._direct_plans if k is not None))
             self._direct_plans[key] = execution
         self._direct_execution_plan = execution
         return execution
