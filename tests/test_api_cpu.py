@@ -318,3 +318,33 @@ def test_tracing_ranges_only_when_enabled(monkeypatch):
     from nvfp4moe_b200.kernels.routing.dispatch import moe_dispatch
 
     assert moe_dispatch.__name__ == "moe_dispatch" and moe_finalize.__name__ == "moe_finalize"
+
+
+def test_ctypes_structs_match_the_header_layout(tmp_path):
+    """The ctypes mirrors of ``lm_gemm_args`` / ``lm_gemm_plan`` have the size and the field
+    offsets a C compiler gives the header's structs (the header is plain C: it compiles with gcc)."""
+    import shutil
+
+    from nvfp4moe_b200 import _lib
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    header = pathlib.Path(__file__).resolve().parents[1] / "include"
+    fields = [name for name, _ in _lib.GemmArgs._fields_]
+    lines = ["#include <stdio.h>", "#include <stddef.h>", '#include "lightmoe_b200.h"', "int main(void) {",
+             '  printf("%zu %zu\\n", sizeof(lm_gemm_args), sizeof(lm_gemm_plan));']
+    lines += [f'  printf("{name} %zu\\n", offsetof(lm_gemm_args, {name}));' for name in fields]
+    lines += ["  return 0;", "}"]
+    source = tmp_path / "layout.c"
+    source.write_text("\n".join(lines))
+    binary = tmp_path / "layout"
+    subprocess.run([gcc, "-std=c99", "-I", str(header), str(source), "-o", str(binary)], check=True)
+    out = subprocess.run([str(binary)], check=True, capture_output=True, text=True).stdout.split("\n")
+    args_size, plan_size = map(int, out[0].split())
+    assert args_size == ctypes.sizeof(_lib.GemmArgs)
+    assert plan_size == ctypes.sizeof(_lib.GemmPlan)
+    offsets = dict(line.split() for line in out[1:] if line)
+    assert set(offsets) == set(fields)
+    for name in fields:
+        assert int(offsets[name]) == getattr(_lib.GemmArgs, name).offset, name
