@@ -348,3 +348,17 @@ def test_ctypes_structs_match_the_header_layout(tmp_path):
     assert set(offsets) == set(fields)
     for name in fields:
         assert int(offsets[name]) == getattr(_lib.GemmArgs, name).offset, name
+
+
+def test_ctypes_signatures_have_the_header_argument_counts():
+    """Every prototype of the header takes as many arguments as the ctypes table passes."""
+    from nvfp4moe_b200 import _lib
+
+    text = (ROOT / "include" / "lightmoe_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    protos = re.findall(r"\b[A-Za-z_][\w\s\*]*?\b(lm_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", text, flags=re.S)
+    assert len(protos) >= 20
+    for name, params in protos:
+        params = params.strip()
+        count = 0 if params in ("void", "") else len(params.split(","))
+        assert count == len(_lib._SIGNATURES[name][1]), name
